@@ -1,0 +1,532 @@
+#!/usr/bin/env python
+"""Benchmark of the decode-attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c2|c3|c4|c5|ref_b1] [--scaling weak|strong]
+
+One "step" is one decode-attention call over one batch of synthetic KV cache.
+The default workload is benchmark configuration 2 (Llama-3-8B-shaped GQA
+decode: batch 32, 32 query / 8 kv heads, head dim 128, 4096 cache rows, bf16,
+K and V ~ 0.5 * N(0,1)). Prints ONE JSON line.
+
+metric / value : algorithmic KV-read bandwidth, GB/s, whole job, inputs
+                 resident in HBM: bytes = sum_b len_b*Hkv*D*2*sizeof + 2*B*Hq*D*sizeof
+                 per step, divided by the CUDA-event time of the timed steps
+                 (max over ranks).
+e2e            : the same metric through the public Python operator with the
+                 step's inputs (q, lens) copied from pinned host memory and the
+                 result copied back and read, every step. The KV cache is decode
+                 STATE (it persists on the device between steps), not a step
+                 input; `e2e_staged` additionally reports the staged entry point
+                 that copies the whole cache from host memory each call.
+roofline       : HBM bound; achieved = algorithmic bytes / step time (partial
+                 kernel + merge kernel + launch gap, so it understates the
+                 partial kernel alone); peak = measured copy bandwidth.
+cpu_baseline   : the reference's own CPU implementation (built from the
+                 reference sources) or, where that build is absent, the C
+                 restatement, on the host cores, on a bounded sample.
+
+`--impl reference` times that CPU implementation alone, on all host cores.
+"""
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+L2_BYTES = 126 * 1024 * 1024
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the split-KV
+# partial kernel on the default workload, from the ncu capture summarised in
+# profiles/ (None until captured).
+NCU_TRAFFIC_BYTES = {"c2": None}
+
+WORKLOADS = {
+    # name: (batch, q heads, kv heads, dim, rows, dtype, paged, description)
+    "c2": dict(B=32, Hq=32, Hkv=8, D=128, T=4096, dtype="bf16", paged=False, kv_scale=0.5,
+               desc="config 2: Llama-3-8B GQA decode, contiguous cache"),
+    "c3": dict(B=64, Hq=32, Hkv=8, D=128, T=8192, dtype="fp16", paged=True, kv_scale=1.0, lens="uniform",
+               desc="config 3: paged, ragged lengths U[128,8192], page 16"),
+    "c4": dict(B=4, Hq=64, Hkv=8, D=128, T=131072, dtype="bf16", paged=False, kv_scale=1.0,
+               desc="config 4: long-context split-KV (KV length split across GPUs when N>1)"),
+    "c5": dict(B=256, Hq=40, Hkv=8, D=128, T=32768, dtype="bf16", paged=True, kv_scale=1.0, lens="loguniform",
+               desc="config 5: serving mix, paged, lengths log-uniform [1024,32768], graph replay"),
+    "ref_b1": dict(B=1, Hq=32, Hkv=8, D=128, T=16384, dtype="bf16", paged=False, kv_scale=1.0,
+                   desc="the reference's own benchmark shape (batch 1, T=16384)"),
+}
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed
+    region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------
+# workload construction
+# ---------------------------------------------------------------------------
+
+def make_lens(w, batch):
+    import numpy as np
+    import cases
+    kind = w.get("lens")
+    if kind == "uniform":
+        return cases.config3_lens(batch)
+    if kind == "loguniform":
+        return cases.config5_lens(batch)
+    return None
+
+
+def algorithmic_bytes(w, lens, batch):
+    es = 4 if w["dtype"] == "f32" else 2
+    rows = int(lens.sum()) if lens is not None else batch * w["T"]
+    return rows * w["Hkv"] * w["D"] * 2 * es + 2 * batch * w["Hq"] * w["D"] * es
+
+
+def build_inputs(w, batch, device, seed, n_sets):
+    """Device-resident q, K/V (n_sets independent copies to defeat L2 where one
+    copy would fit in it), lens / block table."""
+    import numpy as np
+    import torch
+    import cases
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "f32": torch.float32}[w["dtype"]]
+    g = torch.Generator(device=device).manual_seed(seed)
+    lens = make_lens(w, batch)
+    q = torch.randn(batch, w["Hq"], w["D"], device=device, generator=g).to(dt)
+    sets = []
+    table = None
+    if w["paged"]:
+        table_np, nb, width = cases.paged_layout(lens)
+        table = torch.from_numpy(table_np).to(device)
+        shape = (nb, w["Hkv"], 16, w["D"])
+    else:
+        shape = (batch, w["Hkv"], w["T"], w["D"])
+    for _ in range(n_sets):
+        k = torch.empty(shape, device=device, dtype=dt)
+        v = torch.empty(shape, device=device, dtype=dt)
+        # fill in slabs to bound the fp32 temporaries
+        for t, in ((k,), (v,)):
+            flat = t.view(-1)
+            step = 1 << 26
+            for o in range(0, flat.numel(), step):
+                n = min(step, flat.numel() - o)
+                flat[o:o + n] = (torch.randn(n, device=device, generator=g) * w["kv_scale"]).to(dt)
+        sets.append((k, v))
+    lens_t = torch.from_numpy(lens).to(device) if lens is not None else None
+    return q, sets, lens_t, table, lens
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline (reference implementation on the host cores)
+# ---------------------------------------------------------------------------
+
+def cpu_baseline(w, target_seconds, threads):
+    """Times the reference's CPU decode attention on `threads` host threads,
+    each looping over single-sequence calls of the workload's shape (float32
+    values; the CPU path is float32 only). Returns (GB/s of the workload's
+    algorithmic bytes, description)."""
+    import numpy as np
+    import oracle
+    kind = "reference" if oracle.ref_available() else "port"
+    fn = oracle.ref_decode if kind == "reference" else oracle.decode
+    if kind == "port":
+        oracle.decode(np.zeros((1, 1, 4), np.float32), np.zeros((1, 1, 1, 4), np.float32),
+                      np.zeros((1, 1, 1, 4), np.float32))
+    t_rows = min(w["T"], 4096)
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((1, w["Hq"], w["D"])).astype(np.float32)
+    data = []
+    for _ in range(threads):
+        k = (rng.standard_normal((1, w["Hkv"], t_rows, w["D"])) * w["kv_scale"]).astype(np.float32)
+        data.append((k, k.copy()))
+    t0 = time.perf_counter()
+    fn(q, data[0][0], data[0][1])
+    one = time.perf_counter() - t0
+    reps = max(1, int(target_seconds / max(one, 1e-4)))
+
+    def work(i):
+        for _ in range(reps):
+            fn(q, data[i][0], data[i][1])
+
+    ths = [threading.Thread(target=work, args=(i,)) for i in range(threads)]
+    t0 = time.perf_counter()
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    dt = time.perf_counter() - t0
+    es = 4 if w["dtype"] == "f32" else 2
+    bytes_per_seq = t_rows * w["Hkv"] * w["D"] * 2 * es + 2 * w["Hq"] * w["D"] * es
+    seqs = threads * reps
+    gbs = seqs * bytes_per_seq / dt / 1e9
+    sample = ("%d single-sequence calls (%d threads x %d) of shape Hq=%d Hkv=%d D=%d T=%d, float32 values, "
+              "%.1f s; bytes counted at the workload's storage width"
+              % (seqs, threads, reps, w["Hq"], w["Hkv"], w["D"], t_rows, dt))
+    return gbs, seqs / dt, kind, sample, dt
+
+
+def run_reference_arm(args, w, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    per_step = min(8.0, max(0.3, 60.0 / args.steps))
+    for _ in range(args.warmup):
+        cpu_baseline(w, 0.2, threads)
+    vals, seqs, total_t = [], [], 0.0
+    kind = sample = None
+    for _ in range(args.steps):
+        gbs, sps, kind, sample, dt = cpu_baseline(w, per_step, threads)
+        vals.append(gbs)
+        seqs.append(sps)
+        total_t += dt
+    value = sum(vals) / len(vals)
+    line = {
+        "impl": "reference", "metric": "decode_attn_kv_read_GBps", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_t / args.steps * 1e3, "higher_is_better": True, "scaling": args.scaling,
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "seq_steps_per_s": sum(seqs) / len(seqs),
+        "config": {"workload": args.workload + ": " + w["desc"] + " (CPU sample, see cpu_baseline.sample)"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+
+def run_ours(args, w, rank, world, local_rank):
+    import numpy as np
+    import torch
+    import fusedtok_b200 as ft
+    from fusedtok_b200 import _fusedtok
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+
+    split_kv = args.workload == "c4" and world > 1
+    # work per rank
+    if args.scaling == "weak" or world == 1 or split_kv:
+        batch = w["B"]
+    else:
+        assert w["B"] % world == 0, "strong scaling shards the batch evenly"
+        batch = w["B"] // world
+    wl = dict(w)
+    if split_kv:
+        assert w["T"] % world == 0
+        wl["T"] = w["T"] // world            # this rank's slice of the cache rows
+    es = 4 if w["dtype"] == "f32" else 2
+    kv_bytes = 2 * batch * w["Hkv"] * wl["T"] * w["D"] * es
+    n_sets = 1 if kv_bytes >= 3 * L2_BYTES else int(math.ceil(3 * L2_BYTES / kv_bytes))
+    q, sets, lens_t, table, lens_np = build_inputs(wl, batch, device, seed=rank, n_sets=n_sets)
+    bytes_step = algorithmic_bytes(wl, lens_np, batch)
+    stream = torch.cuda.current_stream()
+    out = torch.empty_like(q)
+    dt_code = {"f32": 0, "bf16": 1, "fp16": 2}[w["dtype"]]
+    sfx = {"f32": "", "bf16": "_bf16", "fp16": "_fp16"}[w["dtype"]]
+    lens_ptr = lens_t.data_ptr() if lens_t is not None else 0
+
+    if split_kv:
+        from fusedtok_b200 import sharded
+        dec = sharded.SplitKVDecoder(batch, w["Hq"], w["Hkv"], w["D"], q.dtype, device, dist.group.WORLD)
+
+    def step(i):
+        k, v = sets[i % n_sets]
+        if split_kv:
+            dec.decode(q, k, v, None, out)
+        elif w["paged"]:
+            getattr(_fusedtok, "attention_decode_paged_launch" + sfx)(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), table.data_ptr(), lens_ptr, out.data_ptr(),
+                batch, w["Hq"], w["Hkv"], 16, table.shape[1], w["D"], stream.cuda_stream)
+        else:
+            getattr(_fusedtok, "attention_decode_launch" + sfx)(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), lens_ptr, out.data_ptr(),
+                batch, w["Hq"], w["Hkv"], wl["T"], w["D"], stream.cuda_stream)
+
+    use_graph = args.graph or args.workload == "c5"
+    graphs = None
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    if use_graph and not split_kv:
+        graphs = []
+        for i in range(n_sets):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                step(i)
+            graphs.append(g)
+        for g in graphs:
+            g.replay()
+        torch.cuda.synchronize()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed region: K steps, inputs resident
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    _fusedtok.attention_launch_count(reset=True)
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        if graphs:
+            graphs[i % n_sets].replay()
+        else:
+            step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = _fusedtok.attention_launch_count() if not graphs else 2 * args.steps
+    # a few more steps keep the clock sampler busy long enough to see the load
+    t_end = time.perf_counter() + 1.0
+    j = 0
+    while time.perf_counter() < t_end:
+        for _ in range(50):
+            (graphs[j % n_sets].replay() if graphs else step(j))
+            j += 1
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    status = _fusedtok.attention_device_status()
+
+    # ---- end-to-end region through the public operator: q, lens from pinned host memory
+    q_host = q.cpu().pin_memory()
+    out_host = torch.empty_like(q_host).pin_memory()
+    lens_host = lens_t.cpu().pin_memory() if lens_t is not None else None
+    q_dev = torch.empty_like(q)
+    lens_dev = torch.empty_like(lens_t) if lens_t is not None else None
+
+    def e2e_step(i):
+        k, v = sets[i % n_sets]
+        q_dev.copy_(q_host, non_blocking=True)
+        if lens_dev is not None:
+            lens_dev.copy_(lens_host, non_blocking=True)
+        if split_kv:
+            o = torch.empty_like(q_dev)
+            dec.decode(q_dev, k, v, None, o)
+        elif w["paged"]:
+            if w["Hq"] // w["Hkv"] in (1, 2, 4, 8, 16):
+                o = ft.attention_decode_paged(q_dev, k, v, table, lens_dev)
+            else:   # the wrapper keeps the reference's group rule; the launcher is the public entry for other groups
+                o = torch.empty_like(q_dev)
+                getattr(_fusedtok, "attention_decode_paged_launch" + sfx)(
+                    q_dev.data_ptr(), k.data_ptr(), v.data_ptr(), table.data_ptr(), lens_dev.data_ptr(),
+                    o.data_ptr(), batch, w["Hq"], w["Hkv"], 16, table.shape[1], w["D"], stream.cuda_stream)
+        else:
+            o = ft.attention_decode(q_dev, k, v, lens_dev)
+        out_host.copy_(o, non_blocking=True)
+        torch.cuda.synchronize()
+        return float(out_host[0, 0, 0])     # the host reads the result
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    h2d = q_host.numel() * q_host.element_size() + (lens_host.numel() * 4 if lens_host is not None else 0)
+    d2h = out_host.numel() * out_host.element_size()
+
+    # ---- max over ranks
+    if dist is not None:
+        t = torch.tensor([ms, e2e_s], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1])
+        tot = torch.tensor([float(bytes_step), float(batch)], device=device, dtype=torch.float64)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        job_bytes, job_seqs = float(tot[0]), float(tot[1])
+        if split_kv:
+            job_seqs = float(batch)            # every rank works on the same sequences
+    else:
+        job_bytes, job_seqs = float(bytes_step), float(batch)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    ms_step = ms / args.steps
+    value = job_bytes / (ms_step * 1e-3) / 1e9
+    e2e_value = job_bytes / (e2e_s / args.steps) / 1e9
+    peak, peak_kind = measured_peak()
+    per_gpu = bytes_step / (ms_step * 1e-3) / 1e9
+    line = {
+        "metric": "decode_attn_kv_read_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong" if split_kv else args.scaling,
+        "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "seq_steps_per_s": job_seqs / (ms_step * 1e-3),
+        "pct_of_8TBs_per_gpu": 100.0 * per_gpu / NOMINAL_HBM_GBS,
+        "config": {
+            "workload": args.workload + ": " + w["desc"],
+            "batch_per_gpu": batch, "q_heads": w["Hq"], "kv_heads": w["Hkv"], "head_dim": w["D"],
+            "cache_rows": wl["T"], "paged": w["paged"], "page": 16 if w["paged"] else None,
+            "algorithmic_bytes_per_step_per_gpu": bytes_step,
+            "l2": ("inputs larger than L2 (%.0f MB of K/V per step)" % (kv_bytes / 1e6)) if n_sets == 1 else
+                  ("rotating over %d independent K/V sets (%.0f MB each) so reads come from HBM" % (n_sets, kv_bytes / 1e6)),
+            "parallelism": ("kv-length split x%d + all-gather merge" % world) if split_kv else
+                           ("batch-sharded x%d, no communication" % world),
+            "cuda_graph": bool(graphs),
+        },
+        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
+                     "frac": per_gpu / peak, "peak_kind": "of " + peak_kind,
+                     "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                     "note": "achieved = algorithmic bytes / whole step time (partial + merge kernels)"},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_s / args.steps * 1e3,
+                "note": "public operator; q/lens H2D from pinned memory and result D2H + host read every step; "
+                        "KV cache is device-resident decode state"},
+        "gpu_launches": launches,
+        "device_status": status,
+        "clocks": clocks,
+    }
+
+    if world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        gbs, sps, kind, sample, _ = cpu_baseline(w, 12.0, threads)
+        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": kind,
+                                "sample": sample, "seq_steps_per_s": sps}
+        # the reference's own GPU kernels on the same inputs (informational)
+        try:
+            import oracle
+            if oracle.ref_available() and not w["paged"]:
+                k, v = sets[0]
+                yr = torch.empty_like(q)
+                for _ in range(3):
+                    oracle.ref_gpu_decode_launch(dt_code, q.data_ptr(), k.data_ptr(), v.data_ptr(), lens_ptr,
+                                                 yr.data_ptr(), batch, w["Hq"], w["Hkv"], wl["T"], w["D"],
+                                                 stream.cuda_stream)
+                torch.cuda.synchronize()
+                e0.record()
+                for i in range(10):
+                    k, v = sets[i % n_sets]
+                    oracle.ref_gpu_decode_launch(dt_code, q.data_ptr(), k.data_ptr(), v.data_ptr(), lens_ptr,
+                                                 yr.data_ptr(), batch, w["Hq"], w["Hkv"], wl["T"], w["D"],
+                                                 stream.cuda_stream)
+                e1.record()
+                torch.cuda.synchronize()
+                rms = e0.elapsed_time(e1) / 10
+                line["reference_gpu_kernel"] = {"ms_per_step": rms, "GBps": bytes_step / (rms * 1e-3) / 1e9,
+                                                "note": "the reference's CUDA kernels compiled for sm_100a, same inputs"}
+        except Exception as exc:   # informational only
+            line["reference_gpu_kernel"] = {"error": str(exc)[:200]}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, w, rank)
+        return
+    if args.gpus > 1 and "RANK" not in os.environ:
+        # not under a launcher yet: start one rank per GPU
+        import socket
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(args.gpus),
+               "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    run_ours(args, w, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

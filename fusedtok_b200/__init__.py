@@ -1,0 +1,289 @@
+"""fusedtok_b200 - fusedtok's decode-attention operators on B200 (sm_100a).
+
+Drop-in for the decode-attention path of fusedtok's Python surface
+(reference: python/fusedtok/__init__.py:710-788 ``attention_decode``,
+:849-940 ``attention_decode_paged``): same signatures, same validation and
+error types, zero-copy on CUDA torch tensors, stream-ordered and CUDA-graph
+capturable. Underneath is a from-scratch CUDA library (``csrc/``) reached
+through a C ABI (``include/fusedtok_b200.h``).
+
+One deliberate difference: there is no CPU implementation. The reference runs
+host inputs without ``cuda=True`` through its float32 CPU reference; here that
+combination raises ``RuntimeError`` - pass CUDA tensors (zero-copy path) or
+``cuda=True`` (staged path: host arrays are copied to the GPU and back).
+"""
+
+import numpy as np
+
+from . import _fusedtok
+
+try:
+    import torch
+    _HAS_TORCH = True
+except ImportError:  # pragma: no cover - torch is optional, as in the reference
+    torch = None
+    _HAS_TORCH = False
+
+__version__ = "0.1.0"
+__all__ = ["attention_decode", "attention_decode_paged", "cuda_available"]
+
+_PAGED_GROUPS = (1, 2, 4, 8, 16)
+
+
+def cuda_available():
+    """True if a usable CUDA device is present."""
+    return _fusedtok.cuda_available()
+
+
+# ---------------------------------------------------------------------------
+# helpers (reference: python/fusedtok/__init__.py:108-367)
+# ---------------------------------------------------------------------------
+
+def _is_torch(x):
+    return _HAS_TORCH and torch.is_tensor(x)
+
+
+def _check_torch_att(t, name):
+    """CUDA tensor, float32 / bfloat16 / float16, contiguous
+    (reference: _check_torch_att, :172-182). A host pointer must never reach a
+    kernel, so CPU tensors are rejected before any launch."""
+    if not (_is_torch(t) and t.is_cuda):
+        raise TypeError(f"{name} must be a CUDA tensor (got a CPU tensor on the zero-copy path)")
+    if t.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+        raise TypeError(f"{name} must be float32, bfloat16 or float16, got {t.dtype} "
+                        "(convert with .to(torch.float32))")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _att_launch_fn(t, base):
+    if t.dtype is torch.bfloat16:
+        return getattr(_fusedtok, base + "_bf16")
+    if t.dtype is torch.float16:
+        return getattr(_fusedtok, base + "_fp16")
+    return getattr(_fusedtok, base)
+
+
+def _cuda_stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _host_int_array(t, name="values"):
+    """Host-origin value -> int numpy array; None for a device tensor (whose
+    values are never read back). Non-integral host input is rejected
+    (reference: _host_int_array, :220-235)."""
+    if _is_torch(t):
+        if t.is_cuda:
+            return None
+        host = t.detach().cpu().numpy()
+    else:
+        host = np.asarray(t)
+    if host.size and not np.issubdtype(host.dtype, np.integer):
+        raise TypeError(f"{name} must hold integer values (got dtype {host.dtype})")
+    return host
+
+
+def _host_lens_checked(lens, batch, limit):
+    host = _host_int_array(lens, "lens")
+    if host is None:
+        return None
+    host = np.ascontiguousarray(host, dtype=np.int32)
+    if host.ndim != 1 or host.shape[0] != batch:
+        raise ValueError("lens must be 1-D with batch entries")
+    if host.size and (host.min() < 0 or host.max() > limit):
+        raise ValueError(f"lens entries must be in [0, {limit}]")
+    return host
+
+
+def _i32_cuda(t):
+    if t.dtype is not torch.int32:
+        t = t.to(torch.int32)
+    if not t.is_contiguous():
+        t = t.contiguous()
+    return t
+
+
+def _lens_arg(lens, batch, limit, device):
+    """Host values are validated then uploaded; a device tensor is trusted
+    (reference: _lens_arg, :278-290)."""
+    host = _host_lens_checked(lens, batch, limit)
+    if host is not None:
+        return torch.from_numpy(host).to(device)
+    lt = _i32_cuda(lens)
+    if lt.ndim != 1 or lt.numel() != batch:
+        raise ValueError("lens must be 1-D with batch entries")
+    return lt
+
+
+def _host_table_checked(table, batch, nblocks):
+    host = _host_int_array(table, "block_table")
+    if host is None:
+        return None
+    host = np.ascontiguousarray(host, dtype=np.int32)
+    if host.ndim != 2 or host.shape[0] != batch:
+        raise ValueError("block_table must be [B, S] with batch rows")
+    if host.size and (host.min() < 0 or host.max() >= nblocks):
+        raise ValueError(f"block_table entries must be in [0, {nblocks})")
+    return host
+
+
+def _table_arg(table, batch, nblocks, device):
+    host = _host_table_checked(table, batch, nblocks)
+    if host is not None:
+        return torch.from_numpy(host).to(device)
+    bt = _i32_cuda(table)
+    if bt.ndim != 2 or bt.shape[0] != batch:
+        raise ValueError("block_table must be [B, S] with batch rows")
+    return bt
+
+
+def _as_numpy(x, name):
+    """Anything host-side -> float32 C-contiguous numpy (reference: :346-356)."""
+    if _is_torch(x):
+        if x.is_cuda:
+            raise TypeError(f"{name} is a CUDA tensor while another input is host-side; "
+                            "move all inputs to the same device")
+        return np.ascontiguousarray(x.detach().to(torch.float32).numpy())
+    return np.ascontiguousarray(np.asarray(x, dtype=np.float32))
+
+
+def _no_cpu_path():
+    raise RuntimeError(
+        "fusedtok_b200 has no CPU implementation: pass CUDA tensors (zero-copy) or cuda=True "
+        "(host arrays staged through the GPU)")
+
+
+# ---------------------------------------------------------------------------
+# operators
+# ---------------------------------------------------------------------------
+
+def attention_decode(q, k_cache, v_cache, lens=None, *, cuda=False):
+    """Single-token (decode step) attention with GQA over a contiguous cache:
+
+    ``out[b, h] = softmax(q[b,h] . K[b,kv(h)]^T / sqrt(D)) . V[b,kv(h)]``
+
+    q: [B, Hq, D]; k_cache / v_cache: [B, Hkv, T, D]; lens: optional [B] valid
+    lengths (<= T). Query head h uses kv head ``h // (Hq // Hkv)``. A length of
+    0 gives a zero row. CUDA tensors may be float32, bfloat16 or float16 (output
+    dtype = input dtype, float32 accumulation). Host lens values are validated;
+    a CUDA lens tensor is trusted and never read back.
+    Reference: python/fusedtok/__init__.py:710-788.
+    """
+    if _is_torch(q) and q.is_cuda:
+        for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache)):
+            _check_torch_att(t, name)
+        for name, t in (("k_cache", k_cache), ("v_cache", v_cache)):
+            if t.dtype is not q.dtype:
+                raise TypeError(f"{name} must have the same dtype as q")
+        if q.ndim != 3 or k_cache.ndim != 4 or v_cache.ndim != 4:
+            raise ValueError("q must be [B, Hq, D]; k/v caches [B, Hkv, T, D]")
+        b, hq, d = q.shape
+        b2, hkv, t_rows, d2 = k_cache.shape
+        if (b2, d2) != (b, d) or v_cache.shape != k_cache.shape:
+            raise ValueError("k_cache/v_cache must match q's batch and dim")
+        if hq < 1 or hkv < 1:
+            raise ValueError("head counts must be >= 1")
+        if hq % hkv:
+            raise ValueError("q heads must be a multiple of kv heads")
+        lens_ptr = None
+        if lens is not None:
+            lt = _lens_arg(lens, b, t_rows, q.device)
+            lens_ptr = lt.data_ptr()
+        out = torch.empty((b, hq, d), dtype=q.dtype, device=q.device)
+        if b * hq > 0:
+            with torch.cuda.device(q.device):
+                _att_launch_fn(q, "attention_decode_launch")(
+                    q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), lens_ptr,
+                    out.data_ptr(), b, hq, hkv, t_rows, d, _cuda_stream())
+        return out
+    if not cuda:
+        _no_cpu_path()
+    arr_q = _as_numpy(q, "q")
+    arr_k = _as_numpy(k_cache, "k_cache")
+    arr_v = _as_numpy(v_cache, "v_cache")
+    if arr_q.ndim != 3 or arr_k.ndim != 4 or arr_v.ndim != 4:
+        raise ValueError("q must be [B, Hq, D]; k/v caches [B, Hkv, T, D]")
+    b, hq, d = arr_q.shape
+    b2, hkv, t_rows, d2 = arr_k.shape
+    if (b2, d2) != (b, d) or arr_v.shape != arr_k.shape:
+        raise ValueError("k_cache/v_cache must match q's batch and dim")
+    if hq % hkv:
+        raise ValueError("q heads must be a multiple of kv heads")
+    if lens is None:
+        arr_lens = None
+    else:
+        arr_lens = _host_lens_checked(lens, b, t_rows)
+        if arr_lens is None:
+            raise TypeError("lens must be a host array on this path")
+    res = _fusedtok.attention_decode(arr_q, arr_k, arr_v, arr_lens, b, hq, hkv, t_rows, d)
+    return torch.from_numpy(res) if _is_torch(q) else res
+
+
+def attention_decode_paged(q, k_pool, v_pool, block_table, lens=None, *, cuda=False):
+    """Decode-step attention with GQA over a PAGED cache: pools
+    [Nb, Hkv, P, D], block_table [B, S] mapping token t of sequence b to pool
+    block ``block_table[b, t // P]`` at offset ``t % P``; lens None = S * P rows.
+    GQA group sizes 1/2/4/8/16 (the reference's contract; the native launchers
+    accept any group). Host table / lens values are validated, device tensors
+    trusted. Reference: python/fusedtok/__init__.py:849-940.
+    """
+    if _is_torch(q) and q.is_cuda:
+        for name, t in (("q", q), ("k_pool", k_pool), ("v_pool", v_pool)):
+            _check_torch_att(t, name)
+        for name, t in (("k_pool", k_pool), ("v_pool", v_pool)):
+            if t.dtype is not q.dtype:
+                raise TypeError(f"{name} must have the same dtype as q")
+        if q.ndim != 3 or k_pool.ndim != 4 or v_pool.ndim != 4:
+            raise ValueError("q must be [B, Hq, D]; pools [Nb, Hkv, P, D]")
+        b, hq, d = q.shape
+        nb, hkv, page, d2 = k_pool.shape
+        if d2 != d or v_pool.shape != k_pool.shape:
+            raise ValueError("pools must match q's dim and each other")
+        if hq < 1 or hkv < 1:
+            raise ValueError("head counts must be >= 1")
+        if hq % hkv:
+            raise ValueError("q heads must be a multiple of kv heads")
+        if hq // hkv not in _PAGED_GROUPS:
+            raise ValueError("paged decode supports GQA group sizes 1/2/4/8/16 "
+                             "(use attention_decode otherwise)")
+        bt = _table_arg(block_table, b, nb, q.device)
+        s_width = bt.shape[1]
+        lens_ptr = None
+        if lens is not None:
+            lt = _lens_arg(lens, b, s_width * page, q.device)
+            lens_ptr = lt.data_ptr()
+        out = torch.empty((b, hq, d), dtype=q.dtype, device=q.device)
+        if b * hq > 0:
+            with torch.cuda.device(q.device):
+                _att_launch_fn(q, "attention_decode_paged_launch")(
+                    q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), bt.data_ptr(), lens_ptr,
+                    out.data_ptr(), b, hq, hkv, page, s_width, d, _cuda_stream())
+        return out
+    if not cuda:
+        _no_cpu_path()
+    arr_q = _as_numpy(q, "q")
+    arr_k = _as_numpy(k_pool, "k_pool")
+    arr_v = _as_numpy(v_pool, "v_pool")
+    if arr_q.ndim != 3 or arr_k.ndim != 4 or arr_v.ndim != 4:
+        raise ValueError("q must be [B, Hq, D]; pools [Nb, Hkv, P, D]; block_table [B, S]")
+    b, hq, d = arr_q.shape
+    nb, hkv, page, d2 = arr_k.shape
+    arr_t = _host_table_checked(block_table, b, nb)
+    if arr_t is None:
+        raise TypeError("block_table must be a host array on this path")
+    if d2 != d or arr_v.shape != arr_k.shape:
+        raise ValueError("pools must match q's dim and each other")
+    if hq % hkv:
+        raise ValueError("q heads must be a multiple of kv heads")
+    if hq // hkv not in _PAGED_GROUPS:
+        raise ValueError("paged decode supports GQA group sizes 1/2/4/8/16 "
+                         "(use attention_decode otherwise)")
+    if lens is None:
+        arr_lens = None
+    else:
+        arr_lens = _host_lens_checked(lens, b, arr_t.shape[1] * page)
+        if arr_lens is None:
+            raise TypeError("lens must be a host array on this path")
+    res = _fusedtok.attention_decode_paged(arr_q, arr_k, arr_v, arr_t, arr_lens, b, hq, hkv, page,
+                                           arr_t.shape[1], nb, d)
+    return torch.from_numpy(res) if _is_torch(q) else res

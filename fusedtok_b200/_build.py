@@ -1,0 +1,46 @@
+"""In-tree build of the CUDA library (sm_100a only).
+
+``python fusedtok_b200/_build.py`` compiles ``csrc/fusedtok_b200.cu`` into
+``fusedtok_b200/libfusedtok_b200.so`` with nvcc. The library is the whole
+product: there is no other backend and no CPU fallback, so importing the
+package without it fails.
+"""
+
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libfusedtok_b200.so")
+SOURCES = ["fusedtok_b200.cu"]
+HEADERS = ["common.cuh", "decode_tc.cuh", "decode_simt.cuh", "merge.cuh",
+           os.path.join("..", "..", "include", "fusedtok_b200.h")]
+
+NVCC_FLAGS = [
+    "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+    "-Xcompiler", "-fPIC", "-shared", "-cudart", "static",
+]
+
+
+def stale():
+    if not os.path.exists(LIB):
+        return True
+    t = os.path.getmtime(LIB)
+    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
+    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+
+
+def build(force=False, verbose=False):
+    if not force and not stale():
+        return LIB
+    cmd = ["nvcc"] + NVCC_FLAGS
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB]
+    subprocess.check_call(cmd)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

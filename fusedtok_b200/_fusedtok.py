@@ -1,0 +1,182 @@
+"""ctypes binding of ``libfusedtok_b200.so`` exposing the function names and
+keyword names of the reference's pybind11 module ``fusedtok._fusedtok`` for the
+decode-attention path (reference: src/bindings.cpp:2374-2613), so code and
+tests written against ``_fusedtok.attention_decode_launch(...)`` run unchanged.
+
+Pointer arguments are Python ints (``tensor.data_ptr()``); ``lens`` may be
+``None`` or ``0`` for "all rows valid" (reference: opt_ptr,
+src/bindings.cpp:277-283). Status codes of the C ABI are mapped back to the
+exceptions the reference raises: invalid argument -> ValueError, runtime
+failure -> RuntimeError.
+
+There is no CPU implementation here: the reference's ``*_cpu`` bindings have
+no counterpart, and loading fails loudly when the CUDA library is missing.
+"""
+
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libfusedtok_b200.so")
+
+if not os.path.exists(_LIB_PATH):
+    raise ImportError(
+        "fusedtok_b200: %s is missing - build it with `python fusedtok_b200/_build.py` "
+        "(there is no fallback path)" % _LIB_PATH)
+
+_lib = ctypes.CDLL(_LIB_PATH)
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_sz = ctypes.c_size_t
+
+_lib.fusedtok_last_error.restype = ctypes.c_char_p
+_lib.fusedtok_cuda_available.restype = _i
+for _n in ("", "_bf16", "_fp16"):
+    getattr(_lib, "fusedtok_attention_decode_launch" + _n).argtypes = [_vp] * 5 + [_i] * 5 + [_sz]
+    getattr(_lib, "fusedtok_attention_decode_paged_launch" + _n).argtypes = [_vp] * 6 + [_i] * 6 + [_sz]
+_lib.fusedtok_attention_decode.argtypes = [_vp] * 5 + [_i] * 5
+_lib.fusedtok_attention_decode_paged.argtypes = [_vp] * 6 + [_i] * 7
+_lib.fusedtok_attention_decode_partial_launch.argtypes = [_i] + [_vp] * 5 + [_i] * 5 + [_sz]
+_lib.fusedtok_attention_merge_partials_launch.argtypes = [_i, _vp, _i, _vp, _i, _i, _i, _sz]
+_lib.fusedtok_attention_partial_floats.argtypes = [_i, _i, _i]
+_lib.fusedtok_attention_partial_floats.restype = ctypes.c_longlong
+_lib.fusedtok_attention_device_status.argtypes = [ctypes.POINTER(_i)]
+_lib.fusedtok_attention_launch_count.argtypes = [_i]
+_lib.fusedtok_attention_launch_count.restype = ctypes.c_longlong
+
+# every symbol include/fusedtok_b200.h declares
+EXPORTS = (
+    "fusedtok_last_error", "fusedtok_cuda_available",
+    "fusedtok_attention_decode_launch", "fusedtok_attention_decode_launch_bf16",
+    "fusedtok_attention_decode_launch_fp16",
+    "fusedtok_attention_decode_paged_launch", "fusedtok_attention_decode_paged_launch_bf16",
+    "fusedtok_attention_decode_paged_launch_fp16",
+    "fusedtok_attention_decode", "fusedtok_attention_decode_paged",
+    "fusedtok_attention_decode_partial_launch", "fusedtok_attention_partial_floats",
+    "fusedtok_attention_merge_partials_launch",
+    "fusedtok_attention_device_status", "fusedtok_attention_launch_count",
+)
+
+
+def _check(rc):
+    if rc == 0:
+        return
+    msg = _lib.fusedtok_last_error().decode("utf-8", "replace")
+    if rc == 1:
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def _opt(p):
+    return None if (p is None or p == 0) else int(p)
+
+
+def cuda_available():
+    return bool(_lib.fusedtok_cuda_available())
+
+
+def _make_launch(suffix):
+    fn = getattr(_lib, "fusedtok_attention_decode_launch" + suffix)
+
+    def attention_decode_launch(q, k, v, lens, out, batch, hq, hkv, t_seq, dim, stream=0):
+        _check(fn(int(q), int(k), int(v), _opt(lens), int(out), batch, hq, hkv, t_seq, dim,
+                  int(stream)))
+    attention_decode_launch.__name__ = "attention_decode_launch" + suffix
+    return attention_decode_launch
+
+
+def _make_paged_launch(suffix):
+    fn = getattr(_lib, "fusedtok_attention_decode_paged_launch" + suffix)
+
+    def attention_decode_paged_launch(q, k_pool, v_pool, table, lens, out, batch, hq, hkv, page,
+                                      tbl_width, dim, stream=0):
+        _check(fn(int(q), int(k_pool), int(v_pool), int(table), _opt(lens), int(out), batch, hq,
+                  hkv, page, tbl_width, dim, int(stream)))
+    attention_decode_paged_launch.__name__ = "attention_decode_paged_launch" + suffix
+    return attention_decode_paged_launch
+
+
+attention_decode_launch = _make_launch("")
+attention_decode_launch_bf16 = _make_launch("_bf16")
+attention_decode_launch_fp16 = _make_launch("_fp16")
+attention_decode_paged_launch = _make_paged_launch("")
+attention_decode_paged_launch_bf16 = _make_paged_launch("_bf16")
+attention_decode_paged_launch_fp16 = _make_paged_launch("_fp16")
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data
+
+
+def attention_decode(q, k, v, lens, batch, hq, hkv, t_seq, dim):
+    """Staged path: float32 host arrays in, host array out
+    (reference: src/bindings.cpp:2402-2436)."""
+    q, k, v, lens = _f32(q), _f32(k), _f32(v), _i32(lens)
+    if (q.size != batch * hq * dim or k.size != batch * hkv * t_seq * dim or v.size != k.size):
+        raise ValueError("attention operand size mismatch")
+    if lens is not None and lens.size != batch:
+        raise ValueError("lens must have batch entries")
+    out = np.empty((batch, hq, dim), np.float32)
+    _check(_lib.fusedtok_attention_decode(_ptr(q), _ptr(k), _ptr(v), _ptr(lens), _ptr(out), batch,
+                                          hq, hkv, t_seq, dim))
+    return out
+
+
+def attention_decode_paged(q, k_pool, v_pool, table, lens, batch, hq, hkv, page, tbl_width,
+                           num_blocks, dim):
+    """Staged paged path (reference: src/bindings.cpp:2507-2565)."""
+    q, k_pool, v_pool = _f32(q), _f32(k_pool), _f32(v_pool)
+    table, lens = _i32(table), _i32(lens)
+    if (q.size != batch * hq * dim or k_pool.size != num_blocks * hkv * page * dim
+            or v_pool.size != k_pool.size or table.size != batch * tbl_width):
+        raise ValueError("attention operand size mismatch")
+    if lens is not None and lens.size != batch:
+        raise ValueError("lens must have batch entries")
+    out = np.empty((batch, hq, dim), np.float32)
+    _check(_lib.fusedtok_attention_decode_paged(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table),
+                                                _ptr(lens), _ptr(out), batch, hq, hkv, page,
+                                                tbl_width, num_blocks, dim))
+    return out
+
+
+def attention_decode_partial_launch(dtype, q, k, v, lens, partial, batch, hq, hkv, t_seq, dim,
+                                    stream=0):
+    """Raw (m, l, acc) triples over this GPU's slice of the cache rows
+    (multi-GPU KV-length split; dtype 0 f32, 1 bf16, 2 fp16)."""
+    _check(_lib.fusedtok_attention_decode_partial_launch(
+        dtype, int(q), int(k), int(v), _opt(lens), int(partial), batch, hq, hkv, t_seq, dim,
+        int(stream)))
+
+
+def attention_partial_floats(batch, hq, dim):
+    """Length in float32 elements of one triple block for (batch, hq, dim)."""
+    return int(_lib.fusedtok_attention_partial_floats(batch, hq, dim))
+
+
+def attention_merge_partials_launch(dtype, partials, n_parts, out, batch, hq, dim, stream=0):
+    """Fold n_parts gathered triple blocks into the normalised output."""
+    _check(_lib.fusedtok_attention_merge_partials_launch(
+        dtype, int(partials), n_parts, int(out), batch, hq, dim, int(stream)))
+
+
+def attention_device_status():
+    """Synchronise the current device and return (then clear) the kernels'
+    status word; 0 means every bounded device-side wait completed."""
+    st = _i(0)
+    _check(_lib.fusedtok_attention_device_status(ctypes.byref(st)))
+    return st.value
+
+
+def attention_launch_count(reset=False):
+    return int(_lib.fusedtok_attention_launch_count(1 if reset else 0))

@@ -1,0 +1,483 @@
+// Split-KV partial kernel for 16-bit caches (bf16 / fp16), head dim 64 or 128,
+// up to 16 query heads per kv head and chunk: the sm_100a counterpart of the
+// reference's attn_decode_kernel / attn_split_kernel / attn_split_paged_kernel
+// (src/attention.cu:195-319, 336-466, 567-693), redesigned around the memory
+// system instead of translated.
+//
+//  * One persistent CTA per SM: 1 producer warp + 8 consumer warps.
+//  * The producer streams K/V tiles (64 cache rows) into a shared-memory ring
+//    with TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, L2 evict-first),
+//    completion signalled on mbarriers. It runs ahead across unit boundaries,
+//    so the HBM stream never drains while consumers finish a unit.
+//    Contiguous cache: one [64 x 64-element] box per half of D for K and for V.
+//    Paged cache: the block table is read one entry per lane and every lane
+//    issues the boxes of its own page, so the indirection costs no per-row
+//    integer divide and no dependent load in the consumers.
+//  * The query heads of one GQA group are the M rows of an m16n8k16 tensor-core
+//    tile (S = Q K^T, O += P V), so every K/V byte is read from HBM once and
+//    from shared memory once, for all heads of the group. Tiles alternate
+//    between two groups of 4 consumer warps; each warp owns 16 rows of a tile
+//    and keeps an fp32 online-softmax state (m, l, O) in registers.
+//  * At the end of a segment the 8 warp states are folded through shared
+//    memory and either finished in place or written to the workspace.
+//
+// Every wait on an mbarrier is bounded (wall-clock limit); on expiry the
+// kernel records a status code, stops waiting and still runs to completion,
+// so a lost copy can never hang the GPU.
+#pragma once
+
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace ftk {
+
+constexpr int NCW = 8;                        // consumer warps
+constexpr int TC_THREADS = (NCW + 1) * 32;    // + 1 producer warp
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+template <int D> struct TcCfg {
+    static constexpr int NH = D / 64;                  // 128-byte column blocks per row
+    static constexpr int KV_BYTES = TILE * D * 2;      // K (or V) bytes per stage
+    static constexpr int STAGE_BYTES = 2 * KV_BYTES;
+    static constexpr int NS = (D == 128) ? 5 : 8;      // ring depth
+    static constexpr int ACC_STRIDE = D + 8;           // floats; keeps float2 stores 2-way at worst
+    static constexpr int SCRATCH_BYTES = NCW * 8 * ACC_STRIDE * 4;
+    static constexpr int OFF_SCRATCH = NS * STAGE_BYTES;
+    static constexpr int OFF_ML = OFF_SCRATCH + SCRATCH_BYTES;       // [NCW][8] float2
+    static constexpr int OFF_SCALE = OFF_ML + NCW * 8 * 8;           // [NCW][8] float
+    static constexpr int OFF_GLOB = OFF_SCALE + NCW * 8 * 4;         // [8] float2 (m, l) merged
+    static constexpr int OFF_BAR = OFF_GLOB + 8 * 8;                 // full[NS], empty[NS]
+    static constexpr int OFF_SCHED = OFF_BAR + 2 * NS * 8;
+    static constexpr int OFF_ABORT = OFF_SCHED + (int)sizeof(SchedShared);
+    static constexpr int SMEM_BYTES = OFF_ABORT + 16;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait. Returns false when the limit expired or another warp already
+// gave up; the caller then carries on without the data.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(status, ST_OK, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar), "l"(pol)
+        : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ---- the kernel ------------------------------------------------------------
+// T: __nv_bfloat16 or __half. D: 64 or 128. GP: 8 or 16 = query-head rows of
+// the MMA tile that carry data (heads per unit <= GP). PAGED selects the
+// block-table front end; PAGE_LE_TILE says whether a page is at most one tile.
+template <typename T, int D, int GP, bool PAGED>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                 const DecodeParams p) {
+    using Cfg = TcCfg<D>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    SchedShared* sh = reinterpret_cast<SchedShared*>(smem + Cfg::OFF_SCHED);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_ABORT);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_full = smem_base + Cfg::OFF_BAR;
+    const uint32_t bar_empty = bar_full + Cfg::NS * 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        if (smem_base & 1023u) {      // the swizzle pattern assumes 1024-byte aligned stages
+            *abort_flag = 1;
+            atomicCAS(p.status, ST_OK, ST_SMEM_MISALIGNED);
+        }
+        for (int s = 0; s < Cfg::NS; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 4);     // the 4 warps of the group that consumed the stage
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    Walker w;
+    if (!sched_init<T>(p, sh, w)) return;      // block-uniform
+    const long long total = sh->total;
+    const long long g_begin = w.g;
+    const int upb_nch = p.NCH;
+
+    if (warp == NCW) {
+        // ===================== producer warp =====================
+        if (*abort_flag) return;
+        const uint64_t pol = policy_evict_first();
+        int issued = 0;
+        for (long long i = 0; w.g < w.end; ++i) {
+            const int s = (int)(i % Cfg::NS);
+            const uint32_t ph = (uint32_t)((i / Cfg::NS) & 1);
+            const bool ok = mbar_wait(bar_empty + s * 8, ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY_TIMEOUT);
+            if (!ok) break;
+            const int kv = w.ub / upb_nch;
+            const uint32_t dst_k = smem_base + s * Cfg::STAGE_BYTES;
+            const uint32_t dst_v = dst_k + Cfg::KV_BYTES;
+            const uint32_t fb = bar_full + s * 8;
+            if constexpr (!PAGED) {
+                if (lane == 0) {
+                    const int row = (w.b * p.Hkv + kv) * p.T + w.ti * TILE;
+                    mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+#pragma unroll
+                    for (int h = 0; h < Cfg::NH; ++h) {
+                        tma_load_2d(dst_k + h * (TILE * 128), &tm_k, h * 64, row, fb, pol);
+                        tma_load_2d(dst_v + h * (TILE * 128), &tm_v, h * 64, row, fb, pol);
+                    }
+                }
+            } else {
+                const int t0 = w.ti * TILE;
+                const int valid = min(TILE, w.len - t0);
+                if (p.page <= TILE) {
+                    const int npg = (valid + p.page - 1) / p.page;
+                    if (lane == 0) mbar_expect_tx(fb, (uint32_t)(npg * p.page * D * 4));
+                    __syncwarp();
+                    if (lane < npg) {
+                        const int blk = __ldg(p.table + (size_t)w.b * p.tbl_width + t0 / p.page + lane);
+                        const int row = (blk * p.Hkv + kv) * p.page;
+                        const uint32_t off = (uint32_t)(lane * p.page) * 128u;
+#pragma unroll
+                        for (int h = 0; h < Cfg::NH; ++h) {
+                            tma_load_2d(dst_k + h * (TILE * 128) + off, &tm_k, h * 64, row, fb, pol);
+                            tma_load_2d(dst_v + h * (TILE * 128) + off, &tm_v, h * 64, row, fb, pol);
+                        }
+                    }
+                } else if (lane == 0) {
+                    const int blk = __ldg(p.table + (size_t)w.b * p.tbl_width + t0 / p.page);
+                    const int row = (blk * p.Hkv + kv) * p.page + (t0 % p.page);
+                    mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+#pragma unroll
+                    for (int h = 0; h < Cfg::NH; ++h) {
+                        tma_load_2d(dst_k + h * (TILE * 128), &tm_k, h * 64, row, fb, pol);
+                        tma_load_2d(dst_v + h * (TILE * 128), &tm_v, h * 64, row, fb, pol);
+                    }
+                }
+            }
+            ++issued;
+            walker_advance(p, w);
+        }
+        // If something went wrong, do not leave the CTA while our own copies
+        // may still be landing in its shared memory: wait (bounded) for the
+        // last phase of every stage that was issued.
+        if (*abort_flag) {
+            const int first = issued > Cfg::NS ? issued - Cfg::NS : 0;
+            for (int i = first; i < issued; ++i) {
+                const unsigned long long t0 = global_ns();
+                while (!mbar_try_wait(bar_full + (i % Cfg::NS) * 8, (uint32_t)((i / Cfg::NS) & 1))) {
+                    if (global_ns() - t0 > WAIT_LIMIT_NS) {
+                        atomicCAS(p.status, ST_OK, ST_DRAIN_TIMEOUT);
+                        break;
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ======================= consumer warps =======================
+    const int cg = warp >> 2;           // consumer group: takes every other tile
+    const int wr = warp & 3;            // 16-row block of the tile
+    const int quad = lane >> 2, qi = lane & 3;
+    const float sl2 = p.scale * LOG2E;  // scores are kept in log2 units
+
+    float* s_acc = reinterpret_cast<float*>(smem + Cfg::OFF_SCRATCH);
+    float2* s_ml = reinterpret_cast<float2*>(smem + Cfg::OFF_ML);
+    float* s_scale = reinterpret_cast<float*>(smem + Cfg::OFF_SCALE);
+    float2* s_glob = reinterpret_cast<float2*>(smem + Cfg::OFF_GLOB);
+
+    constexpr int KSTEPS = D / 16;
+    constexpr int NB = D / 8;
+    uint32_t qa[KSTEPS][GP == 16 ? 4 : 2];
+    float acc[NB][4];
+    float m_run[2], l_run[2];
+    long long seg_first = w.g;
+
+    // per-lane ldmatrix row geometry (constant over the kernel)
+    const int lrow = lane & 7, lmat = lane >> 3;
+    // K (non-transposed): matrices (rows 0-7, chunk c), (rows 0-7, c+1), (rows 8-15, c), (rows 8-15, c+1)
+    const int k_row = wr * 16 + (lmat >> 1) * 8 + lrow;
+    const int k_csel = lmat & 1;
+    // V (transposed): matrices (rows 0-7, chunk c), (rows 8-15, c), (rows 0-7, c+1), (rows 8-15, c+1)
+    const int v_row = wr * 16 + (lmat & 1) * 8 + lrow;
+    const int v_csel = lmat >> 1;
+
+    for (long long i = 0; w.g < w.end; ++i) {
+        if (i == 0 || w.ti == 0) {
+            // ---- segment begins: fetch the group's query rows as MMA A fragments
+            seg_first = w.g;
+            const int kv = w.ub / upb_nch, ch = w.ub % upb_nch;
+            const int gvalid = min(p.GC, p.G - ch * p.GC);
+            const T* qb = reinterpret_cast<const T*>(p.q) + ((size_t)w.b * p.Hq + kv * p.G + ch * p.GC) * D;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+                const int d0 = kk * 16 + qi * 2;
+                const bool lo_ok = quad < gvalid;
+                qa[kk][0] = lo_ok ? *reinterpret_cast<const uint32_t*>(qb + (size_t)quad * D + d0) : 0u;
+                qa[kk][GP == 16 ? 2 : 1] = lo_ok ? *reinterpret_cast<const uint32_t*>(qb + (size_t)quad * D + d0 + 8) : 0u;
+                if constexpr (GP == 16) {
+                    const bool hi_ok = quad + 8 < gvalid;
+                    qa[kk][1] = hi_ok ? *reinterpret_cast<const uint32_t*>(qb + (size_t)(quad + 8) * D + d0) : 0u;
+                    qa[kk][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(qb + (size_t)(quad + 8) * D + d0 + 8) : 0u;
+                }
+            }
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.0f;
+            m_run[0] = m_run[1] = -INFINITY;
+            l_run[0] = l_run[1] = 0.0f;
+        }
+
+        if ((int)(i & 1) == cg) {
+            const int s = (int)(i % Cfg::NS);
+            const uint32_t ph = (uint32_t)((i / Cfg::NS) & 1);
+            const bool ok = mbar_wait(bar_full + s * 8, ph, abort_flag, p.status, ST_WAIT_FULL_TIMEOUT);
+            const int rows_valid = w.len - w.ti * TILE;      // >= 1
+            if (ok && wr * 16 < rows_valid) {
+                const uint32_t st_k = smem_base + s * Cfg::STAGE_BYTES;
+                const uint32_t st_v = st_k + Cfg::KV_BYTES;
+                const bool ragged = rows_valid < wr * 16 + 16;
+                if (ragged) {
+                    // rows at and past the sequence end may hold anything
+                    // (stale or foreign data): clear the V rows so that a zero
+                    // weight times their contents stays zero
+                    uint8_t* vb = smem + s * Cfg::STAGE_BYTES + Cfg::KV_BYTES;
+                    for (int r = wr * 16 + (rows_valid - wr * 16); r < wr * 16 + 16; ++r)
+                        for (int h = 0; h < Cfg::NH; ++h)
+                            if (lane < 8)
+                                *reinterpret_cast<uint4*>(vb + h * (TILE * 128) + r * 128 + lane * 16) = make_uint4(0, 0, 0, 0);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                }
+                // ---- S = Q K^T for 16 cache rows (two n-blocks of 8)
+                float sa[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                float sb[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    const int chunk = kk * 2 + k_csel;
+                    const uint32_t addr = st_k + (chunk >> 3) * (TILE * 128) + k_row * 128 +
+                                          (((chunk & 7) ^ lrow) << 4);
+                    uint32_t r0, r1, r2, r3;
+                    ldsm_x4(addr, r0, r1, r2, r3);
+                    const uint32_t a0 = qa[kk][0];
+                    const uint32_t a1 = (GP == 16) ? qa[kk][1] : 0u;
+                    const uint32_t a2 = qa[kk][GP == 16 ? 2 : 1];
+                    const uint32_t a3 = (GP == 16) ? qa[kk][GP == 16 ? 3 : 1] : 0u;
+                    if (kk & 1) {
+                        mma16816<T>(sb[0], a0, a1, a2, a3, r0, r1);
+                        mma16816<T>(sb[1], a0, a1, a2, a3, r2, r3);
+                    } else {
+                        mma16816<T>(sa[0], a0, a1, a2, a3, r0, r1);
+                        mma16816<T>(sa[1], a0, a1, a2, a3, r2, r3);
+                    }
+                }
+                // ---- online softmax (log2 domain), rows `quad` and `quad + 8`
+                float sc[2][4];
+#pragma unroll
+                for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sc[nb][e] = (sa[nb][e] + sb[nb][e]) * sl2;
+                if (ragged) {
+#pragma unroll
+                    for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int r = wr * 16 + nb * 8 + qi * 2 + (e & 1);
+                            if (r >= rows_valid) sc[nb][e] = -INFINITY;
+                        }
+                }
+                uint32_t pa[4];
+#pragma unroll
+                for (int hh = 0; hh < (GP == 16 ? 2 : 1); ++hh) {
+                    float mx = fmaxf(fmaxf(sc[0][2 * hh], sc[0][2 * hh + 1]), fmaxf(sc[1][2 * hh], sc[1][2 * hh + 1]));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    const float m_new = fmaxf(m_run[hh], mx);
+                    const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+                    const float alpha = ex2(m_run[hh] - m_safe);
+                    const float p00 = ex2(sc[0][2 * hh] - m_safe), p01 = ex2(sc[0][2 * hh + 1] - m_safe);
+                    const float p10 = ex2(sc[1][2 * hh] - m_safe), p11 = ex2(sc[1][2 * hh + 1] - m_safe);
+                    l_run[hh] = l_run[hh] * alpha + ((p00 + p01) + (p10 + p11));
+                    m_run[hh] = m_new;
+                    pa[hh] = pack2<T>(p00, p01);          // A regs: rows quad (+8), k 0-7
+                    pa[hh + 2] = pack2<T>(p10, p11);      //                         k 8-15
+                    if (alpha != 1.0f) {
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) {
+                            acc[nb][2 * hh] *= alpha;
+                            acc[nb][2 * hh + 1] *= alpha;
+                        }
+                    }
+                }
+                if constexpr (GP == 8) { pa[1] = 0u; pa[3] = 0u; }
+                // ---- O += P V
+#pragma unroll
+                for (int c = 0; c < NB; c += 2) {
+                    const int chunk = c + v_csel;
+                    const uint32_t addr = st_v + (chunk >> 3) * (TILE * 128) + v_row * 128 +
+                                          (((chunk & 7) ^ lrow) << 4);
+                    uint32_t r0, r1, r2, r3;
+                    ldsm_x4_t(addr, r0, r1, r2, r3);
+                    mma16816<T>(acc[c], pa[0], pa[1], pa[2], pa[3], r0, r1);
+                    mma16816<T>(acc[c + 1], pa[0], pa[1], pa[2], pa[3], r2, r3);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + s * 8);
+        }
+
+        const bool seg_end = (w.ti == w.nt - 1) || (w.g + 1 == w.end);
+        if (seg_end) {
+            // ---- fold the 8 warp states and emit
+            const SegDest dst = seg_dest(p, w, total, seg_first);
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
+                l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
+            }
+#pragma unroll
+            for (int hh = 0; hh < (GP == 16 ? 2 : 1); ++hh) {
+                bar_consumers();                                   // scratch is free again
+                float* my = s_acc + ((size_t)warp * 8 + quad) * Cfg::ACC_STRIDE + qi * 2;
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+                    *reinterpret_cast<float2*>(my + nb * 8) = make_float2(acc[nb][2 * hh], acc[nb][2 * hh + 1]);
+                if (qi == 0) s_ml[warp * 8 + quad] = make_float2(m_run[hh], l_run[hh]);
+                bar_consumers();
+                const int tc = warp * 32 + lane;
+                if (tc < NCW * 8) {
+                    const int row = tc & 7;
+                    float mg = -INFINITY;
+#pragma unroll
+                    for (int ww = 0; ww < NCW; ++ww) mg = fmaxf(mg, s_ml[ww * 8 + row].x);
+                    const float mg_safe = (mg == -INFINITY) ? 0.0f : mg;
+                    s_scale[tc] = ex2(s_ml[tc].x - mg_safe);       // tc = (warp index) * 8 + row
+                    if (tc < 8) {
+                        float lg = 0.0f;
+#pragma unroll
+                        for (int ww = 0; ww < NCW; ++ww)
+                            lg += s_ml[ww * 8 + row].y * ex2(s_ml[ww * 8 + row].x - mg_safe);
+                        s_glob[row] = make_float2(mg * LN2, lg);   // m back in natural-log units
+                    }
+                }
+                bar_consumers();
+                for (int e = tc; e < 8 * (D / 2); e += NCW * 32) {
+                    const int row = e / (D / 2), d = (e % (D / 2)) * 2;
+                    const int g = hh * 8 + row;
+                    if (g >= dst.gvalid) continue;
+                    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+                    for (int ww = 0; ww < NCW; ++ww) {
+                        const float sc = s_scale[ww * 8 + row];
+                        const float2 v = *reinterpret_cast<const float2*>(
+                            s_acc + ((size_t)ww * 8 + row) * Cfg::ACC_STRIDE + d);
+                        a0 += v.x * sc;
+                        a1 += v.y * sc;
+                    }
+                    const float2 ml = s_glob[row];
+                    if (dst.whole) {
+                        emit_final2<T>(p, dst.b, dst.h0 + g, d, ml.x, ml.y, a0, a1, d == 0);
+                    } else {
+                        const size_t pr = dst.slot * p.GC + g;
+                        *reinterpret_cast<float2*>(p.ws_acc + pr * D + d) = make_float2(a0, a1);
+                        if (d == 0) *reinterpret_cast<float2*>(p.ws_ml + pr * 2) = ml;
+                    }
+                }
+            }
+        }
+        walker_advance(p, w);
+    }
+    (void)g_begin;
+}
+
+}  // namespace ftk

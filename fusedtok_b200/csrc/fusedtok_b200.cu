@@ -1,0 +1,557 @@
+// Host side of the C ABI declared in include/fusedtok_b200.h: argument
+// validation with the reference's error contract, per-device workspace,
+// TMA descriptor encoding, kernel selection and launch. Counterpart of the
+// reference's launchers (src/attention.cu:1468-1585, 1791-1915), its staged
+// bindings (src/bindings.cpp:2402-2436, 2507-2565) and cuda_available
+// (src/fusedtok.cu:34-37).
+
+#include "../../include/fusedtok_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "decode_simt.cuh"
+#include "decode_tc.cuh"
+#include "merge.cuh"
+
+namespace {
+
+using namespace ftk;
+
+thread_local std::string g_err;
+thread_local long long g_launches = 0;
+
+int fail(int code, const std::string& msg) {
+    g_err = msg;
+    return code;
+}
+int cuda_fail(const char* what, cudaError_t e) {
+    return fail(FUSEDTOK_RUNTIME_ERROR, std::string(what) + ": " + cudaGetErrorString(e));
+}
+// launch failures surface as runtime errors (reference: check_launch, src/cuda_util.cuh:21-25)
+int check_launch(const char* what) {
+    ++g_launches;
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(what, e);
+    return FUSEDTOK_OK;
+}
+// reference: stream_is_capturing, src/cuda_util.cuh:259-264
+bool stream_is_capturing(cudaStream_t s) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &st) != cudaSuccess) cudaGetLastError();
+    return st == cudaStreamCaptureStatusActive;
+}
+
+enum DType { F32 = 0, BF16 = 1, F16 = 2 };
+inline size_t dtype_size(int dt) { return dt == F32 ? 4 : 2; }
+
+// ---- per-device state --------------------------------------------------------
+constexpr int kMaxDevices = 64;
+constexpr size_t kArenaMin = 32u << 20;      // first allocation: covers common shapes
+
+struct DeviceState {
+    bool init = false;
+    int sm_count = 0;
+    char* arena = nullptr;                   // current arena (older ones stay alive: graphs may hold them)
+    size_t arena_bytes = 0;
+    int* status = nullptr;                   // separate small allocation, never moves
+    bool smem_attr_set = false;
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mutex;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int get_encode_fn() {
+    if (g_encode) return FUSEDTOK_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || !fn || qres != cudaDriverEntryPointSuccess)
+        return fail(FUSEDTOK_RUNTIME_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return FUSEDTOK_OK;
+}
+
+template <typename K> int set_smem(K kernel, int bytes) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
+    return FUSEDTOK_OK;
+}
+
+int set_all_smem_attrs() {
+    int rc = 0;
+#define FTK_SET(T, D, GP, PG) \
+    if ((rc = set_smem(decode_tc_kernel<T, D, GP, PG>, TcCfg<D>::SMEM_BYTES))) return rc;
+#define FTK_SET_ALL(T)                                                                          \
+    FTK_SET(T, 64, 8, false) FTK_SET(T, 64, 16, false) FTK_SET(T, 64, 8, true) FTK_SET(T, 64, 16, true) \
+    FTK_SET(T, 128, 8, false) FTK_SET(T, 128, 16, false) FTK_SET(T, 128, 8, true) FTK_SET(T, 128, 16, true)
+    FTK_SET_ALL(__nv_bfloat16)
+    FTK_SET_ALL(__half)
+#undef FTK_SET_ALL
+#undef FTK_SET
+    return rc;
+}
+
+int device_state(DeviceState** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail("cudaGetDevice", e);
+    if (dev < 0 || dev >= kMaxDevices) return fail(FUSEDTOK_RUNTIME_ERROR, "device index out of range");
+    DeviceState& d = g_dev[dev];
+    if (!d.init) {
+        e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return cuda_fail("cudaDeviceGetAttribute", e);
+        d.init = true;
+    }
+    *out = &d;
+    return FUSEDTOK_OK;
+}
+
+struct Arena {
+    int* status;
+    long long* total;
+    int2* meta;
+    float* ws_ml;
+    float* ws_acc;
+};
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Workspace for `units` units split over `ncta` CTAs. Grow-only; allocation is
+// refused while the stream is being captured.
+int get_arena(DeviceState& d, cudaStream_t cs, size_t units, int ncta, int gc, int dim, bool need_smem_attr,
+              Arena* a) {
+    const size_t slots = units + (size_t)ncta;
+    const size_t meta_b = align_up(units * sizeof(int2), 256);
+    const size_t ml_b = align_up(slots * gc * 2 * sizeof(float), 256);
+    const size_t acc_b = align_up(slots * gc * (size_t)dim * sizeof(float), 256);
+    const size_t need = meta_b + ml_b + acc_b;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    const bool first = d.status == nullptr || (need_smem_attr && !d.smem_attr_set);
+    if (first || need > d.arena_bytes) {
+        if (stream_is_capturing(cs))
+            return fail(FUSEDTOK_RUNTIME_ERROR,
+                        "decode attention workspace must be allocated outside a CUDA graph capture - "
+                        "warm the shape up once before capturing");
+        if (!d.status) {
+            cudaError_t e = cudaMalloc(&d.status, 256);
+            if (e != cudaSuccess) return cuda_fail("status word allocation failed", e);
+            e = cudaMemset(d.status, 0, 256);
+            if (e != cudaSuccess) return cuda_fail("status word clear failed", e);
+        }
+        if (need_smem_attr && !d.smem_attr_set) {
+            const int rc = set_all_smem_attrs();
+            if (rc) return rc;
+            d.smem_attr_set = true;
+        }
+        if (need > d.arena_bytes) {
+            const size_t bytes = std::max(need, kArenaMin);
+            char* mem = nullptr;
+            const cudaError_t e = cudaMalloc(&mem, bytes);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                return fail(FUSEDTOK_RUNTIME_ERROR, "decode attention workspace allocation failed");
+            }
+            d.arena = mem;          // the previous arena is deliberately kept: captured graphs may point into it
+            d.arena_bytes = bytes;
+        }
+    }
+    a->status = d.status;
+    a->total = reinterpret_cast<long long*>(d.status) + 1;
+    a->meta = reinterpret_cast<int2*>(d.arena);
+    a->ws_ml = reinterpret_cast<float*>(d.arena + meta_b);
+    a->ws_acc = reinterpret_cast<float*>(d.arena + meta_b + ml_b);
+    return FUSEDTOK_OK;
+}
+
+// reference: attention_check, src/attention.cu:184-193
+int attention_check(int batch, int hq, int hkv, long long t_seq, int dim) {
+    if (batch < 0 || hq < 1 || hkv < 1 || t_seq < 0 || dim < 1)
+        return fail(FUSEDTOK_INVALID_ARGUMENT,
+                    "attention shapes must satisfy batch>=0, heads>=1, rows>=0, dim>=1");
+    if (hq % hkv != 0)
+        return fail(FUSEDTOK_INVALID_ARGUMENT,
+                    "q heads must be a multiple of kv heads (contiguous GQA groups)");
+    if (dim % 4 != 0 || dim > 512)
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "dim must be a multiple of 4 and at most 512");
+    return FUSEDTOK_OK;
+}
+
+int encode_map(CUtensorMap* map, int dt, const void* base, unsigned long long rows, int dim, int box_rows) {
+    const cuuint64_t gdim[2] = {(cuuint64_t)dim, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)dim * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = g_encode(map, dt == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                2, const_cast<void*>(base), gdim, gstride, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(FUSEDTOK_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed (code " + std::to_string((int)r) + ")");
+    return FUSEDTOK_OK;
+}
+
+template <typename T, int D, int GP, bool PG>
+void launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, cudaStream_t cs) {
+    decode_tc_kernel<T, D, GP, PG><<<p.ncta, TC_THREADS, TcCfg<D>::SMEM_BYTES, cs>>>(mk, mv, p);
+}
+template <typename T>
+void launch_tc_t(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, int gp, bool paged,
+                 cudaStream_t cs) {
+#define FTK_GO(D, GP)                                              \
+    do {                                                           \
+        if (paged) launch_tc<T, D, GP, true>(mk, mv, p, cs);       \
+        else launch_tc<T, D, GP, false>(mk, mv, p, cs);            \
+    } while (0)
+    if (p.D == 64) { if (gp == 8) FTK_GO(64, 8); else FTK_GO(64, 16); }
+    else           { if (gp == 8) FTK_GO(128, 8); else FTK_GO(128, 16); }
+#undef FTK_GO
+}
+
+template <typename T> void launch_simt_t(const DecodeParams& p, int lc, cudaStream_t cs) {
+#define FTK_GO(GC, LC) decode_simt_kernel<T, GC, LC><<<p.ncta, SIMT_THREADS, 0, cs>>>(p)
+    if (lc == 1) { if (p.GC == 1) FTK_GO(1, 1); else if (p.GC == 4) FTK_GO(4, 1); else FTK_GO(8, 1); }
+    else if (lc == 2) { if (p.GC == 1) FTK_GO(1, 2); else FTK_GO(4, 2); }
+    else { if (p.GC == 1) FTK_GO(1, 4); else FTK_GO(2, 4); }
+#undef FTK_GO
+}
+
+template <typename T> void launch_merge_t(const DecodeParams& p, cudaStream_t cs) {
+    const long long rows = (long long)p.B * p.Hq;
+    const unsigned grid = (unsigned)((rows + MERGE_WARPS - 1) / MERGE_WARPS);
+    merge_kernel<T><<<grid, MERGE_WARPS * 32, 0, cs>>>(p);
+}
+
+inline bool is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
+
+// The one launcher behind every zero-copy entry point.
+// table == nullptr: contiguous cache with `rows` cache rows per (b, kv).
+// table != nullptr: paged pools, page rows per block, tbl_width entries per sequence.
+// partial != nullptr: emit raw triples instead of the normalised output.
+int decode_common(int dt, const void* q, const void* k, const void* v, const int* table, const int* lens,
+                  void* out, float* partial, int batch, int hq, int hkv, int rows, int page, int tbl_width,
+                  int dim, uintptr_t stream) {
+    cudaStream_t cs = (cudaStream_t)stream;
+    if (batch == 0) return FUSEDTOK_OK;                       // nothing to compute (src/attention.cu:1474)
+    const long long out_rows = (long long)batch * hq;
+    const int G = hq / hkv;
+    float* tr_ml = partial;
+    float* tr_acc = partial ? partial + triple_acc_offset(out_rows) : nullptr;
+
+    if (rows == 0) {
+        // empty cache: zero rows (src/attention.cu:211-216) or empty triples
+        if (partial) {
+            const long long n = out_rows * dim;
+            fill_empty_triple_kernel<<<(unsigned)((n + 255) / 256), 256, 0, cs>>>(tr_ml, tr_acc, out_rows, dim);
+            return check_launch("attention empty-triple kernel launch");
+        }
+        const cudaError_t e = cudaMemsetAsync(out, 0, (size_t)out_rows * dim * dtype_size(dt), cs);
+        if (e != cudaSuccess) return cuda_fail("attention zero fill failed", e);
+        return FUSEDTOK_OK;
+    }
+
+    DeviceState* dev = nullptr;
+    int rc = device_state(&dev);
+    if (rc) return rc;
+
+    // ---- kernel family and head chunking
+    const bool paged = table != nullptr;
+    const unsigned long long map_rows =
+        paged ? 0ull : (unsigned long long)batch * hkv * (unsigned long long)rows;
+    bool use_tc = dt != F32 && (dim == 64 || dim == 128) &&
+                  ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
+                  ((reinterpret_cast<uintptr_t>(q)) & 3u) == 0;
+    if (use_tc && !paged && map_rows >= (1ull << 31)) use_tc = false;
+    if (use_tc && paged && !(is_pow2(page) && page >= 8)) use_tc = false;
+
+    DecodeParams p;
+    memset(&p, 0, sizeof(p));
+    p.q = q; p.k = k; p.v = v; p.out = out; p.lens = lens; p.table = table;
+    p.triple_ml = tr_ml; p.triple_acc = tr_acc;
+    p.B = batch; p.Hq = hq; p.Hkv = hkv; p.G = G; p.T = rows; p.D = dim;
+    p.page = page; p.tbl_width = tbl_width;
+    p.scale = 1.0f / sqrtf((float)dim);
+    int lc = 1, gp = 8;
+    if (use_tc) {
+        p.GC = std::min(G, 16);
+        gp = p.GC <= 8 ? 8 : 16;
+    } else {
+        lc = dim <= 128 ? 1 : (dim <= 256 ? 2 : 4);
+        if (G == 1) p.GC = 1;
+        else if (lc == 1) p.GC = G <= 4 ? 4 : 8;
+        else if (lc == 2) p.GC = 4;
+        else p.GC = 2;
+    }
+    p.NCH = (G + p.GC - 1) / p.GC;
+
+    const unsigned long long units = (unsigned long long)batch * hkv * p.NCH;
+    const unsigned long long max_tiles = units * (unsigned long long)((rows + TILE - 1) / TILE);
+    const int per_sm = use_tc ? 1 : 2;
+    p.ncta = (int)std::min<unsigned long long>((unsigned long long)dev->sm_count * per_sm, max_tiles);
+    if (p.ncta < 1) p.ncta = 1;
+
+    Arena a;
+    rc = get_arena(*dev, cs, (size_t)units, p.ncta, p.GC, dim, use_tc, &a);
+    if (rc) return rc;
+    p.ws_ml = a.ws_ml; p.ws_acc = a.ws_acc; p.meta = a.meta; p.status = a.status; p.total_out = a.total;
+
+    if (use_tc) {
+        rc = get_encode_fn();
+        if (rc) return rc;
+        CUtensorMap mk, mv;
+        unsigned long long trows;
+        int box_rows;
+        if (paged) {
+            // pool rows are not known here (table values are trusted): describe the largest range
+            // the int32 TMA coordinate can address; the hardware zero-fills nothing it is not asked for
+            trows = (1ull << 31) - 1;
+            box_rows = std::min(page, TILE);
+        } else {
+            trows = map_rows;
+            box_rows = TILE;
+        }
+        if ((rc = encode_map(&mk, dt, k, trows, dim, box_rows))) return rc;
+        if ((rc = encode_map(&mv, dt, v, trows, dim, box_rows))) return rc;
+        if (dt == BF16) launch_tc_t<__nv_bfloat16>(mk, mv, p, gp, paged, cs);
+        else launch_tc_t<__half>(mk, mv, p, gp, paged, cs);
+        if ((rc = check_launch("attention split-KV tensor-core kernel launch"))) return rc;
+    } else {
+        if (dt == F32) launch_simt_t<float>(p, lc, cs);
+        else if (dt == BF16) launch_simt_t<__nv_bfloat16>(p, lc, cs);
+        else launch_simt_t<__half>(p, lc, cs);
+        if ((rc = check_launch("attention split-KV kernel launch"))) return rc;
+    }
+    if (dt == F32) launch_merge_t<float>(p, cs);
+    else if (dt == BF16) launch_merge_t<__nv_bfloat16>(p, cs);
+    else launch_merge_t<__half>(p, cs);
+    return check_launch("attention merge kernel launch");
+}
+
+int decode_contig(int dt, const void* q, const void* k, const void* v, const int* lens, void* out,
+                  float* partial, int batch, int hq, int hkv, int t_seq, int dim, uintptr_t stream) {
+    const int rc = attention_check(batch, hq, hkv, t_seq, dim);
+    if (rc) return rc;
+    return decode_common(dt, q, k, v, nullptr, lens, out, partial, batch, hq, hkv, t_seq, 0, 0, dim, stream);
+}
+
+// reference: attention_decode_paged_launch_t, src/attention.cu:1791-1815
+int decode_paged(int dt, const void* q, const void* kp, const void* vp, const int* table, const int* lens,
+                 void* out, int batch, int hq, int hkv, int page, int tbl_width, int dim, uintptr_t stream) {
+    const long long span = (long long)tbl_width * page;
+    if (span > (1LL << 30)) return fail(FUSEDTOK_INVALID_ARGUMENT, "table capacity too large");
+    const int rc = attention_check(batch, hq, hkv, span, dim);
+    if (rc) return rc;
+    if (page < 1) return fail(FUSEDTOK_INVALID_ARGUMENT, "page size must be >= 1");
+    if (tbl_width < 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "table width must be >= 0");
+    return decode_common(dt, q, kp, vp, table, lens, out, nullptr, batch, hq, hkv, (int)span, page, tbl_width,
+                         dim, stream);
+}
+
+// RAII device buffer for the staged paths (reference: DevBuf, src/bindings.cpp:47-66)
+struct DevBuf {
+    void* p = nullptr;
+    cudaError_t err = cudaSuccess;
+    explicit DevBuf(size_t bytes) {
+        if (bytes) err = cudaMalloc(&p, bytes);
+    }
+    ~DevBuf() {
+        if (p) cudaFree(p);
+    }
+    DevBuf(const DevBuf&) = delete;
+    DevBuf& operator=(const DevBuf&) = delete;
+};
+
+}  // namespace
+
+extern "C" {
+
+const char* fusedtok_last_error(void) { return g_err.c_str(); }
+
+int fusedtok_cuda_available(void) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return count > 0;
+}
+
+int fusedtok_attention_decode_launch(const float* q, const float* k, const float* v, const int* lens,
+                                     float* out, int batch, int q_heads, int kv_heads, int cache_rows,
+                                     int dim, uintptr_t stream) {
+    return decode_contig(F32, q, k, v, lens, out, nullptr, batch, q_heads, kv_heads, cache_rows, dim, stream);
+}
+int fusedtok_attention_decode_launch_bf16(const void* q, const void* k, const void* v, const int* lens,
+                                          void* out, int batch, int q_heads, int kv_heads, int cache_rows,
+                                          int dim, uintptr_t stream) {
+    return decode_contig(BF16, q, k, v, lens, out, nullptr, batch, q_heads, kv_heads, cache_rows, dim, stream);
+}
+int fusedtok_attention_decode_launch_fp16(const void* q, const void* k, const void* v, const int* lens,
+                                          void* out, int batch, int q_heads, int kv_heads, int cache_rows,
+                                          int dim, uintptr_t stream) {
+    return decode_contig(F16, q, k, v, lens, out, nullptr, batch, q_heads, kv_heads, cache_rows, dim, stream);
+}
+
+int fusedtok_attention_decode_paged_launch(const float* q, const float* k_pool, const float* v_pool,
+                                           const int* table, const int* lens, float* out, int batch,
+                                           int q_heads, int kv_heads, int page, int tbl_width, int dim,
+                                           uintptr_t stream) {
+    return decode_paged(F32, q, k_pool, v_pool, table, lens, out, batch, q_heads, kv_heads, page, tbl_width, dim,
+                        stream);
+}
+int fusedtok_attention_decode_paged_launch_bf16(const void* q, const void* k_pool, const void* v_pool,
+                                                const int* table, const int* lens, void* out, int batch,
+                                                int q_heads, int kv_heads, int page, int tbl_width, int dim,
+                                                uintptr_t stream) {
+    return decode_paged(BF16, q, k_pool, v_pool, table, lens, out, batch, q_heads, kv_heads, page, tbl_width,
+                        dim, stream);
+}
+int fusedtok_attention_decode_paged_launch_fp16(const void* q, const void* k_pool, const void* v_pool,
+                                                const int* table, const int* lens, void* out, int batch,
+                                                int q_heads, int kv_heads, int page, int tbl_width, int dim,
+                                                uintptr_t stream) {
+    return decode_paged(F16, q, k_pool, v_pool, table, lens, out, batch, q_heads, kv_heads, page, tbl_width,
+                        dim, stream);
+}
+
+int fusedtok_attention_decode(const float* q, const float* k, const float* v, const int* lens, float* out,
+                              int batch, int q_heads, int kv_heads, int cache_rows, int dim) {
+    int rc = attention_check(batch, q_heads, kv_heads, cache_rows, dim);
+    if (rc) return rc;
+    if (lens)
+        for (int i = 0; i < batch; ++i)
+            if (lens[i] < 0 || lens[i] > cache_rows)
+                return fail(FUSEDTOK_INVALID_ARGUMENT, "lens entries must be within [0, cache rows]");
+    const size_t q_b = (size_t)batch * q_heads * dim * 4;
+    const size_t kv_b = (size_t)batch * kv_heads * cache_rows * dim * 4;
+    if (q_b == 0) return FUSEDTOK_OK;
+    DevBuf dq(q_b), dk(kv_b), dv(kv_b), dl(lens ? (size_t)batch * 4 : 0), dy(q_b);
+    for (const DevBuf* b : {&dq, &dk, &dv, &dl, &dy})
+        if (b->err != cudaSuccess) return cuda_fail("cudaMalloc failed", b->err);
+    cudaError_t e;
+    if ((e = cudaMemcpy(dq.p, q, q_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if (kv_b) {
+        if ((e = cudaMemcpy(dk.p, k, kv_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+        if ((e = cudaMemcpy(dv.p, v, kv_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    }
+    if (lens && (e = cudaMemcpy(dl.p, lens, (size_t)batch * 4, cudaMemcpyHostToDevice)) != cudaSuccess)
+        return cuda_fail("H2D copy failed", e);
+    rc = fusedtok_attention_decode_launch((const float*)dq.p, (const float*)dk.p, (const float*)dv.p,
+                                          lens ? (const int*)dl.p : nullptr, (float*)dy.p, batch, q_heads,
+                                          kv_heads, cache_rows, dim, 0);
+    if (rc) return rc;
+    if ((e = cudaMemcpy(out, dy.p, q_b, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("D2H copy failed", e);
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return cuda_fail("attention decode kernel failed", e);
+    return FUSEDTOK_OK;
+}
+
+int fusedtok_attention_decode_paged(const float* q, const float* k_pool, const float* v_pool, const int* table,
+                                    const int* lens, float* out, int batch, int q_heads, int kv_heads,
+                                    int page, int tbl_width, int num_blocks, int dim) {
+    const long long span = (long long)tbl_width * page;
+    if (span > (1LL << 30)) return fail(FUSEDTOK_INVALID_ARGUMENT, "table capacity too large");
+    int rc = attention_check(batch, q_heads, kv_heads, span, dim);
+    if (rc) return rc;
+    if (page < 1) return fail(FUSEDTOK_INVALID_ARGUMENT, "page size must be >= 1");
+    if (num_blocks < 0 || tbl_width < 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "attention operand size mismatch");
+    // host-side validation of table and lens values (src/bindings.cpp:2524-2539)
+    const size_t tbl_n = (size_t)batch * tbl_width;
+    for (size_t i = 0; i < tbl_n; ++i)
+        if (table[i] < 0 || table[i] >= num_blocks)
+            return fail(FUSEDTOK_INVALID_ARGUMENT, "block table entries must be valid pool block ids");
+    if (lens)
+        for (int i = 0; i < batch; ++i)
+            if (lens[i] < 0 || lens[i] > span)
+                return fail(FUSEDTOK_INVALID_ARGUMENT, "lens entries must be within [0, table width * page]");
+    const size_t q_b = (size_t)batch * q_heads * dim * 4;
+    const size_t kv_b = (size_t)num_blocks * kv_heads * page * dim * 4;
+    if (q_b == 0) return FUSEDTOK_OK;
+    DevBuf dq(q_b), dk(kv_b), dv(kv_b), dt(tbl_n * 4), dl(lens ? (size_t)batch * 4 : 0), dy(q_b);
+    for (const DevBuf* b : {&dq, &dk, &dv, &dt, &dl, &dy})
+        if (b->err != cudaSuccess) return cuda_fail("cudaMalloc failed", b->err);
+    cudaError_t e;
+    if ((e = cudaMemcpy(dq.p, q, q_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if (kv_b) {
+        if ((e = cudaMemcpy(dk.p, k_pool, kv_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+        if ((e = cudaMemcpy(dv.p, v_pool, kv_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    }
+    if (tbl_n && (e = cudaMemcpy(dt.p, table, tbl_n * 4, cudaMemcpyHostToDevice)) != cudaSuccess)
+        return cuda_fail("H2D copy failed", e);
+    if (lens && (e = cudaMemcpy(dl.p, lens, (size_t)batch * 4, cudaMemcpyHostToDevice)) != cudaSuccess)
+        return cuda_fail("H2D copy failed", e);
+    rc = fusedtok_attention_decode_paged_launch((const float*)dq.p, (const float*)dk.p, (const float*)dv.p,
+                                                (const int*)dt.p, lens ? (const int*)dl.p : nullptr,
+                                                (float*)dy.p, batch, q_heads, kv_heads, page, tbl_width, dim, 0);
+    if (rc) return rc;
+    if ((e = cudaMemcpy(out, dy.p, q_b, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("D2H copy failed", e);
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return cuda_fail("attention decode paged kernel failed", e);
+    return FUSEDTOK_OK;
+}
+
+int fusedtok_attention_decode_partial_launch(int dtype, const void* q, const void* k, const void* v,
+                                             const int* lens, float* partial, int batch, int q_heads,
+                                             int kv_heads, int cache_rows, int dim, uintptr_t stream) {
+    if (dtype < 0 || dtype > 2) return fail(FUSEDTOK_INVALID_ARGUMENT, "dtype must be 0 (f32), 1 (bf16) or 2 (fp16)");
+    if (!partial) return fail(FUSEDTOK_INVALID_ARGUMENT, "partial buffer must not be null");
+    return decode_contig(dtype, q, k, v, lens, nullptr, partial, batch, q_heads, kv_heads, cache_rows, dim, stream);
+}
+
+long long fusedtok_attention_partial_floats(int batch, int q_heads, int dim) {
+    const long long rows = (long long)batch * q_heads;
+    return (long long)ftk::triple_acc_offset(rows) + rows * dim;
+}
+
+int fusedtok_attention_merge_partials_launch(int dtype, const float* partials, int n_parts, void* out, int batch,
+                                             int q_heads, int dim, uintptr_t stream) {
+    if (dtype < 0 || dtype > 2) return fail(FUSEDTOK_INVALID_ARGUMENT, "dtype must be 0 (f32), 1 (bf16) or 2 (fp16)");
+    if (batch < 0 || q_heads < 1 || n_parts < 1 || dim < 1 || dim % 4 != 0 || dim > 512)
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "merge shapes must satisfy batch>=0, heads>=1, parts>=1, dim%4==0, dim<=512");
+    const long long rows = (long long)batch * q_heads;
+    if (rows == 0) return FUSEDTOK_OK;
+    cudaStream_t cs = (cudaStream_t)stream;
+    const unsigned grid = (unsigned)((rows + ftk::MERGE_WARPS - 1) / ftk::MERGE_WARPS);
+    if (dtype == F32)
+        ftk::merge_parts_kernel<float><<<grid, ftk::MERGE_WARPS * 32, 0, cs>>>(partials, n_parts, (float*)out, rows, dim);
+    else if (dtype == BF16)
+        ftk::merge_parts_kernel<__nv_bfloat16><<<grid, ftk::MERGE_WARPS * 32, 0, cs>>>(partials, n_parts, (__nv_bfloat16*)out, rows, dim);
+    else
+        ftk::merge_parts_kernel<__half><<<grid, ftk::MERGE_WARPS * 32, 0, cs>>>(partials, n_parts, (__half*)out, rows, dim);
+    return check_launch("attention partial-merge kernel launch");
+}
+
+int fusedtok_attention_device_status(int* status) {
+    if (!status) return fail(FUSEDTOK_INVALID_ARGUMENT, "status pointer must not be null");
+    *status = 0;
+    DeviceState* dev = nullptr;
+    const int rc = device_state(&dev);
+    if (rc) return rc;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail("device synchronize failed", e);
+    if (!dev->status) return FUSEDTOK_OK;
+    if ((e = cudaMemcpy(status, dev->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+        return cuda_fail("status read failed", e);
+    if (*status != 0 && (e = cudaMemset(dev->status, 0, sizeof(int))) != cudaSuccess)
+        return cuda_fail("status clear failed", e);
+    return FUSEDTOK_OK;
+}
+
+long long fusedtok_attention_launch_count(int reset) {
+    const long long n = g_launches;
+    if (reset) g_launches = 0;
+    return n;
+}
+
+}  // extern "C"

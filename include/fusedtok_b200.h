@@ -1,0 +1,137 @@
+/*
+ * fusedtok_b200 - C ABI of the B200 (sm_100a) decode-attention library.
+ *
+ * Drop-in boundary for fusedtok's decode-attention launchers: every entry
+ * point below replaces the C++ launcher (or pybind staged binding) of the
+ * same name in the reference, with the same parameter order and meaning.
+ * Differences from the reference's C++ interface are only those a C ABI
+ * forces: functions return an int status instead of throwing
+ * (FUSEDTOK_INVALID_ARGUMENT <-> std::invalid_argument -> Python ValueError,
+ * FUSEDTOK_RUNTIME_ERROR <-> std::runtime_error -> Python RuntimeError) and
+ * the message is fetched with fusedtok_last_error().
+ *
+ * Contract of the *_launch functions (reference:
+ * include/fusedtok/cuda_launch.hpp:3-17): all pointers are caller-owned DEVICE
+ * memory on the current device; the work is asynchronous on `stream` (0 = the
+ * default stream); nothing is synchronised, read back or retained except the
+ * library-owned fp32 workspace, which is allocated (per device, grow-only,
+ * never freed) on first use. A call that would have to allocate while `stream`
+ * is being captured into a CUDA graph fails with FUSEDTOK_RUNTIME_ERROR: warm
+ * a shape up once outside the capture. Launches on different streams of one
+ * device share the workspace and must not overlap (same rule as the
+ * reference, include/fusedtok/cuda_launch.hpp:187-190).
+ *
+ * Shapes: q [B, Hq, D]; contiguous cache k, v [B, Hkv, T, D]; paged pools
+ * [Nb, Hkv, P, D] with block table [B, S] (token t of sequence b lives at
+ * pool[table[b][t / P]][kv][t % P]); lens [B] int32 or NULL (all rows valid);
+ * out [B, Hq, D] in the storage type. Query head h reads kv head
+ * h / (Hq / Hkv). Rows at and past lens[b] are never used; lens[b] == 0 or
+ * T == 0 gives an exact zero row. D % 4 == 0, D <= 512, Hq % Hkv == 0.
+ * Softmax scale 1/sqrt(D); accumulation in float32.
+ */
+#ifndef FUSEDTOK_B200_H
+#define FUSEDTOK_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FUSEDTOK_OK 0
+#define FUSEDTOK_INVALID_ARGUMENT 1
+#define FUSEDTOK_RUNTIME_ERROR 2
+
+/* Message of the last failing call on this thread ("" if none). */
+const char* fusedtok_last_error(void);
+
+/* 1 if a usable CUDA device is present. Replaces fusedtok::cuda_available,
+ * src/fusedtok.cu:34-37. */
+int fusedtok_cuda_available(void);
+
+/* ---- contiguous cache, zero-copy ------------------------------------------
+ * Replace fusedtok::attention_decode_launch / _bf16 / _fp16,
+ * include/fusedtok/cuda_launch.hpp:334-355 (src/attention.cu:1557-1585). */
+int fusedtok_attention_decode_launch(const float* q, const float* k, const float* v,
+                                     const int* lens, float* out, int batch, int q_heads,
+                                     int kv_heads, int cache_rows, int dim, uintptr_t stream);
+int fusedtok_attention_decode_launch_bf16(const void* q, const void* k, const void* v,
+                                          const int* lens, void* out, int batch, int q_heads,
+                                          int kv_heads, int cache_rows, int dim, uintptr_t stream);
+int fusedtok_attention_decode_launch_fp16(const void* q, const void* k, const void* v,
+                                          const int* lens, void* out, int batch, int q_heads,
+                                          int kv_heads, int cache_rows, int dim, uintptr_t stream);
+
+/* ---- paged cache, zero-copy -----------------------------------------------
+ * Replace fusedtok::attention_decode_paged_launch / _bf16 / _fp16,
+ * include/fusedtok/cuda_launch.hpp:381-407 (src/attention.cu:1879-1915).
+ * Table VALUES are trusted (device memory is not read back). Superset of the
+ * reference: any GQA group size is accepted (the reference launcher rejects
+ * groups other than 1/2/4/8/16, src/attention.cu:1807-1812; the Python
+ * wrapper of this package keeps that rejection). */
+int fusedtok_attention_decode_paged_launch(const float* q, const float* k_pool,
+                                           const float* v_pool, const int* table, const int* lens,
+                                           float* out, int batch, int q_heads, int kv_heads,
+                                           int page, int tbl_width, int dim, uintptr_t stream);
+int fusedtok_attention_decode_paged_launch_bf16(const void* q, const void* k_pool,
+                                                const void* v_pool, const int* table,
+                                                const int* lens, void* out, int batch, int q_heads,
+                                                int kv_heads, int page, int tbl_width, int dim,
+                                                uintptr_t stream);
+int fusedtok_attention_decode_paged_launch_fp16(const void* q, const void* k_pool,
+                                                const void* v_pool, const int* table,
+                                                const int* lens, void* out, int batch, int q_heads,
+                                                int kv_heads, int page, int tbl_width, int dim,
+                                                uintptr_t stream);
+
+/* ---- staged entry points: HOST buffers in, HOST buffer out ----------------
+ * Replace the pybind bindings `attention_decode` / `attention_decode_paged`,
+ * src/bindings.cpp:2402-2436 and :2507-2565: float32 only; device buffers are
+ * allocated, filled, the float32 launcher runs on the default stream, the
+ * result is copied back and the device is synchronised. Host lens / table
+ * values are validated (lens in [0, rows], every table entry in [0,
+ * num_blocks)). */
+int fusedtok_attention_decode(const float* q, const float* k, const float* v, const int* lens,
+                              float* out, int batch, int q_heads, int kv_heads, int cache_rows,
+                              int dim);
+int fusedtok_attention_decode_paged(const float* q, const float* k_pool, const float* v_pool,
+                                    const int* table, const int* lens, float* out, int batch,
+                                    int q_heads, int kv_heads, int page, int tbl_width,
+                                    int num_blocks, int dim);
+
+/* ---- KV-length split across GPUs (no counterpart in the reference, which is
+ * single-GPU; the exchanged triple and the merge rule are the reference's
+ * intra-GPU ones, src/attention.cu:434-463 and :503-548) --------------------
+ * *_partial_launch*: same inputs as the contiguous launchers over THIS GPU's
+ * slice of the cache rows, but instead of the normalised output it writes the
+ * raw triple of every (b, h): `partial` is float32
+ * [B*Hq*2 (m, l), padded to a multiple of 4 floats | B*Hq*D unnormalised acc],
+ * i.e. fusedtok_attention_partial_floats(batch, q_heads, dim) floats; empty
+ * rows give (-inf, 0, 0).
+ * dtype: 0 float32, 1 bfloat16, 2 float16.
+ * merge_partials_launch: folds n such blocks laid out back to back (the
+ * layout an all-gather produces) into the normalised output [B, Hq, D]. */
+int fusedtok_attention_decode_partial_launch(int dtype, const void* q, const void* k, const void* v,
+                                             const int* lens, float* partial, int batch,
+                                             int q_heads, int kv_heads, int cache_rows, int dim,
+                                             uintptr_t stream);
+long long fusedtok_attention_partial_floats(int batch, int q_heads, int dim);
+int fusedtok_attention_merge_partials_launch(int dtype, const float* partials, int n_parts,
+                                             void* out, int batch, int q_heads, int dim,
+                                             uintptr_t stream);
+
+/* ---- diagnostics -----------------------------------------------------------
+ * Every device-side wait in the kernels is bounded; a wait that expires stores
+ * a non-zero code in a per-device status word and the kernel still completes.
+ * This call synchronises the current device, returns the word through
+ * `status` (0 = ok) and clears it. */
+int fusedtok_attention_device_status(int* status);
+
+/* Number of kernels this library has launched on this thread since the last
+ * call with reset != 0 (benchmark bookkeeping). */
+long long fusedtok_attention_launch_count(int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUSEDTOK_B200_H */
