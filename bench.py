@@ -48,8 +48,8 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the split-KV
 # partial kernel on the default workload, from the ncu capture summarised in
-# profiles/ (None until captured).
-NCU_TRAFFIC_BYTES = {"c2": None}
+# profiles/decode_tc_bf16_d128_config2.md (537.18 MB read + 4.44 MB written).
+NCU_TRAFFIC_BYTES = {"c2": 541619968}
 
 WORKLOADS = {
     # name: (batch, q heads, kv heads, dim, rows, dtype, paged, description)
@@ -359,6 +359,12 @@ def run_ours(args, w, rank, world, local_rank):
     barrier()
     ms = e0.elapsed_time(e1)
     launches = _fusedtok.attention_launch_count() if not graphs else 2 * args.steps
+    if args.profile:
+        print(json.dumps({"profile_run": True, "ms_per_step": ms / args.steps, "workload": args.workload,
+                          "GBps": bytes_step / (ms / args.steps * 1e-3) / 1e9}), flush=True)
+        if rank == 0:
+            sampler.stop()
+        return
     # a few more steps keep the clock sampler busy long enough to see the load
     t_end = time.perf_counter() + 1.0
     j = 0
@@ -508,6 +514,8 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="profiler run: warm-up and timed steps only (no clock sampling, no end-to-end or CPU legs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -42,8 +42,15 @@ template <int D> struct TcCfg {
     static constexpr int NH = D / 64;                  // 128-byte column blocks per row
     static constexpr int KV_BYTES = TILE * D * 2;      // K (or V) bytes per stage
     static constexpr int STAGE_BYTES = 2 * KV_BYTES;
-    static constexpr int NS = (D == 128) ? 5 : 8;      // ring depth
-    static constexpr int ACC_STRIDE = D + 8;           // floats; keeps float2 stores 2-way at worst
+    // Ring depth. MUST be even: tiles alternate between the two consumer
+    // groups, and with an even depth a stage is always consumed by the same
+    // group, which therefore observes every phase of that stage's barrier in
+    // order. With an odd depth a group would wait on a stage it did not
+    // consume the previous time round, and a parity wait cannot tell "not
+    // filled yet" from "filled twice since".
+    static constexpr int NS = (D == 128) ? 6 : 8;
+    static_assert(NS % 2 == 0, "ring depth must be even (see above)");
+    static constexpr int ACC_STRIDE = D + 4;           // floats; rows stay 16-byte aligned
     static constexpr int SCRATCH_BYTES = NCW * 8 * ACC_STRIDE * 4;
     static constexpr int OFF_SCRATCH = NS * STAGE_BYTES;
     static constexpr int OFF_ML = OFF_SCRATCH + SCRATCH_BYTES;       // [NCW][8] float2
@@ -53,6 +60,7 @@ template <int D> struct TcCfg {
     static constexpr int OFF_SCHED = OFF_BAR + 2 * NS * 8;
     static constexpr int OFF_ABORT = OFF_SCHED + (int)sizeof(SchedShared);
     static constexpr int SMEM_BYTES = OFF_ABORT + 16;
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
 // ---- PTX wrappers ----------------------------------------------------------
