@@ -43,6 +43,7 @@ _lib.fusedtok_attention_decode_partial_launch.argtypes = [_i] + [_vp] * 5 + [_i]
 _lib.fusedtok_attention_merge_partials_launch.argtypes = [_i, _vp, _i, _vp, _i, _i, _i, _sz]
 _lib.fusedtok_attention_partial_floats.argtypes = [_i, _i, _i]
 _lib.fusedtok_attention_partial_floats.restype = ctypes.c_longlong
+_lib.fusedtok_attention_decode_launch_noalloc.argtypes = [_i] + [_vp] * 5 + [_i] * 5 + [_sz]
 _lib.fusedtok_attention_device_status.argtypes = [ctypes.POINTER(_i)]
 _lib.fusedtok_attention_launch_count.argtypes = [_i]
 _lib.fusedtok_attention_launch_count.restype = ctypes.c_longlong
@@ -57,6 +58,7 @@ EXPORTS = (
     "fusedtok_attention_decode", "fusedtok_attention_decode_paged",
     "fusedtok_attention_decode_partial_launch", "fusedtok_attention_partial_floats",
     "fusedtok_attention_merge_partials_launch",
+    "fusedtok_attention_decode_launch_noalloc",
     "fusedtok_attention_device_status", "fusedtok_attention_launch_count",
 )
 
@@ -168,6 +170,17 @@ def attention_merge_partials_launch(dtype, partials, n_parts, out, batch, hq, di
     """Fold n_parts gathered triple blocks into the normalised output."""
     _check(_lib.fusedtok_attention_merge_partials_launch(
         dtype, int(partials), n_parts, int(out), batch, hq, dim, int(stream)))
+
+
+def attention_decode_launch_noalloc(dtype, q, k, v, lens, out, batch, hq, hkv, t_seq, dim, stream=0):
+    """Contiguous-cache decode for callers that may not allocate device memory
+    after start-up (pre-budgeted serving processes, allocator-policed hosts):
+    identical results to ``attention_decode_launch*`` but the split-KV scratch
+    is a fixed 4 MiB array inside the library, so nothing is allocated. dtype:
+    0 f32, 1 bf16, 2 fp16. Larger shapes raise ValueError. Make the first call
+    on a device outside stream capture; do not overlap calls on one device."""
+    _check(_lib.fusedtok_attention_decode_launch_noalloc(
+        dtype, int(q), int(k), int(v), _opt(lens), int(out), batch, hq, hkv, t_seq, dim, int(stream)))
 
 
 def attention_device_status():

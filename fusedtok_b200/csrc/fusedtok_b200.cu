@@ -548,6 +548,150 @@ int fusedtok_attention_device_status(int* status) {
     return FUSEDTOK_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the contiguous-cache launcher.
+//
+// Some hosts may never call cudaMalloc once they are up: an inference server
+// that hands its whole memory budget to its own pool at start-up and treats any
+// later driver allocation as a bug, a process running under a memory-accounting
+// shim that forbids allocations outside a registered allocator, or code inside
+// a real-time loop where cudaMalloc's implicit device synchronisation is not
+// acceptable. For them the split-KV workspace below lives in the library image
+// itself: a fixed 4 MiB __device__ array that every GPU loading the library
+// carries until the process exits. Nothing is allocated, by this function or by
+// anything it calls.
+//
+// The array's name is only a host-side handle; its device address is looked up
+// with cudaGetSymbolAddress once per device (with that device current), on the
+// first call made on that device, together with the kernels' shared-memory
+// attribute. Make that first call outside any stream capture.
+//
+// All calls on a device share the one array and it keeps whatever the previous
+// call left there. The status / tile-total header is cleared (stream-ordered) at
+// the start of every call; everything else is written before it is read within
+// a call. Two calls that overlap on the GPU (different streams) race on it.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kNoAllocBytes = 4u << 20;          // the stated maximum: 4 MiB of scratch
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+struct NoAllocDevice {
+    bool ready = false;
+    unsigned char* base = nullptr;                  // device address of g_noalloc_scratch on this device
+};
+NoAllocDevice g_noalloc_dev[kMaxDevices];
+std::mutex g_noalloc_mutex;
+
+int noalloc_setup(unsigned char** base_out, int* sm_count) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail("cudaGetDevice", e);
+    if (dev < 0 || dev >= kMaxDevices) return fail(FUSEDTOK_RUNTIME_ERROR, "device index out of range");
+    e = cudaDeviceGetAttribute(sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail("cudaDeviceGetAttribute", e);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    NoAllocDevice& d = g_noalloc_dev[dev];
+    if (!d.ready) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || !ptr) return cuda_fail("cudaGetSymbolAddress(static scratch)", e);
+        const int rc = set_all_smem_attrs();
+        if (rc) return rc;
+        d.base = static_cast<unsigned char*>(ptr);
+        d.ready = true;
+    }
+    *base_out = d.base;
+    return FUSEDTOK_OK;
+}
+
+}  // namespace
+
+int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const void* k, const void* v,
+                                             const int* lens, void* out, int batch, int q_heads, int kv_heads,
+                                             int cache_rows, int dim, uintptr_t stream) {
+    if (dtype < 0 || dtype > 2) return fail(FUSEDTOK_INVALID_ARGUMENT, "dtype must be 0 (f32), 1 (bf16) or 2 (fp16)");
+    int rc = attention_check(batch, q_heads, kv_heads, cache_rows, dim);
+    if (rc) return rc;
+    if (batch == 0) return FUSEDTOK_OK;
+    cudaStream_t cs = (cudaStream_t)stream;
+    const long long out_rows = (long long)batch * q_heads;
+    if (cache_rows == 0) {
+        const cudaError_t e = cudaMemsetAsync(out, 0, (size_t)out_rows * dim * dtype_size(dtype), cs);
+        if (e != cudaSuccess) return cuda_fail("attention zero fill failed", e);
+        return FUSEDTOK_OK;
+    }
+    unsigned char* base = nullptr;
+    int sm_count = 0;
+    if ((rc = noalloc_setup(&base, &sm_count))) return rc;
+
+    // same kernel selection as the allocating launcher
+    const int G = q_heads / kv_heads;
+    const unsigned long long map_rows = (unsigned long long)batch * kv_heads * (unsigned long long)cache_rows;
+    const bool use_tc = dtype != F32 && (dim == 64 || dim == 128) && map_rows < (1ull << 31) &&
+                        ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
+                        ((reinterpret_cast<uintptr_t>(q)) & 3u) == 0;
+    DecodeParams p;
+    memset(&p, 0, sizeof(p));
+    p.q = q; p.k = k; p.v = v; p.out = out; p.lens = lens;
+    p.B = batch; p.Hq = q_heads; p.Hkv = kv_heads; p.G = G; p.T = cache_rows; p.D = dim;
+    p.scale = 1.0f / sqrtf((float)dim);
+    int lc = 1, gp = 8;
+    if (use_tc) {
+        p.GC = std::min(G, 16);
+        gp = p.GC <= 8 ? 8 : 16;
+    } else {
+        lc = dim <= 128 ? 1 : (dim <= 256 ? 2 : 4);
+        if (G == 1) p.GC = 1;
+        else if (lc == 1) p.GC = G <= 4 ? 4 : 8;
+        else if (lc == 2) p.GC = 4;
+        else p.GC = 2;
+    }
+    p.NCH = (G + p.GC - 1) / p.GC;
+    const unsigned long long units = (unsigned long long)batch * kv_heads * p.NCH;
+    const unsigned long long max_tiles = units * (unsigned long long)((cache_rows + TILE - 1) / TILE);
+    p.ncta = (int)std::min<unsigned long long>((unsigned long long)sm_count * (use_tc ? 1 : 2), max_tiles);
+    if (p.ncta < 1) p.ncta = 1;
+
+    // carve the static array: [256 B header | meta | (m, l) slots | acc slots]
+    const size_t slots = (size_t)units + (size_t)p.ncta;
+    const size_t meta_b = align_up((size_t)units * sizeof(int2), 256);
+    const size_t ml_b = align_up(slots * p.GC * 2 * sizeof(float), 256);
+    const size_t acc_b = align_up(slots * p.GC * (size_t)dim * sizeof(float), 256);
+    const size_t need = 256 + meta_b + ml_b + acc_b;
+    if (need > kNoAllocBytes)
+        return fail(FUSEDTOK_INVALID_ARGUMENT,
+                    "shape needs " + std::to_string(need) + " bytes of split-KV scratch but the allocation-free "
+                    "entry point has a fixed " + std::to_string(kNoAllocBytes) + " bytes; use "
+                    "fusedtok_attention_decode_launch* for this shape");
+    p.status = reinterpret_cast<int*>(base);
+    p.total_out = reinterpret_cast<long long*>(base) + 1;
+    p.meta = reinterpret_cast<int2*>(base + 256);
+    p.ws_ml = reinterpret_cast<float*>(base + 256 + meta_b);
+    p.ws_acc = reinterpret_cast<float*>(base + 256 + meta_b + ml_b);
+    cudaError_t e = cudaMemsetAsync(base, 0, 256, cs);          // header must start at zero
+    if (e != cudaSuccess) return cuda_fail("static scratch header clear failed", e);
+
+    if (use_tc) {
+        if ((rc = get_encode_fn())) return rc;
+        CUtensorMap mk, mv;
+        if ((rc = encode_map(&mk, dtype, k, map_rows, dim, TILE))) return rc;
+        if ((rc = encode_map(&mv, dtype, v, map_rows, dim, TILE))) return rc;
+        if (dtype == BF16) launch_tc_t<__nv_bfloat16>(mk, mv, p, gp, false, cs);
+        else launch_tc_t<__half>(mk, mv, p, gp, false, cs);
+        if ((rc = check_launch("attention split-KV tensor-core kernel launch"))) return rc;
+    } else {
+        if (dtype == F32) launch_simt_t<float>(p, lc, cs);
+        else if (dtype == BF16) launch_simt_t<__nv_bfloat16>(p, lc, cs);
+        else launch_simt_t<__half>(p, lc, cs);
+        if ((rc = check_launch("attention split-KV kernel launch"))) return rc;
+    }
+    if (dtype == F32) launch_merge_t<float>(p, cs);
+    else if (dtype == BF16) launch_merge_t<__nv_bfloat16>(p, cs);
+    else launch_merge_t<__half>(p, cs);
+    return check_launch("attention merge kernel launch");
+}
+
 long long fusedtok_attention_launch_count(int reset) {
     const long long n = g_launches;
     if (reset) g_launches = 0;

@@ -120,6 +120,25 @@ int fusedtok_attention_merge_partials_launch(int dtype, const float* partials, i
                                              void* out, int batch, int q_heads, int dim,
                                              uintptr_t stream);
 
+/* ---- allocation-free launcher (no counterpart in the reference, whose split
+ * path always owns a cudaMalloc'ed workspace) -------------------------------
+ * For hosts that must not allocate device memory after start-up (a server that
+ * gave its whole budget to its own pool, a process under an allocator-policing
+ * shim, a latency-critical loop that cannot take cudaMalloc's implicit sync).
+ * Same inputs, outputs and results as fusedtok_attention_decode_launch{,_bf16,
+ * _fp16} (dtype 0 float32, 1 bfloat16, 2 float16), but the split-KV scratch is
+ * a fixed 4 MiB array inside the library image, held by every GPU that loads
+ * the library until the process exits. Calls no cudaMalloc / cudaFree and no
+ * allocating library routine. Shapes whose scratch would exceed 4 MiB
+ * ((batch*kv_heads*chunks + CTAs) * heads_per_chunk * (dim + 2) floats, plus
+ * 8 bytes per unit) are rejected with FUSEDTOK_INVALID_ARGUMENT. The first call
+ * on a device looks up the array's device address and sets kernel attributes:
+ * make it before any stream capture. All calls on a device share the array;
+ * calls that overlap on the GPU race on it. */
+int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const void* k, const void* v,
+                                             const int* lens, void* out, int batch, int q_heads,
+                                             int kv_heads, int cache_rows, int dim, uintptr_t stream);
+
 /* ---- diagnostics -----------------------------------------------------------
  * Every device-side wait in the kernels is bounded; a wait that expires stores
  * a non-zero code in a per-device status word and the kernel still completes.
