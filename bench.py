@@ -20,8 +20,8 @@ e2e            : the same metric through the public Python operator with the
                  input; `e2e_staged` additionally reports the staged entry point
                  that copies the whole cache from host memory each call.
 roofline       : HBM bound; achieved = algorithmic bytes / step time (partial
-                 kernel + merge kernel + launch gap, so it understates the
-                 partial kernel alone); peak = measured copy bandwidth.
+                 kernel incl. its in-kernel merge, plus the launch gap between
+                 steps); peak = measured copy bandwidth.
 cpu_baseline   : the reference's own CPU implementation (built from the
                  reference sources) or, where that build is absent, the C
                  restatement, on the host cores, on a bounded sample.
@@ -309,6 +309,7 @@ def run_ours(args, w, rank, world, local_rank):
 
     def step(i):
         k, v = sets[i % n_sets]
+        stream = torch.cuda.current_stream()        # the capture stream while a graph is being recorded
         if split_kv:
             dec.decode(q, k, v, None, out)
         elif w["paged"]:
@@ -358,7 +359,7 @@ def run_ours(args, w, rank, world, local_rank):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    launches = _fusedtok.attention_launch_count() if not graphs else 2 * args.steps
+    launches = _fusedtok.attention_launch_count() if not graphs else args.steps
     if args.profile:
         print(json.dumps({"profile_run": True, "ms_per_step": ms / args.steps, "workload": args.workload,
                           "GBps": bytes_step / (ms / args.steps * 1e-3) / 1e9}), flush=True)
@@ -460,7 +461,7 @@ def run_ours(args, w, rank, world, local_rank):
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                      "frac": per_gpu / peak, "peak_kind": "of " + peak_kind,
                      "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                     "note": "achieved = algorithmic bytes / whole step time (partial + merge kernels)"},
+                     "note": "achieved = algorithmic bytes / whole step time (one kernel per step, launch gaps included)"},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s / args.steps * 1e3,
                 "note": "public operator; q/lens H2D from pinned memory and result D2H + host read every step; "

@@ -19,7 +19,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libfusedtok_b200.so")
+# FUSEDTOK_B200_LIB may point at another build of the same library (e.g. an instrumented one)
+_LIB_PATH = os.environ.get("FUSEDTOK_B200_LIB") or os.path.join(_HERE, "libfusedtok_b200.so")
 
 if not os.path.exists(_LIB_PATH):
     raise ImportError(

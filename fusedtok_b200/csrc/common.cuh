@@ -11,9 +11,12 @@
 // a few SEGMENTS (maximal runs of tiles of one unit). A segment that covers
 // its whole unit is finished in place; otherwise its (m, l, acc) goes to the
 // workspace slot c + unit (unique, because both indices only grow along the
-// walk) and the merge kernel folds the slots of that unit in CTA order.
-// The split depends only on (lens, n), so results are bit-identical from
-// call to call.
+// walk), the CTA bumps the unit's arrival counter, and whichever CTA arrives
+// last folds the unit's slots - always in CTA order, so the result does not
+// depend on who was last. The split depends only on (lens, n): results are
+// bit-identical from call to call. (Counterpart of the reference's workspace +
+// attn_reduce_kernel, src/attention.cu:434-463 and :478-549, without the
+// second launch.)
 #pragma once
 
 #include <cuda_bf16.h>
@@ -46,9 +49,8 @@ struct DecodeParams {
     const int* table;     // [B, tbl_width] block ids, null for contiguous
     float* ws_ml;         // [slots][GC][2]  (m natural-log units, l)
     float* ws_acc;        // [slots][GC][D]  unnormalised
-    int2* meta;           // [units] (first CTA, last CTA) touching the unit
+    int* counters;        // [units] arrival counters, zero between launches (the last arriver resets)
     int* status;          // device status word
-    long long* total_out; // tiles in this launch (written by CTA 0, read by the merge kernel)
     float* triple_ml;     // when non-null: emit (m, l) here [B, Hq, 2] ...
     float* triple_acc;    // ... and unnormalised acc here [B, Hq, D]
     int B, Hq, Hkv, G;    // G = Hq / Hkv
@@ -56,8 +58,12 @@ struct DecodeParams {
     int T;                // cache rows (contiguous) or tbl_width * page
     int D;
     int page, tbl_width;
+    int box_rows, box_shift;   // rows per TMA box (a power of two) and its log2 (tensor-core kernel)
     int ncta;
     float scale;          // 1/sqrt(D)
+#ifdef FTK_PROFILE
+    long long* prof;      // per-CTA cycle counters (instrumented builds only)
+#endif
 };
 
 // Float offset of the acc block inside a triple buffer of `rows` (b, h) rows:
@@ -194,7 +200,6 @@ __device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w) {
         total_nt = block_sum(loc, sh->red);
     }
     const long long total = total_nt * upb;
-    if (c == 0 && threadIdx.x == 0) *p.total_out = total;
     const long long start = (total * c) / p.ncta;
     const long long end = (total * (c + 1)) / p.ncta;
     if (start >= end) return false;
@@ -277,15 +282,22 @@ __device__ __forceinline__ int owner_of(long long x, long long total, int n) {
 struct SegDest {
     bool whole;          // the segment covers its whole unit: finish in place
     size_t slot;         // workspace slot otherwise
+    long long unit;      // global unit index
     int b, h0;           // sequence and first query head of the unit
     int gvalid;          // query heads in this unit
+    int c_first, c_last; // CTAs holding the unit's first and last tile
+    int nparts;          // CTAs that deliver a partial for this unit
 };
+
+__device__ __forceinline__ bool cta_range_empty(long long total, int n, int c) {
+    return (total * c) / n == (total * (c + 1)) / n;
+}
 
 __device__ __forceinline__ SegDest seg_dest(const DecodeParams& p, const Walker& w, long long total,
                                             long long seg_first_g) {
     SegDest d;
     const int upb = p.Hkv * p.NCH;
-    const long long unit = (long long)w.b * upb + w.ub;
+    d.unit = (long long)w.b * upb + w.ub;
     const long long u_start = w.g - w.ti;            // global index of the unit's tile 0
     const long long u_end = u_start + w.nt;
     const int kv = w.ub / p.NCH, ch = w.ub % p.NCH;
@@ -293,12 +305,16 @@ __device__ __forceinline__ SegDest seg_dest(const DecodeParams& p, const Walker&
     d.h0 = kv * p.G + ch * p.GC;
     d.gvalid = min(p.GC, p.G - ch * p.GC);
     d.whole = (seg_first_g == u_start) && (w.g + 1 == u_end);
-    d.slot = (size_t)blockIdx.x + (size_t)unit;
-    if (seg_first_g == u_start && (threadIdx.x & 31) == 0) {
-        // the CTA holding the unit's first tile records who else holds parts
-        // (every warp's lane 0 writes the same value)
-        const int c_last = owner_of(u_end - 1, total, p.ncta);
-        p.meta[unit] = make_int2((int)blockIdx.x, c_last);
+    d.slot = (size_t)blockIdx.x + (size_t)d.unit;
+    d.c_first = d.c_last = (int)blockIdx.x;
+    d.nparts = 1;
+    if (!d.whole) {
+        d.c_first = owner_of(u_start, total, p.ncta);
+        d.c_last = owner_of(u_end - 1, total, p.ncta);
+        d.nparts = d.c_last - d.c_first + 1;
+        if (p.ncta > total)                          // more CTAs than tiles: some ranges are empty
+            for (int c = d.c_first + 1; c < d.c_last; ++c)
+                if (cta_range_empty(total, p.ncta, c)) --d.nparts;
     }
     return d;
 }
@@ -320,6 +336,62 @@ __device__ __forceinline__ void emit_final2(const DecodeParams& p, int b, int h,
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         Store<T>::st2(reinterpret_cast<T*>(p.out) + r * p.D + d, a0 * inv, a1 * inv);
     }
+}
+
+// Fold the workspace slots of a split unit into its final rows. Called by all
+// `nthreads` threads (index `tid`) of the CTA that delivered the last partial.
+// The reference's rule (attn_reduce_kernel, src/attention.cu:503-548):
+// partials with l <= 0 are skipped, the first live one is adopted verbatim,
+// later ones are max-rescaled, then the row is divided by l.
+template <typename T>
+__device__ __forceinline__ void merge_unit(const DecodeParams& p, const SegDest& d, long long total, int tid,
+                                           int nthreads) {
+    constexpr int BATCH = 8;                      // slots fetched together: one L2 round trip per batch
+    const int D = p.D, halfd = D >> 1;
+    const bool sparse = p.ncta > total;
+    for (int e = tid; e < d.gvalid * halfd; e += nthreads) {
+        const int g = e / halfd, dd = (e % halfd) * 2;
+        float m = -INFINITY, l = 0.0f, a0 = 0.0f, a1 = 0.0f;
+        for (int c0 = d.c_first; c0 <= d.c_last; c0 += BATCH) {
+            float2 ml[BATCH], x[BATCH];
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) {
+                const int c = c0 + j;
+                ml[j] = make_float2(0.0f, 0.0f);
+                x[j] = make_float2(0.0f, 0.0f);
+                if (c <= d.c_last && !(sparse && cta_range_empty(total, p.ncta, c))) {
+                    const size_t pr = ((size_t)c + (size_t)d.unit) * p.GC + g;
+                    ml[j] = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + pr * 2));
+                    x[j] = __ldcg(reinterpret_cast<const float2*>(p.ws_acc + pr * D + dd));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < BATCH; ++j) {
+                if (ml[j].y <= 0.0f) continue;
+                if (l == 0.0f) {
+                    m = ml[j].x; l = ml[j].y; a0 = x[j].x; a1 = x[j].y;
+                    continue;
+                }
+                const float m_new = fmaxf(m, ml[j].x);
+                const float r_old = expf(m - m_new), r_new = expf(ml[j].x - m_new);
+                l = l * r_old + ml[j].y * r_new;
+                a0 = a0 * r_old + x[j].x * r_new;
+                a1 = a1 * r_old + x[j].y * r_new;
+                m = m_new;
+            }
+        }
+        emit_final2<T>(p, d.b, d.h0 + g, dd, m, l, a0, a1, dd == 0);
+    }
+}
+
+// One thread per CTA calls this after every thread of the CTA has written and
+// fenced its part of the partial. Returns true if this CTA delivered the last
+// partial of the unit and must therefore merge it.
+__device__ __forceinline__ bool deliver_partial(const DecodeParams& p, const SegDest& d) {
+    const int old = atomicAdd(p.counters + d.unit, 1);
+    const bool last = old == d.nparts - 1;
+    if (last) p.counters[d.unit] = 0;          // ready for the next launch
+    return last;
 }
 
 }  // namespace ftk

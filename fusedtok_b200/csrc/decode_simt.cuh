@@ -33,6 +33,7 @@ decode_simt_kernel(const DecodeParams p) {
     __shared__ float2 s_ml[SIMT_WARPS][GC];
     __shared__ float s_scale[SIMT_WARPS][GC];
     __shared__ float2 s_glob[GC];
+    __shared__ int s_last;
 
     Walker w;
     if (!sched_init<T>(p, &sh, w)) return;
@@ -188,6 +189,17 @@ decode_simt_kernel(const DecodeParams p) {
                     const size_t pr = dst.slot * p.GC + g;
                     *reinterpret_cast<float2*>(p.ws_acc + pr * D + d) = make_float2(a0, a1);
                     if (d == 0) *reinterpret_cast<float2*>(p.ws_ml + pr * 2) = ml;
+                }
+            }
+            if (!dst.whole) {
+                // publish the partial; the CTA that publishes a unit's last one merges it
+                __threadfence();
+                __syncthreads();
+                if (threadIdx.x == 0) s_last = deliver_partial(p, dst) ? 1 : 0;
+                __syncthreads();
+                if (s_last) {
+                    __threadfence();
+                    merge_unit<T>(p, dst, total, threadIdx.x, SIMT_THREADS);
                 }
             }
         }

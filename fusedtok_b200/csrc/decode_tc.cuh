@@ -9,17 +9,23 @@
 //    with TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, L2 evict-first),
 //    completion signalled on mbarriers. It runs ahead across unit boundaries,
 //    so the HBM stream never drains while consumers finish a unit.
-//    Contiguous cache: one [64 x 64-element] box per half of D for K and for V.
-//    Paged cache: the block table is read one entry per lane and every lane
-//    issues the boxes of its own page, so the indirection costs no per-row
-//    integer divide and no dependent load in the consumers.
+//    The cache is described to TMA as a rank-3 tensor (64 elements, rows,
+//    128-byte column blocks of a row), so ONE copy brings a [rows x D] box and
+//    lays it out as [column block][row][128 B] in shared memory, the layout
+//    the swizzled ldmatrix reads want. Contiguous cache: one 16 KB box for K
+//    and one for V per tile. Paged cache: the block table is read one entry
+//    per lane and every lane issues the two boxes of its own page, so the
+//    indirection costs no per-row integer divide and no dependent load in
+//    the consumers.
 //  * The query heads of one GQA group are the M rows of an m16n8k16 tensor-core
 //    tile (S = Q K^T, O += P V), so every K/V byte is read from HBM once and
 //    from shared memory once, for all heads of the group. Tiles alternate
 //    between two groups of 4 consumer warps; each warp owns 16 rows of a tile
 //    and keeps an fp32 online-softmax state (m, l, O) in registers.
 //  * At the end of a segment the 8 warp states are folded through shared
-//    memory and either finished in place or written to the workspace.
+//    memory and either finished in place or written to the workspace; the
+//    CTA that delivers the last partial of a unit merges them (no second
+//    launch).
 //
 // Every wait on an mbarrier is bounded (wall-clock limit); on expiry the
 // kernel records a status code, stops waiting and still runs to completion,
@@ -115,23 +121,26 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
     return pol;
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
-                                            uint32_t bar, uint64_t pol) {
+// Box [64 elements, box_rows rows, D/64 column blocks] starting at row `row`.
+__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* map, int row, uint32_t bar,
+                                              uint64_t pol) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%2, %3}], [%4], %5;"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar), "l"(pol)
+        "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3, %4}], [%5], %6;"
+        ::"r"(dst), "l"(map), "r"(0), "r"(row), "r"(0), "r"(bar), "l"(pol)
         : "memory");
 }
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
+                 : "r"(addr)
+                 : "memory");
 }
 __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
+                 : "r"(addr)
+                 : "memory");
 }
 template <typename T>
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -195,6 +204,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
     __syncthreads();
 
+#ifdef FTK_PROFILE
+    const long long prof_t0 = clock64();
+    long long prof_wait = 0, prof_epi = 0, prof_first = 0, prof_qk = 0, prof_sm = 0, prof_pv = 0, prof_segb = 0;
+#endif
     Walker w;
     if (!sched_init<T>(p, sh, w)) return;      // block-uniform
     const long long total = sh->total;
@@ -206,10 +219,20 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         if (*abort_flag) return;
         const uint64_t pol = policy_evict_first();
         int issued = 0;
-        for (long long i = 0; w.g < w.end; ++i) {
-            const int s = (int)(i % Cfg::NS);
-            const uint32_t ph = (uint32_t)((i / Cfg::NS) & 1);
+        // paged cache: 32 consecutive block-table entries of the current sequence, one per lane,
+        // fetched with one coalesced load and reused for the tiles they cover
+        int tbl_b = -1, tbl_base = 0, tbl_val = 0;
+        int s = 0;                 // ring stage of tile i
+        uint32_t ph = 0;           // phase parity of that stage's current use
+        for (int i = 0; w.g < w.end; ++i) {
+#ifdef FTK_PROFILE
+            const long long tw0 = clock64();
+#endif
             const bool ok = mbar_wait(bar_empty + s * 8, ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY_TIMEOUT);
+#ifdef FTK_PROFILE
+            prof_wait += clock64() - tw0;
+            if (i == 0) prof_first = clock64() - prof_t0;
+#endif
             if (!ok) break;
             const int kv = w.ub / upb_nch;
             const uint32_t dst_k = smem_base + s * Cfg::STAGE_BYTES;
@@ -219,43 +242,47 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 if (lane == 0) {
                     const int row = (w.b * p.Hkv + kv) * p.T + w.ti * TILE;
                     mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-#pragma unroll
-                    for (int h = 0; h < Cfg::NH; ++h) {
-                        tma_load_2d(dst_k + h * (TILE * 128), &tm_k, h * 64, row, fb, pol);
-                        tma_load_2d(dst_v + h * (TILE * 128), &tm_v, h * 64, row, fb, pol);
-                    }
+                    tma_load_rows(dst_k, &tm_k, row, fb, pol);
+                    tma_load_rows(dst_v, &tm_v, row, fb, pol);
                 }
             } else {
                 const int t0 = w.ti * TILE;
                 const int valid = min(TILE, w.len - t0);
                 if (p.page <= TILE) {
                     const int npg = (valid + p.page - 1) / p.page;
+                    const int pg0 = t0 >> p.box_shift;                 // first page of the tile (page == box rows)
+                    if (tbl_b != w.b || pg0 < tbl_base || pg0 + npg > tbl_base + 32) {
+                        tbl_b = w.b;
+                        tbl_base = pg0;
+                        const int idx = pg0 + lane;
+                        tbl_val = idx < p.tbl_width ? __ldg(p.table + (size_t)w.b * p.tbl_width + idx) : 0;
+                    }
                     if (lane == 0) mbar_expect_tx(fb, (uint32_t)(npg * p.page * D * 4));
-                    __syncwarp();
+                    const int blk = __shfl_sync(0xffffffffu, tbl_val, (pg0 - tbl_base + lane) & 31);
                     if (lane < npg) {
-                        const int blk = __ldg(p.table + (size_t)w.b * p.tbl_width + t0 / p.page + lane);
                         const int row = (blk * p.Hkv + kv) * p.page;
-                        const uint32_t off = (uint32_t)(lane * p.page) * 128u;
-#pragma unroll
-                        for (int h = 0; h < Cfg::NH; ++h) {
-                            tma_load_2d(dst_k + h * (TILE * 128) + off, &tm_k, h * 64, row, fb, pol);
-                            tma_load_2d(dst_v + h * (TILE * 128) + off, &tm_v, h * 64, row, fb, pol);
-                        }
+                        const uint32_t off = (uint32_t)(lane * p.page) * (uint32_t)(D * 2);   // page-major stage
+                        tma_load_rows(dst_k + off, &tm_k, row, fb, pol);
+                        tma_load_rows(dst_v + off, &tm_v, row, fb, pol);
                     }
                 } else if (lane == 0) {
                     const int blk = __ldg(p.table + (size_t)w.b * p.tbl_width + t0 / p.page);
                     const int row = (blk * p.Hkv + kv) * p.page + (t0 % p.page);
                     mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-#pragma unroll
-                    for (int h = 0; h < Cfg::NH; ++h) {
-                        tma_load_2d(dst_k + h * (TILE * 128), &tm_k, h * 64, row, fb, pol);
-                        tma_load_2d(dst_v + h * (TILE * 128), &tm_v, h * 64, row, fb, pol);
-                    }
+                    tma_load_rows(dst_k, &tm_k, row, fb, pol);
+                    tma_load_rows(dst_v, &tm_v, row, fb, pol);
                 }
             }
             ++issued;
             walker_advance(p, w);
+            if (++s == Cfg::NS) { s = 0; ph ^= 1u; }
         }
+#ifdef FTK_PROFILE
+        if (lane == 0 && p.prof) {
+            long long* o = p.prof + (size_t)blockIdx.x * 16;
+            o[4] = prof_wait; o[5] = prof_first; o[6] = clock64() - prof_t0; o[7] = issued;
+        }
+#endif
         // If something went wrong, do not leave the CTA while our own copies
         // may still be landing in its shared memory: wait (bounded) for the
         // last phase of every stage that was issued.
@@ -292,18 +319,37 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     float m_run[2], l_run[2];
     long long seg_first = w.g;
 
+    // Stage layout: boxes of `box_rows` rows back to back; inside a box the
+    // D/64 column blocks one after the other, each [box_rows][128 B] with the
+    // 16-byte chunks of a row XOR-swizzled by (row & 7).
+    const int box_rows = p.box_rows, box_shift = p.box_shift;
+    const uint32_t half_stride = (uint32_t)box_rows * 128u;
+    auto row_off = [&](int r) -> uint32_t {
+        return (uint32_t)(r >> box_shift) * (uint32_t)(box_rows * D * 2) + (uint32_t)(r & (box_rows - 1)) * 128u;
+    };
     // per-lane ldmatrix row geometry (constant over the kernel)
     const int lrow = lane & 7, lmat = lane >> 3;
     // K (non-transposed): matrices (rows 0-7, chunk c), (rows 0-7, c+1), (rows 8-15, c), (rows 8-15, c+1)
-    const int k_row = wr * 16 + (lmat >> 1) * 8 + lrow;
+    const uint32_t k_off = row_off(wr * 16 + (lmat >> 1) * 8 + lrow);
     const int k_csel = lmat & 1;
     // V (transposed): matrices (rows 0-7, chunk c), (rows 8-15, c), (rows 0-7, c+1), (rows 8-15, c+1)
-    const int v_row = wr * 16 + (lmat & 1) * 8 + lrow;
+    const uint32_t v_off = row_off(wr * 16 + (lmat & 1) * 8 + lrow);
     const int v_csel = lmat >> 1;
 
-    for (long long i = 0; w.g < w.end; ++i) {
+#ifdef FTK_PROFILE
+    long long prof_own = 0, prof_other = 0;
+#endif
+    int s = 0;                     // ring stage of tile i
+    uint32_t ph = 0;               // phase parity of that stage's current use
+    for (int i = 0; w.g < w.end; ++i) {
+#ifdef FTK_PROFILE
+        const long long ti0 = clock64();
+#endif
         if (i == 0 || w.ti == 0) {
             // ---- segment begins: fetch the group's query rows as MMA A fragments
+#ifdef FTK_PROFILE
+            const long long tb0 = clock64();
+#endif
             seg_first = w.g;
             const int kv = w.ub / upb_nch, ch = w.ub % upb_nch;
             const int gvalid = min(p.GC, p.G - ch * p.GC);
@@ -324,14 +370,26 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             for (int nb = 0; nb < NB; ++nb) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.0f;
             m_run[0] = m_run[1] = -INFINITY;
             l_run[0] = l_run[1] = 0.0f;
+#ifdef FTK_PROFILE
+            prof_segb += clock64() - tb0;
+#endif
         }
 
-        if ((int)(i & 1) == cg) {
-            const int s = (int)(i % Cfg::NS);
-            const uint32_t ph = (uint32_t)((i / Cfg::NS) & 1);
+        if ((i & 1) == cg) {
+#ifdef FTK_PROFILE
+            const long long tw0 = clock64();
+#endif
             const bool ok = mbar_wait(bar_full + s * 8, ph, abort_flag, p.status, ST_WAIT_FULL_TIMEOUT);
+#ifdef FTK_PROFILE
+            prof_wait += clock64() - tw0;
+            if (i < 2) prof_first = clock64() - prof_t0;
+#endif
             const int rows_valid = w.len - w.ti * TILE;      // >= 1
+#ifdef FTK_EXP_NOCOMPUTE
+            if (false) {
+#else
             if (ok && wr * 16 < rows_valid) {
+#endif
                 const uint32_t st_k = smem_base + s * Cfg::STAGE_BYTES;
                 const uint32_t st_v = st_k + Cfg::KV_BYTES;
                 const bool ragged = rows_valid < wr * 16 + 16;
@@ -340,21 +398,23 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     // (stale or foreign data): clear the V rows so that a zero
                     // weight times their contents stays zero
                     uint8_t* vb = smem + s * Cfg::STAGE_BYTES + Cfg::KV_BYTES;
-                    for (int r = wr * 16 + (rows_valid - wr * 16); r < wr * 16 + 16; ++r)
+                    for (int r = rows_valid; r < wr * 16 + 16; ++r)
                         for (int h = 0; h < Cfg::NH; ++h)
                             if (lane < 8)
-                                *reinterpret_cast<uint4*>(vb + h * (TILE * 128) + r * 128 + lane * 16) = make_uint4(0, 0, 0, 0);
+                                *reinterpret_cast<uint4*>(vb + row_off(r) + h * half_stride + lane * 16) = make_uint4(0, 0, 0, 0);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                 }
+#ifdef FTK_PROFILE
+                const long long tq0 = clock64();
+#endif
                 // ---- S = Q K^T for 16 cache rows (two n-blocks of 8)
                 float sa[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
                 float sb[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
                 for (int kk = 0; kk < KSTEPS; ++kk) {
                     const int chunk = kk * 2 + k_csel;
-                    const uint32_t addr = st_k + (chunk >> 3) * (TILE * 128) + k_row * 128 +
-                                          (((chunk & 7) ^ lrow) << 4);
+                    const uint32_t addr = st_k + k_off + (chunk >> 3) * half_stride + (((chunk & 7) ^ lrow) << 4);
                     uint32_t r0, r1, r2, r3;
                     ldsm_x4(addr, r0, r1, r2, r3);
                     const uint32_t a0 = qa[kk][0];
@@ -371,6 +431,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 }
                 // ---- online softmax (log2 domain), rows `quad` and `quad + 8`
                 float sc[2][4];
+#ifdef FTK_PROFILE
+                const long long tq1 = clock64();
+                prof_qk += tq1 - tq0;
+#endif
 #pragma unroll
                 for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
@@ -408,25 +472,37 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     }
                 }
                 if constexpr (GP == 8) { pa[1] = 0u; pa[3] = 0u; }
+#ifdef FTK_PROFILE
+                const long long tq2 = clock64();
+                prof_sm += tq2 - tq1;
+#endif
                 // ---- O += P V
 #pragma unroll
                 for (int c = 0; c < NB; c += 2) {
                     const int chunk = c + v_csel;
-                    const uint32_t addr = st_v + (chunk >> 3) * (TILE * 128) + v_row * 128 +
-                                          (((chunk & 7) ^ lrow) << 4);
+                    const uint32_t addr = st_v + v_off + (chunk >> 3) * half_stride + (((chunk & 7) ^ lrow) << 4);
                     uint32_t r0, r1, r2, r3;
                     ldsm_x4_t(addr, r0, r1, r2, r3);
                     mma16816<T>(acc[c], pa[0], pa[1], pa[2], pa[3], r0, r1);
                     mma16816<T>(acc[c + 1], pa[0], pa[1], pa[2], pa[3], r2, r3);
                 }
+#ifdef FTK_PROFILE
+                prof_pv += clock64() - tq2;
+#endif
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + s * 8);
         }
 
+#ifdef FTK_PROFILE
+        if ((i & 1) == cg) prof_own += clock64() - ti0; else prof_other += clock64() - ti0;
+#endif
         const bool seg_end = (w.ti == w.nt - 1) || (w.g + 1 == w.end);
         if (seg_end) {
             // ---- fold the 8 warp states and emit
+#ifdef FTK_PROFILE
+            const long long te0 = clock64();
+#endif
             const SegDest dst = seg_dest(p, w, total, seg_first);
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
@@ -482,9 +558,34 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     }
                 }
             }
+            if (!dst.whole) {
+                // publish the partial; the CTA that publishes a unit's last one merges it
+                __threadfence();
+                bar_consumers();
+                volatile int* s_last = abort_flag + 1;
+                if (warp == 0 && lane == 0) *s_last = deliver_partial(p, dst) ? 1 : 0;
+                bar_consumers();
+                if (*s_last) {
+                    __threadfence();
+                    merge_unit<T>(p, dst, total, warp * 32 + lane, NCW * 32);
+                }
+            }
+#ifdef FTK_PROFILE
+            prof_epi += clock64() - te0;
+#endif
         }
         walker_advance(p, w);
+        if (++s == Cfg::NS) { s = 0; ph ^= 1u; }
     }
+#ifdef FTK_PROFILE
+    if (warp < 2 && lane == 0 && p.prof) {      // warp 0: group 0, warp 4 would be group 1; record warp 0 only
+        if (warp == 0) {
+            long long* o = p.prof + (size_t)blockIdx.x * 16;
+            o[0] = clock64() - prof_t0; o[1] = prof_first; o[2] = prof_wait; o[3] = prof_epi;
+            o[8] = prof_qk; o[9] = prof_sm; o[10] = prof_pv; o[11] = prof_segb; o[12] = prof_own; o[13] = prof_other;
+        }
+    }
+#endif
     (void)g_begin;
 }
 

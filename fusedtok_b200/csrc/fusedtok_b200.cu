@@ -26,6 +26,9 @@ namespace {
 
 using namespace ftk;
 
+#ifdef FTK_PROFILE
+long long* g_prof_buf = nullptr;
+#endif
 thread_local std::string g_err;
 thread_local long long g_launches = 0;
 
@@ -63,6 +66,8 @@ struct DeviceState {
     char* arena = nullptr;                   // current arena (older ones stay alive: graphs may hold them)
     size_t arena_bytes = 0;
     int* status = nullptr;                   // separate small allocation, never moves
+    int* counters = nullptr;                 // per-unit arrival counters, zero between launches
+    size_t counters_cap = 0;                 // in units
     bool smem_attr_set = false;
 };
 DeviceState g_dev[kMaxDevices];
@@ -122,11 +127,11 @@ int device_state(DeviceState** out) {
 
 struct Arena {
     int* status;
-    long long* total;
-    int2* meta;
+    int* counters;
     float* ws_ml;
     float* ws_acc;
 };
+constexpr size_t kCountersMin = 1u << 16;    // units covered by the first counters allocation
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -135,13 +140,12 @@ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 int get_arena(DeviceState& d, cudaStream_t cs, size_t units, int ncta, int gc, int dim, bool need_smem_attr,
               Arena* a) {
     const size_t slots = units + (size_t)ncta;
-    const size_t meta_b = align_up(units * sizeof(int2), 256);
     const size_t ml_b = align_up(slots * gc * 2 * sizeof(float), 256);
     const size_t acc_b = align_up(slots * gc * (size_t)dim * sizeof(float), 256);
-    const size_t need = meta_b + ml_b + acc_b;
+    const size_t need = ml_b + acc_b;
     std::lock_guard<std::mutex> lock(g_mutex);
     const bool first = d.status == nullptr || (need_smem_attr && !d.smem_attr_set);
-    if (first || need > d.arena_bytes) {
+    if (first || need > d.arena_bytes || units > d.counters_cap) {
         if (stream_is_capturing(cs))
             return fail(FUSEDTOK_RUNTIME_ERROR,
                         "decode attention workspace must be allocated outside a CUDA graph capture - "
@@ -157,6 +161,20 @@ int get_arena(DeviceState& d, cudaStream_t cs, size_t units, int ncta, int gc, i
             if (rc) return rc;
             d.smem_attr_set = true;
         }
+        if (units > d.counters_cap) {
+            // counters live apart from the slots: slot regions of different shapes overlap, counters
+            // must stay zero between launches whatever shape ran last
+            const size_t cap = std::max(units, kCountersMin);
+            int* mem = nullptr;
+            cudaError_t e = cudaMalloc(&mem, cap * sizeof(int));
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                return fail(FUSEDTOK_RUNTIME_ERROR, "decode attention workspace allocation failed");
+            }
+            if ((e = cudaMemset(mem, 0, cap * sizeof(int))) != cudaSuccess) return cuda_fail("counter clear failed", e);
+            d.counters = mem;       // the previous block is kept alive for graphs captured earlier
+            d.counters_cap = cap;
+        }
         if (need > d.arena_bytes) {
             const size_t bytes = std::max(need, kArenaMin);
             char* mem = nullptr;
@@ -170,10 +188,9 @@ int get_arena(DeviceState& d, cudaStream_t cs, size_t units, int ncta, int gc, i
         }
     }
     a->status = d.status;
-    a->total = reinterpret_cast<long long*>(d.status) + 1;
-    a->meta = reinterpret_cast<int2*>(d.arena);
-    a->ws_ml = reinterpret_cast<float*>(d.arena + meta_b);
-    a->ws_acc = reinterpret_cast<float*>(d.arena + meta_b + ml_b);
+    a->counters = d.counters;
+    a->ws_ml = reinterpret_cast<float*>(d.arena);
+    a->ws_acc = reinterpret_cast<float*>(d.arena + ml_b);
     return FUSEDTOK_OK;
 }
 
@@ -190,13 +207,15 @@ int attention_check(int batch, int hq, int hkv, long long t_seq, int dim) {
     return FUSEDTOK_OK;
 }
 
+// The cache as a rank-3 tensor: (64 elements, rows with a stride of one cache row, D/64 column blocks of
+// 128 bytes). A box [64, box_rows, D/64] is one copy and lands as [column block][row][128 B].
 int encode_map(CUtensorMap* map, int dt, const void* base, unsigned long long rows, int dim, int box_rows) {
-    const cuuint64_t gdim[2] = {(cuuint64_t)dim, (cuuint64_t)rows};
-    const cuuint64_t gstride[1] = {(cuuint64_t)dim * 2};
-    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1u, 1u};
+    const cuuint64_t gdim[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(dim / 64)};
+    const cuuint64_t gstride[2] = {(cuuint64_t)dim * 2, 128u};
+    const cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)(dim / 64)};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
     const CUresult r = g_encode(map, dt == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                                2, const_cast<void*>(base), gdim, gstride, box, estr,
+                                3, const_cast<void*>(base), gdim, gstride, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -227,12 +246,6 @@ template <typename T> void launch_simt_t(const DecodeParams& p, int lc, cudaStre
     else if (lc == 2) { if (p.GC == 1) FTK_GO(1, 2); else FTK_GO(4, 2); }
     else { if (p.GC == 1) FTK_GO(1, 4); else FTK_GO(2, 4); }
 #undef FTK_GO
-}
-
-template <typename T> void launch_merge_t(const DecodeParams& p, cudaStream_t cs) {
-    const long long rows = (long long)p.B * p.Hq;
-    const unsigned grid = (unsigned)((rows + MERGE_WARPS - 1) / MERGE_WARPS);
-    merge_kernel<T><<<grid, MERGE_WARPS * 32, 0, cs>>>(p);
 }
 
 inline bool is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
@@ -306,7 +319,15 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
     Arena a;
     rc = get_arena(*dev, cs, (size_t)units, p.ncta, p.GC, dim, use_tc, &a);
     if (rc) return rc;
-    p.ws_ml = a.ws_ml; p.ws_acc = a.ws_acc; p.meta = a.meta; p.status = a.status; p.total_out = a.total;
+    p.ws_ml = a.ws_ml; p.ws_acc = a.ws_acc; p.counters = a.counters; p.status = a.status;
+#ifdef FTK_PROFILE
+    {
+        static long long* prof_buf = nullptr;
+        if (!prof_buf) { cudaMalloc(&prof_buf, 1024 * 16 * sizeof(long long)); cudaMemset(prof_buf, 0, 1024 * 16 * sizeof(long long)); }
+        p.prof = prof_buf;
+        g_prof_buf = prof_buf;
+    }
+#endif
 
     if (use_tc) {
         rc = get_encode_fn();
@@ -323,21 +344,19 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
             trows = map_rows;
             box_rows = TILE;
         }
+        p.box_rows = box_rows;
+        p.box_shift = 0;
+        while ((1 << p.box_shift) < box_rows) ++p.box_shift;
         if ((rc = encode_map(&mk, dt, k, trows, dim, box_rows))) return rc;
         if ((rc = encode_map(&mv, dt, v, trows, dim, box_rows))) return rc;
         if (dt == BF16) launch_tc_t<__nv_bfloat16>(mk, mv, p, gp, paged, cs);
         else launch_tc_t<__half>(mk, mv, p, gp, paged, cs);
-        if ((rc = check_launch("attention split-KV tensor-core kernel launch"))) return rc;
-    } else {
-        if (dt == F32) launch_simt_t<float>(p, lc, cs);
-        else if (dt == BF16) launch_simt_t<__nv_bfloat16>(p, lc, cs);
-        else launch_simt_t<__half>(p, lc, cs);
-        if ((rc = check_launch("attention split-KV kernel launch"))) return rc;
+        return check_launch("attention split-KV tensor-core kernel launch");
     }
-    if (dt == F32) launch_merge_t<float>(p, cs);
-    else if (dt == BF16) launch_merge_t<__nv_bfloat16>(p, cs);
-    else launch_merge_t<__half>(p, cs);
-    return check_launch("attention merge kernel launch");
+    if (dt == F32) launch_simt_t<float>(p, lc, cs);
+    else if (dt == BF16) launch_simt_t<__nv_bfloat16>(p, lc, cs);
+    else launch_simt_t<__half>(p, lc, cs);
+    return check_launch("attention split-KV kernel launch");
 }
 
 int decode_contig(int dt, const void* q, const void* k, const void* v, const int* lens, void* out,
@@ -543,8 +562,12 @@ int fusedtok_attention_device_status(int* status) {
     if (!dev->status) return FUSEDTOK_OK;
     if ((e = cudaMemcpy(status, dev->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
         return cuda_fail("status read failed", e);
-    if (*status != 0 && (e = cudaMemset(dev->status, 0, sizeof(int))) != cudaSuccess)
-        return cuda_fail("status clear failed", e);
+    if (*status != 0) {
+        // a launch that gave up may have left arrival counters half-way: start clean
+        if ((e = cudaMemset(dev->status, 0, sizeof(int))) != cudaSuccess) return cuda_fail("status clear failed", e);
+        if (dev->counters && (e = cudaMemset(dev->counters, 0, dev->counters_cap * sizeof(int))) != cudaSuccess)
+            return cuda_fail("counter clear failed", e);
+    }
     return FUSEDTOK_OK;
 }
 
@@ -567,13 +590,15 @@ int fusedtok_attention_device_status(int* status) {
 // attribute. Make that first call outside any stream capture.
 //
 // All calls on a device share the one array and it keeps whatever the previous
-// call left there. The status / tile-total header is cleared (stream-ordered) at
-// the start of every call; everything else is written before it is read within
-// a call. Two calls that overlap on the GPU (different streams) race on it.
+// call left there. The status header is cleared (stream-ordered) at the start
+// of every call; the per-unit arrival counters are left at zero by the kernels
+// themselves; everything else is written before it is read within a call. Two
+// calls that overlap on the GPU (different streams) race on it.
 // ---------------------------------------------------------------------------
 namespace {
 
 constexpr size_t kNoAllocBytes = 4u << 20;          // the stated maximum: 4 MiB of scratch
+constexpr size_t kNoAllocUnits = 16384;             // (sequence, kv head, head chunk) units it can track (64 KiB)
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 struct NoAllocDevice {
@@ -653,44 +678,56 @@ int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const voi
     p.ncta = (int)std::min<unsigned long long>((unsigned long long)sm_count * (use_tc ? 1 : 2), max_tiles);
     if (p.ncta < 1) p.ncta = 1;
 
-    // carve the static array: [256 B header | meta | (m, l) slots | acc slots]
+    // carve the static array: [256 B header | arrival counters (fixed size) | (m, l) slots | acc slots].
+    // The counter region has a fixed place and size so that it is never reused as slot storage:
+    // counters must read zero at the start of every call whatever shape ran before (the kernels
+    // leave them at zero; the array itself starts zeroed).
     const size_t slots = (size_t)units + (size_t)p.ncta;
-    const size_t meta_b = align_up((size_t)units * sizeof(int2), 256);
+    const size_t cnt_b = kNoAllocUnits * sizeof(int);
     const size_t ml_b = align_up(slots * p.GC * 2 * sizeof(float), 256);
     const size_t acc_b = align_up(slots * p.GC * (size_t)dim * sizeof(float), 256);
-    const size_t need = 256 + meta_b + ml_b + acc_b;
+    const size_t need = 256 + cnt_b + ml_b + acc_b;
+    if (units > kNoAllocUnits)
+        return fail(FUSEDTOK_INVALID_ARGUMENT,
+                    "shape has " + std::to_string(units) + " (sequence, kv head) units but the allocation-free "
+                    "entry point is limited to " + std::to_string(kNoAllocUnits));
     if (need > kNoAllocBytes)
         return fail(FUSEDTOK_INVALID_ARGUMENT,
                     "shape needs " + std::to_string(need) + " bytes of split-KV scratch but the allocation-free "
                     "entry point has a fixed " + std::to_string(kNoAllocBytes) + " bytes; use "
                     "fusedtok_attention_decode_launch* for this shape");
     p.status = reinterpret_cast<int*>(base);
-    p.total_out = reinterpret_cast<long long*>(base) + 1;
-    p.meta = reinterpret_cast<int2*>(base + 256);
-    p.ws_ml = reinterpret_cast<float*>(base + 256 + meta_b);
-    p.ws_acc = reinterpret_cast<float*>(base + 256 + meta_b + ml_b);
+    p.counters = reinterpret_cast<int*>(base + 256);
+    p.ws_ml = reinterpret_cast<float*>(base + 256 + cnt_b);
+    p.ws_acc = reinterpret_cast<float*>(base + 256 + cnt_b + ml_b);
     cudaError_t e = cudaMemsetAsync(base, 0, 256, cs);          // header must start at zero
     if (e != cudaSuccess) return cuda_fail("static scratch header clear failed", e);
 
     if (use_tc) {
         if ((rc = get_encode_fn())) return rc;
         CUtensorMap mk, mv;
+        p.box_rows = TILE;
+        p.box_shift = 6;
         if ((rc = encode_map(&mk, dtype, k, map_rows, dim, TILE))) return rc;
         if ((rc = encode_map(&mv, dtype, v, map_rows, dim, TILE))) return rc;
         if (dtype == BF16) launch_tc_t<__nv_bfloat16>(mk, mv, p, gp, false, cs);
         else launch_tc_t<__half>(mk, mv, p, gp, false, cs);
-        if ((rc = check_launch("attention split-KV tensor-core kernel launch"))) return rc;
-    } else {
-        if (dtype == F32) launch_simt_t<float>(p, lc, cs);
-        else if (dtype == BF16) launch_simt_t<__nv_bfloat16>(p, lc, cs);
-        else launch_simt_t<__half>(p, lc, cs);
-        if ((rc = check_launch("attention split-KV kernel launch"))) return rc;
+        return check_launch("attention split-KV tensor-core kernel launch");
     }
-    if (dtype == F32) launch_merge_t<float>(p, cs);
-    else if (dtype == BF16) launch_merge_t<__nv_bfloat16>(p, cs);
-    else launch_merge_t<__half>(p, cs);
-    return check_launch("attention merge kernel launch");
+    if (dtype == F32) launch_simt_t<float>(p, lc, cs);
+    else if (dtype == BF16) launch_simt_t<__nv_bfloat16>(p, lc, cs);
+    else launch_simt_t<__half>(p, lc, cs);
+    return check_launch("attention split-KV kernel launch");
 }
+
+#ifdef FTK_PROFILE
+// instrumented builds only: copy the per-CTA cycle counters of the last launch to the host
+int fusedtok_profile_read(long long* host, int n_ctas) {
+    if (!g_prof_buf) return 1;
+    cudaDeviceSynchronize();
+    return cudaMemcpy(host, g_prof_buf, (size_t)n_ctas * 16 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess;
+}
+#endif
 
 long long fusedtok_attention_launch_count(int reset) {
     const long long n = g_launches;

@@ -1,13 +1,10 @@
-// Log-sum-exp merge kernels: counterpart of the reference's attn_reduce_kernel
-// (src/attention.cu:478-549), with one warp per (sequence, query head) and no
-// redundant warps.
-//
-// merge_kernel folds the workspace slots a unit was split into (in CTA order,
-// with the reference's rule: partials with l <= 0 skipped, first live partial
-// adopted verbatim, later ones max-rescaled) and writes the normalised row -
-// or, for the multi-GPU layer, the merged raw triple.
-// merge_parts_kernel folds n whole-batch triples (one per GPU of a KV-length
-// split, as laid out by an all-gather) into the normalised output.
+// Cross-GPU log-sum-exp merge: merge_parts_kernel folds n whole-batch triples
+// (one per GPU of a KV-length split, as laid out by an all-gather) into the
+// normalised output, one warp per (sequence, query head), with the reference's
+// rule (attn_reduce_kernel, src/attention.cu:503-548): partials with l <= 0
+// skipped, first live partial adopted verbatim, later ones max-rescaled.
+// (Within one GPU the same fold runs inside the partial kernels: merge_unit in
+// common.cuh.)
 #pragma once
 
 #include "common.cuh"
@@ -16,83 +13,6 @@ namespace ftk {
 
 constexpr int MERGE_WARPS = 4;
 constexpr int MAX_LANE_CHUNKS = 4;      // head dim <= 512
-
-template <typename T>
-__global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const DecodeParams p) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long r = (long long)blockIdx.x * MERGE_WARPS + warp;
-    if (r >= (long long)p.B * p.Hq) return;
-    const int b = (int)(r / p.Hq), h = (int)(r % p.Hq);
-    if (seq_len(p, b) == 0) return;          // zero row already written by the partial kernel
-    const int kv = h / p.G, gi = h % p.G;
-    const int ch = gi / p.GC, g = gi % p.GC;
-    const long long unit = ((long long)b * p.Hkv + kv) * p.NCH + ch;
-    const int2 span = p.meta[unit];
-    if (span.x == span.y) return;            // finished in place by a single CTA
-    const int D = p.D, chunks = D >> 2;
-
-    float4 o[MAX_LANE_CHUNKS];
-#pragma unroll
-    for (int j = 0; j < MAX_LANE_CHUNKS; ++j) o[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-    float m = -INFINITY, l = 0.0f;
-    const long long total = *p.total_out;
-    for (int c = span.x; c <= span.y; ++c) {
-        // CTAs whose tile range is empty (more CTAs than tiles) wrote no slot
-        if ((total * c) / p.ncta == (total * (c + 1)) / p.ncta) continue;
-        const size_t pr = ((size_t)c + (size_t)unit) * p.GC + g;
-        const float2 ml = *reinterpret_cast<const float2*>(p.ws_ml + pr * 2);
-        if (ml.y <= 0.0f) continue;
-        const float* a = p.ws_acc + pr * D;
-        if (l == 0.0f) {
-            m = ml.x;
-            l = ml.y;
-#pragma unroll
-            for (int j = 0; j < MAX_LANE_CHUNKS; ++j) {
-                const int cc = lane + 32 * j;
-                if (cc < chunks) o[j] = *reinterpret_cast<const float4*>(a + cc * 4);
-            }
-            continue;
-        }
-        const float m_new = fmaxf(m, ml.x);
-        const float r_old = expf(m - m_new), r_new = expf(ml.x - m_new);
-        l = l * r_old + ml.y * r_new;
-#pragma unroll
-        for (int j = 0; j < MAX_LANE_CHUNKS; ++j) {
-            const int cc = lane + 32 * j;
-            if (cc < chunks) {
-                const float4 x = *reinterpret_cast<const float4*>(a + cc * 4);
-                o[j].x = o[j].x * r_old + x.x * r_new;
-                o[j].y = o[j].y * r_old + x.y * r_new;
-                o[j].z = o[j].z * r_old + x.z * r_new;
-                o[j].w = o[j].w * r_old + x.w * r_new;
-            }
-        }
-        m = m_new;
-    }
-    const size_t row = (size_t)b * p.Hq + h;
-    if (p.triple_ml) {
-        if (lane == 0) {
-            p.triple_ml[row * 2] = m;
-            p.triple_ml[row * 2 + 1] = l;
-        }
-#pragma unroll
-        for (int j = 0; j < MAX_LANE_CHUNKS; ++j) {
-            const int cc = lane + 32 * j;
-            if (cc < chunks) *reinterpret_cast<float4*>(p.triple_acc + row * D + cc * 4) = o[j];
-        }
-        return;
-    }
-    T* out = reinterpret_cast<T*>(p.out) + row * D;
-#pragma unroll
-    for (int j = 0; j < MAX_LANE_CHUNKS; ++j) {
-        const int cc = lane + 32 * j;
-        if (cc < chunks) {
-            float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (l > 0.0f) y = make_float4(o[j].x / l, o[j].y / l, o[j].z / l, o[j].w / l);
-            Store<T>::st4(out + cc * 4, y);
-        }
-    }
-}
 
 // parts: n blocks of [rows*2 (m,l), padded to a multiple of 4 | rows*D acc] floats, rows = B*Hq.
 template <typename T>

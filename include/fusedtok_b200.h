@@ -130,8 +130,9 @@ int fusedtok_attention_merge_partials_launch(int dtype, const float* partials, i
  * a fixed 4 MiB array inside the library image, held by every GPU that loads
  * the library until the process exits. Calls no cudaMalloc / cudaFree and no
  * allocating library routine. Shapes whose scratch would exceed 4 MiB
- * ((batch*kv_heads*chunks + CTAs) * heads_per_chunk * (dim + 2) floats, plus
- * 8 bytes per unit) are rejected with FUSEDTOK_INVALID_ARGUMENT. The first call
+ * (64 KiB of counters + (batch*kv_heads*chunks + CTAs) * heads_per_chunk *
+ * (dim + 2) floats), or with more than 16384 (sequence, kv head, chunk) units,
+ * are rejected with FUSEDTOK_INVALID_ARGUMENT. The first call
  * on a device looks up the array's device address and sets kernel attributes:
  * make it before any stream capture. All calls on a device share the array;
  * calls that overlap on the GPU race on it. */
