@@ -61,9 +61,6 @@ struct DecodeParams {
     int box_rows, box_shift;   // rows per TMA box (a power of two) and its log2 (tensor-core kernel)
     int ncta;
     float scale;          // 1/sqrt(D)
-#ifdef FTK_PROFILE
-    long long* prof;      // per-CTA cycle counters (instrumented builds only)
-#endif
 };
 
 // Float offset of the acc block inside a triple buffer of `rows` (b, h) rows:

@@ -166,6 +166,13 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+// Transpose an 8x8 matrix of 16-bit elements held one row pair per thread
+// (row = lane / 4, columns 2 * (lane % 4) + {0, 1}) across the warp.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
 __device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory"); }
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -204,14 +211,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
     __syncthreads();
 
-#ifdef FTK_PROFILE
-    const long long prof_t0 = clock64();
-    long long prof_wait = 0, prof_epi = 0, prof_first = 0, prof_qk = 0, prof_sm = 0, prof_pv = 0, prof_segb = 0;
-#endif
     Walker w;
     if (!sched_init<T>(p, sh, w)) return;      // block-uniform
     const long long total = sh->total;
-    const long long g_begin = w.g;
     const int upb_nch = p.NCH;
 
     if (warp == NCW) {
@@ -225,14 +227,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         int s = 0;                 // ring stage of tile i
         uint32_t ph = 0;           // phase parity of that stage's current use
         for (int i = 0; w.g < w.end; ++i) {
-#ifdef FTK_PROFILE
-            const long long tw0 = clock64();
-#endif
             const bool ok = mbar_wait(bar_empty + s * 8, ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY_TIMEOUT);
-#ifdef FTK_PROFILE
-            prof_wait += clock64() - tw0;
-            if (i == 0) prof_first = clock64() - prof_t0;
-#endif
             if (!ok) break;
             const int kv = w.ub / upb_nch;
             const uint32_t dst_k = smem_base + s * Cfg::STAGE_BYTES;
@@ -277,12 +272,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             walker_advance(p, w);
             if (++s == Cfg::NS) { s = 0; ph ^= 1u; }
         }
-#ifdef FTK_PROFILE
-        if (lane == 0 && p.prof) {
-            long long* o = p.prof + (size_t)blockIdx.x * 16;
-            o[4] = prof_wait; o[5] = prof_first; o[6] = clock64() - prof_t0; o[7] = issued;
-        }
-#endif
         // If something went wrong, do not leave the CTA while our own copies
         // may still be landing in its shared memory: wait (bounded) for the
         // last phase of every stage that was issued.
@@ -302,6 +291,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
 
     // ======================= consumer warps =======================
+    // Tokens are the M dimension of the MMA and query heads the N dimension
+    // (8 per block): S^T[16 rows x 8 heads] = K[16 x D] . Q^T[D x 8] and
+    // O^T[D x 8 heads] += V^T[D x 16 rows] . P^T[16 rows x 8 heads]. With up to
+    // 8 heads per unit that is D/16 + D/16 MMAs per 16 cache rows - half of
+    // what heads-on-M costs - which matters because the legacy mma.sync pipe is
+    // the scarce compute resource of this kernel on sm_100.
     const int cg = warp >> 2;           // consumer group: takes every other tile
     const int wr = warp & 3;            // 16-row block of the tile
     const int quad = lane >> 2, qi = lane & 3;
@@ -311,12 +306,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     float2* s_ml = reinterpret_cast<float2*>(smem + Cfg::OFF_ML);
     float* s_scale = reinterpret_cast<float*>(smem + Cfg::OFF_SCALE);
     float2* s_glob = reinterpret_cast<float2*>(smem + Cfg::OFF_GLOB);
+    volatile int* s_last = abort_flag + 1;
 
-    constexpr int KSTEPS = D / 16;
-    constexpr int NB = D / 8;
-    uint32_t qa[KSTEPS][GP == 16 ? 4 : 2];
-    float acc[NB][4];
-    float m_run[2], l_run[2];
+    constexpr int KSTEPS = D / 16;      // k-steps of S^T = K Q^T
+    constexpr int MT = D / 16;          // 16-row m-tiles of O^T = V^T P^T
+    constexpr int NBK = GP / 8;         // 8-head blocks
+    uint32_t qb[NBK][KSTEPS][2];        // Q^T as B fragments: head 8*nbk + quad, d = 16*kk + 2*qi + {0,1} (+8)
+    float acc[NBK][MT][4];              // O^T: d = 16*mt + quad (+8 for [2],[3]); head 8*nbk + 2*qi + {0,1}
+    float m_run[NBK][2], l_run[NBK][2]; // per head 8*nbk + 2*qi + e; l is this thread's share until the epilogue
     long long seg_first = w.g;
 
     // Stage layout: boxes of `box_rows` rows back to back; inside a box the
@@ -327,69 +324,45 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     auto row_off = [&](int r) -> uint32_t {
         return (uint32_t)(r >> box_shift) * (uint32_t)(box_rows * D * 2) + (uint32_t)(r & (box_rows - 1)) * 128u;
     };
-    // per-lane ldmatrix row geometry (constant over the kernel)
+    // per-lane ldmatrix geometry (constant over the kernel)
     const int lrow = lane & 7, lmat = lane >> 3;
-    // K (non-transposed): matrices (rows 0-7, chunk c), (rows 0-7, c+1), (rows 8-15, c), (rows 8-15, c+1)
-    const uint32_t k_off = row_off(wr * 16 + (lmat >> 1) * 8 + lrow);
-    const int k_csel = lmat & 1;
-    // V (transposed): matrices (rows 0-7, chunk c), (rows 8-15, c), (rows 0-7, c+1), (rows 8-15, c+1)
-    const uint32_t v_off = row_off(wr * 16 + (lmat & 1) * 8 + lrow);
-    const int v_csel = lmat >> 1;
+    // K as the A operand: matrices (rows 0-7, chunk c), (rows 8-15, c), (rows 0-7, c+1), (rows 8-15, c+1)
+    const uint32_t k_off = row_off(wr * 16 + (lmat & 1) * 8 + lrow);
+    const int k_csel = lmat >> 1;
+    // V^T as the A operand (transposing load): (rows 0-7, chunk c), (rows 0-7, c+1), (rows 8-15, c), (rows 8-15, c+1)
+    const uint32_t v_off = row_off(wr * 16 + (lmat >> 1) * 8 + lrow);
+    const int v_csel = lmat & 1;
 
-#ifdef FTK_PROFILE
-    long long prof_own = 0, prof_other = 0;
-#endif
-    int s = 0;                     // ring stage of tile i
-    uint32_t ph = 0;               // phase parity of that stage's current use
+    int s = 0;                          // ring stage of tile i
+    uint32_t ph = 0;                    // phase parity of that stage's current use
     for (int i = 0; w.g < w.end; ++i) {
-#ifdef FTK_PROFILE
-        const long long ti0 = clock64();
-#endif
         if (i == 0 || w.ti == 0) {
-            // ---- segment begins: fetch the group's query rows as MMA A fragments
-#ifdef FTK_PROFILE
-            const long long tb0 = clock64();
-#endif
+            // ---- segment begins: fetch the unit's query rows as MMA B fragments
             seg_first = w.g;
             const int kv = w.ub / upb_nch, ch = w.ub % upb_nch;
             const int gvalid = min(p.GC, p.G - ch * p.GC);
-            const T* qb = reinterpret_cast<const T*>(p.q) + ((size_t)w.b * p.Hq + kv * p.G + ch * p.GC) * D;
+            const T* qbase = reinterpret_cast<const T*>(p.q) + ((size_t)w.b * p.Hq + kv * p.G + ch * p.GC) * D;
 #pragma unroll
-            for (int kk = 0; kk < KSTEPS; ++kk) {
-                const int d0 = kk * 16 + qi * 2;
-                const bool lo_ok = quad < gvalid;
-                qa[kk][0] = lo_ok ? *reinterpret_cast<const uint32_t*>(qb + (size_t)quad * D + d0) : 0u;
-                qa[kk][GP == 16 ? 2 : 1] = lo_ok ? *reinterpret_cast<const uint32_t*>(qb + (size_t)quad * D + d0 + 8) : 0u;
-                if constexpr (GP == 16) {
-                    const bool hi_ok = quad + 8 < gvalid;
-                    qa[kk][1] = hi_ok ? *reinterpret_cast<const uint32_t*>(qb + (size_t)(quad + 8) * D + d0) : 0u;
-                    qa[kk][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(qb + (size_t)(quad + 8) * D + d0 + 8) : 0u;
+            for (int nbk = 0; nbk < NBK; ++nbk) {
+                const int head = nbk * 8 + quad;
+                const bool live = head < gvalid;
+                const T* qrow = qbase + (size_t)head * D + qi * 2;
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    qb[nbk][kk][0] = live ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16) : 0u;
+                    qb[nbk][kk][1] = live ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + 8) : 0u;
                 }
-            }
 #pragma unroll
-            for (int nb = 0; nb < NB; ++nb) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.0f;
-            m_run[0] = m_run[1] = -INFINITY;
-            l_run[0] = l_run[1] = 0.0f;
-#ifdef FTK_PROFILE
-            prof_segb += clock64() - tb0;
-#endif
+                for (int mt = 0; mt < MT; ++mt) acc[nbk][mt][0] = acc[nbk][mt][1] = acc[nbk][mt][2] = acc[nbk][mt][3] = 0.0f;
+                m_run[nbk][0] = m_run[nbk][1] = -INFINITY;
+                l_run[nbk][0] = l_run[nbk][1] = 0.0f;
+            }
         }
 
         if ((i & 1) == cg) {
-#ifdef FTK_PROFILE
-            const long long tw0 = clock64();
-#endif
             const bool ok = mbar_wait(bar_full + s * 8, ph, abort_flag, p.status, ST_WAIT_FULL_TIMEOUT);
-#ifdef FTK_PROFILE
-            prof_wait += clock64() - tw0;
-            if (i < 2) prof_first = clock64() - prof_t0;
-#endif
             const int rows_valid = w.len - w.ti * TILE;      // >= 1
-#ifdef FTK_EXP_NOCOMPUTE
-            if (false) {
-#else
             if (ok && wr * 16 < rows_valid) {
-#endif
                 const uint32_t st_k = smem_base + s * Cfg::STAGE_BYTES;
                 const uint32_t st_v = st_k + Cfg::KV_BYTES;
                 const bool ragged = rows_valid < wr * 16 + 16;
@@ -405,120 +378,107 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                 }
-#ifdef FTK_PROFILE
-                const long long tq0 = clock64();
-#endif
-                // ---- S = Q K^T for 16 cache rows (two n-blocks of 8)
-                float sa[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-                float sb[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                // ---- S^T = K Q^T for 16 cache rows; even / odd k-steps in separate accumulators
+                float sa[NBK][4], sb[NBK][4];
+#pragma unroll
+                for (int nbk = 0; nbk < NBK; ++nbk)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sa[nbk][e] = sb[nbk][e] = 0.0f;
 #pragma unroll
                 for (int kk = 0; kk < KSTEPS; ++kk) {
                     const int chunk = kk * 2 + k_csel;
                     const uint32_t addr = st_k + k_off + (chunk >> 3) * half_stride + (((chunk & 7) ^ lrow) << 4);
-                    uint32_t r0, r1, r2, r3;
-                    ldsm_x4(addr, r0, r1, r2, r3);
-                    const uint32_t a0 = qa[kk][0];
-                    const uint32_t a1 = (GP == 16) ? qa[kk][1] : 0u;
-                    const uint32_t a2 = qa[kk][GP == 16 ? 2 : 1];
-                    const uint32_t a3 = (GP == 16) ? qa[kk][GP == 16 ? 3 : 1] : 0u;
-                    if (kk & 1) {
-                        mma16816<T>(sb[0], a0, a1, a2, a3, r0, r1);
-                        mma16816<T>(sb[1], a0, a1, a2, a3, r2, r3);
-                    } else {
-                        mma16816<T>(sa[0], a0, a1, a2, a3, r0, r1);
-                        mma16816<T>(sa[1], a0, a1, a2, a3, r2, r3);
+                    uint32_t a0, a1, a2, a3;
+                    ldsm_x4(addr, a0, a1, a2, a3);
+#pragma unroll
+                    for (int nbk = 0; nbk < NBK; ++nbk) {
+                        if (kk & 1) mma16816<T>(sb[nbk], a0, a1, a2, a3, qb[nbk][kk][0], qb[nbk][kk][1]);
+                        else mma16816<T>(sa[nbk], a0, a1, a2, a3, qb[nbk][kk][0], qb[nbk][kk][1]);
                     }
                 }
-                // ---- online softmax (log2 domain), rows `quad` and `quad + 8`
-                float sc[2][4];
-#ifdef FTK_PROFILE
-                const long long tq1 = clock64();
-                prof_qk += tq1 - tq0;
-#endif
+                // ---- online softmax (log2 domain). This thread holds, for heads 8*nbk + 2*qi + e,
+                // the scores of rows `quad` ([e]) and `quad + 8` ([2 + e]) of the block.
+                const int r_lo = wr * 16 + quad;
+                uint32_t pb[NBK][2];
 #pragma unroll
-                for (int nb = 0; nb < 2; ++nb)
+                for (int nbk = 0; nbk < NBK; ++nbk) {
+                    float plo[2], phi[2];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) sc[nb][e] = (sa[nb][e] + sb[nb][e]) * sl2;
-                if (ragged) {
-#pragma unroll
-                    for (int nb = 0; nb < 2; ++nb)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int r = wr * 16 + nb * 8 + qi * 2 + (e & 1);
-                            if (r >= rows_valid) sc[nb][e] = -INFINITY;
+                    for (int e = 0; e < 2; ++e) {
+                        float v0 = (sa[nbk][e] + sb[nbk][e]) * sl2;
+                        float v1 = (sa[nbk][2 + e] + sb[nbk][2 + e]) * sl2;
+                        if (ragged) {
+                            if (r_lo >= rows_valid) v0 = -INFINITY;
+                            if (r_lo + 8 >= rows_valid) v1 = -INFINITY;
                         }
-                }
-                uint32_t pa[4];
+                        float mx = fmaxf(v0, v1);
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                        const float m_new = fmaxf(m_run[nbk][e], mx);
+                        const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+                        const float alpha = ex2(m_run[nbk][e] - m_safe);
+                        plo[e] = ex2(v0 - m_safe);
+                        phi[e] = ex2(v1 - m_safe);
+                        l_run[nbk][e] = l_run[nbk][e] * alpha + (plo[e] + phi[e]);
+                        m_run[nbk][e] = m_new;
+                        if (alpha != 1.0f) {
 #pragma unroll
-                for (int hh = 0; hh < (GP == 16 ? 2 : 1); ++hh) {
-                    float mx = fmaxf(fmaxf(sc[0][2 * hh], sc[0][2 * hh + 1]), fmaxf(sc[1][2 * hh], sc[1][2 * hh + 1]));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                    const float m_new = fmaxf(m_run[hh], mx);
-                    const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
-                    const float alpha = ex2(m_run[hh] - m_safe);
-                    const float p00 = ex2(sc[0][2 * hh] - m_safe), p01 = ex2(sc[0][2 * hh + 1] - m_safe);
-                    const float p10 = ex2(sc[1][2 * hh] - m_safe), p11 = ex2(sc[1][2 * hh + 1] - m_safe);
-                    l_run[hh] = l_run[hh] * alpha + ((p00 + p01) + (p10 + p11));
-                    m_run[hh] = m_new;
-                    pa[hh] = pack2<T>(p00, p01);          // A regs: rows quad (+8), k 0-7
-                    pa[hh + 2] = pack2<T>(p10, p11);      //                         k 8-15
-                    if (alpha != 1.0f) {
-#pragma unroll
-                        for (int nb = 0; nb < NB; ++nb) {
-                            acc[nb][2 * hh] *= alpha;
-                            acc[nb][2 * hh + 1] *= alpha;
+                            for (int mt = 0; mt < MT; ++mt) {
+                                acc[nbk][mt][e] *= alpha;
+                                acc[nbk][mt][2 + e] *= alpha;
+                            }
                         }
                     }
+                    // P^T as the B operand: transpose the two 8x8 blocks (rows 0-7 / 8-15 of the block)
+                    pb[nbk][0] = movmatrix_trans(pack2<T>(plo[0], plo[1]));
+                    pb[nbk][1] = movmatrix_trans(pack2<T>(phi[0], phi[1]));
                 }
-                if constexpr (GP == 8) { pa[1] = 0u; pa[3] = 0u; }
-#ifdef FTK_PROFILE
-                const long long tq2 = clock64();
-                prof_sm += tq2 - tq1;
-#endif
-                // ---- O += P V
+                // ---- O^T += V^T P^T
 #pragma unroll
-                for (int c = 0; c < NB; c += 2) {
-                    const int chunk = c + v_csel;
+                for (int mt = 0; mt < MT; ++mt) {
+                    const int chunk = mt * 2 + v_csel;
                     const uint32_t addr = st_v + v_off + (chunk >> 3) * half_stride + (((chunk & 7) ^ lrow) << 4);
-                    uint32_t r0, r1, r2, r3;
-                    ldsm_x4_t(addr, r0, r1, r2, r3);
-                    mma16816<T>(acc[c], pa[0], pa[1], pa[2], pa[3], r0, r1);
-                    mma16816<T>(acc[c + 1], pa[0], pa[1], pa[2], pa[3], r2, r3);
+                    uint32_t a0, a1, a2, a3;
+                    ldsm_x4_t(addr, a0, a1, a2, a3);
+#pragma unroll
+                    for (int nbk = 0; nbk < NBK; ++nbk)
+                        mma16816<T>(acc[nbk][mt], a0, a1, a2, a3, pb[nbk][0], pb[nbk][1]);
                 }
-#ifdef FTK_PROFILE
-                prof_pv += clock64() - tq2;
-#endif
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + s * 8);
         }
 
-#ifdef FTK_PROFILE
-        if ((i & 1) == cg) prof_own += clock64() - ti0; else prof_other += clock64() - ti0;
-#endif
         const bool seg_end = (w.ti == w.nt - 1) || (w.g + 1 == w.end);
         if (seg_end) {
             // ---- fold the 8 warp states and emit
-#ifdef FTK_PROFILE
-            const long long te0 = clock64();
-#endif
             const SegDest dst = seg_dest(p, w, total, seg_first);
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
-                l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
-            }
+            for (int nbk = 0; nbk < NBK; ++nbk)
 #pragma unroll
-            for (int hh = 0; hh < (GP == 16 ? 2 : 1); ++hh) {
+                for (int e = 0; e < 2; ++e) {
+                    float l = l_run[nbk][e];
+                    l += __shfl_xor_sync(0xffffffffu, l, 4);
+                    l += __shfl_xor_sync(0xffffffffu, l, 8);
+                    l += __shfl_xor_sync(0xffffffffu, l, 16);
+                    l_run[nbk][e] = l;
+                }
+            const int tc = warp * 32 + lane;
+#pragma unroll
+            for (int hh = 0; hh < NBK; ++hh) {
                 bar_consumers();                                   // scratch is free again
-                float* my = s_acc + ((size_t)warp * 8 + quad) * Cfg::ACC_STRIDE + qi * 2;
 #pragma unroll
-                for (int nb = 0; nb < NB; ++nb)
-                    *reinterpret_cast<float2*>(my + nb * 8) = make_float2(acc[nb][2 * hh], acc[nb][2 * hh + 1]);
-                if (qi == 0) s_ml[warp * 8 + quad] = make_float2(m_run[hh], l_run[hh]);
+                for (int e = 0; e < 2; ++e) {
+                    float* my = s_acc + ((size_t)warp * 8 + qi * 2 + e) * Cfg::ACC_STRIDE + quad;
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        my[mt * 16] = acc[hh][mt][e];
+                        my[mt * 16 + 8] = acc[hh][mt][2 + e];
+                    }
+                    if (quad == 0) s_ml[warp * 8 + qi * 2 + e] = make_float2(m_run[hh][e], l_run[hh][e]);
+                }
                 bar_consumers();
-                const int tc = warp * 32 + lane;
                 if (tc < NCW * 8) {
                     const int row = tc & 7;
                     float mg = -INFINITY;
@@ -562,31 +522,17 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 // publish the partial; the CTA that publishes a unit's last one merges it
                 __threadfence();
                 bar_consumers();
-                volatile int* s_last = abort_flag + 1;
-                if (warp == 0 && lane == 0) *s_last = deliver_partial(p, dst) ? 1 : 0;
+                if (tc == 0) *s_last = deliver_partial(p, dst) ? 1 : 0;
                 bar_consumers();
                 if (*s_last) {
                     __threadfence();
-                    merge_unit<T>(p, dst, total, warp * 32 + lane, NCW * 32);
+                    merge_unit<T>(p, dst, total, tc, NCW * 32);
                 }
             }
-#ifdef FTK_PROFILE
-            prof_epi += clock64() - te0;
-#endif
         }
         walker_advance(p, w);
         if (++s == Cfg::NS) { s = 0; ph ^= 1u; }
     }
-#ifdef FTK_PROFILE
-    if (warp < 2 && lane == 0 && p.prof) {      // warp 0: group 0, warp 4 would be group 1; record warp 0 only
-        if (warp == 0) {
-            long long* o = p.prof + (size_t)blockIdx.x * 16;
-            o[0] = clock64() - prof_t0; o[1] = prof_first; o[2] = prof_wait; o[3] = prof_epi;
-            o[8] = prof_qk; o[9] = prof_sm; o[10] = prof_pv; o[11] = prof_segb; o[12] = prof_own; o[13] = prof_other;
-        }
-    }
-#endif
-    (void)g_begin;
 }
 
 }  // namespace ftk

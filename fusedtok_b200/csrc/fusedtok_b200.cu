@@ -26,9 +26,6 @@ namespace {
 
 using namespace ftk;
 
-#ifdef FTK_PROFILE
-long long* g_prof_buf = nullptr;
-#endif
 thread_local std::string g_err;
 thread_local long long g_launches = 0;
 
@@ -320,14 +317,6 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
     rc = get_arena(*dev, cs, (size_t)units, p.ncta, p.GC, dim, use_tc, &a);
     if (rc) return rc;
     p.ws_ml = a.ws_ml; p.ws_acc = a.ws_acc; p.counters = a.counters; p.status = a.status;
-#ifdef FTK_PROFILE
-    {
-        static long long* prof_buf = nullptr;
-        if (!prof_buf) { cudaMalloc(&prof_buf, 1024 * 16 * sizeof(long long)); cudaMemset(prof_buf, 0, 1024 * 16 * sizeof(long long)); }
-        p.prof = prof_buf;
-        g_prof_buf = prof_buf;
-    }
-#endif
 
     if (use_tc) {
         rc = get_encode_fn();
@@ -720,14 +709,6 @@ int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const voi
     return check_launch("attention split-KV kernel launch");
 }
 
-#ifdef FTK_PROFILE
-// instrumented builds only: copy the per-CTA cycle counters of the last launch to the host
-int fusedtok_profile_read(long long* host, int n_ctas) {
-    if (!g_prof_buf) return 1;
-    cudaDeviceSynchronize();
-    return cudaMemcpy(host, g_prof_buf, (size_t)n_ctas * 16 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess;
-}
-#endif
 
 long long fusedtok_attention_launch_count(int reset) {
     const long long n = g_launches;
