@@ -141,6 +141,8 @@ def make_lens(w, batch):
         return cases.config3_lens(batch)
     if kind == "loguniform":
         return cases.config5_lens(batch)
+    if kind == "full" or (kind is None and w["paged"]):
+        return np.full(batch, w["T"], np.int32)
     return None
 
 

@@ -54,7 +54,11 @@ template <int D> struct TcCfg {
     // order. With an odd depth a group would wait on a stage it did not
     // consume the previous time round, and a parity wait cannot tell "not
     // filled yet" from "filled twice since".
+#ifdef FTK_NS
+    static constexpr int NS = FTK_NS;
+#else
     static constexpr int NS = (D == 128) ? 6 : 8;
+#endif
     static_assert(NS % 2 == 0, "ring depth must be even (see above)");
     static constexpr int ACC_STRIDE = D + 4;           // floats; rows stay 16-byte aligned
     static constexpr int SCRATCH_BYTES = NCW * 8 * ACC_STRIDE * 4;
@@ -98,10 +102,36 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait. Returns false when the limit expired or another warp already
 // gave up; the caller then carries on without the data.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
+#ifdef FTK_SPIN_TEST_WAIT
+    if (mbar_test_wait(bar, parity)) return true;
+    const long long c0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((it & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - c0 > 6000000000ll) {
+                *abort_flag = 1;
+                atomicCAS(status, ST_OK, code);
+                return false;
+            }
+        }
+    }
+#else
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (uint32_t it = 1;; ++it) {
@@ -115,6 +145,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             }
         }
     }
+#endif
 }
 __device__ __forceinline__ uint64_t policy_evict_first() {
     uint64_t pol;
@@ -233,6 +264,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             const uint32_t dst_k = smem_base + s * Cfg::STAGE_BYTES;
             const uint32_t dst_v = dst_k + Cfg::KV_BYTES;
             const uint32_t fb = bar_full + s * 8;
+#ifdef FTK_EXP_NOLOAD
+            if (lane == 0) mbar_arrive(fb);
+            if (false) {
+#else
+            {
+#endif
             if constexpr (!PAGED) {
                 if (lane == 0) {
                     const int row = (w.b * p.Hkv + kv) * p.T + w.ti * TILE;
@@ -268,6 +305,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     tma_load_rows(dst_v, &tm_v, row, fb, pol);
                 }
             }
+            }
             ++issued;
             walker_advance(p, w);
             if (++s == Cfg::NS) { s = 0; ph ^= 1u; }
@@ -300,7 +338,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const int cg = warp >> 2;           // consumer group: takes every other tile
     const int wr = warp & 3;            // 16-row block of the tile
     const int quad = lane >> 2, qi = lane & 3;
-    const float sl2 = p.scale * LOG2E;  // scores are kept in log2 units
+    const float sl2 = p.scale * LOG2E;  // raw score differences -> ex2 arguments
 
     float* s_acc = reinterpret_cast<float*>(smem + Cfg::OFF_SCRATCH);
     float2* s_ml = reinterpret_cast<float2*>(smem + Cfg::OFF_ML);
@@ -328,17 +366,134 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const int lrow = lane & 7, lmat = lane >> 3;
     // K as the A operand: matrices (rows 0-7, chunk c), (rows 8-15, c), (rows 0-7, c+1), (rows 8-15, c+1)
     const uint32_t k_off = row_off(wr * 16 + (lmat & 1) * 8 + lrow);
-    const int k_csel = lmat >> 1;
+    const int k_x = (lmat >> 1) ^ lrow;          // (chunk + csel) ^ lrow == chunk ^ (csel ^ lrow) for even chunk
     // V^T as the A operand (transposing load): (rows 0-7, chunk c), (rows 0-7, c+1), (rows 8-15, c), (rows 8-15, c+1)
     const uint32_t v_off = row_off(wr * 16 + (lmat >> 1) * 8 + lrow);
-    const int v_csel = lmat & 1;
+    const int v_x = (lmat & 1) ^ lrow;
 
-    int s = 0;                          // ring stage of tile i
-    uint32_t ph = 0;                    // phase parity of that stage's current use
-    for (int i = 0; w.g < w.end; ++i) {
-        if (i == 0 || w.ti == 0) {
-            // ---- segment begins: fetch the unit's query rows as MMA B fragments
-            seg_first = w.g;
+    // One loop iteration per SEGMENT; inside, a tight loop over the tiles of
+    // the segment that belong to this consumer group (every other tile). The
+    // ring depth is even, so the stage of an own tile advances by 2 and keeps
+    // its parity; `own` is the CTA-local index of this group's next tile.
+    const float neg_inf = -INFINITY;
+    int i0 = 0;                         // CTA-local index of the segment's first tile
+    int own = cg;                       // next own tile (CTA-local index), always == cg (mod 2)
+    int s = cg;                         // its ring stage ...
+    uint32_t ph = 0;                    // ... and the phase parity of that stage's current use
+
+    // QK^T, online softmax and PV for this warp's 16 rows of the tile in stage `s`.
+    auto process = [&](auto ragged_tag, int rows_valid) {
+        constexpr bool RAGGED = decltype(ragged_tag)::value;
+        const uint32_t st_k = smem_base + s * Cfg::STAGE_BYTES;
+        const uint32_t st_v = st_k + Cfg::KV_BYTES;
+        if constexpr (RAGGED) {
+            // rows at and past the sequence end may hold anything (stale or
+            // foreign data): clear the V rows so that a zero weight times
+            // their contents stays zero
+            if (rows_valid < wr * 16 + 16) {
+                uint8_t* vb = smem + s * Cfg::STAGE_BYTES + Cfg::KV_BYTES;
+                for (int r = rows_valid; r < wr * 16 + 16; ++r)
+                    for (int h = 0; h < Cfg::NH; ++h)
+                        if (lane < 8)
+                            *reinterpret_cast<uint4*>(vb + row_off(r) + h * half_stride + lane * 16) = make_uint4(0, 0, 0, 0);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+            }
+        }
+        // Shared-memory fragment loads are issued a few steps ahead of the MMAs
+        // that use them (the asm statements keep source order, so the order
+        // below IS the schedule): PF fragments of K up front, the rest as the
+        // MMAs free them; the first PF fragments of V before the softmax, whose
+        // latency then hides theirs.
+        constexpr int PF = 4;
+        auto k_addr = [&](int kk) -> uint32_t {
+            const int chunk = kk * 2;       // k_csel is folded into k_x
+            return st_k + k_off + (chunk >> 3) * half_stride + ((uint32_t)((chunk & 7) ^ k_x) << 4);
+        };
+        auto v_addr = [&](int mt) -> uint32_t {
+            const int chunk = mt * 2;
+            return st_v + v_off + (chunk >> 3) * half_stride + ((uint32_t)((chunk & 7) ^ v_x) << 4);
+        };
+        uint32_t fk[PF][4], fv[PF][4];
+#pragma unroll
+        for (int j = 0; j < PF; ++j) ldsm_x4(k_addr(j), fk[j][0], fk[j][1], fk[j][2], fk[j][3]);
+        // ---- S^T = K Q^T; even / odd k-steps in separate accumulators
+        float sa[NBK][4], sb[NBK][4];
+#pragma unroll
+        for (int nbk = 0; nbk < NBK; ++nbk)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sa[nbk][e] = sb[nbk][e] = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            uint32_t (&f)[4] = fk[kk % PF];
+#pragma unroll
+            for (int nbk = 0; nbk < NBK; ++nbk) {
+                if (kk & 1) mma16816<T>(sb[nbk], f[0], f[1], f[2], f[3], qb[nbk][kk][0], qb[nbk][kk][1]);
+                else mma16816<T>(sa[nbk], f[0], f[1], f[2], f[3], qb[nbk][kk][0], qb[nbk][kk][1]);
+            }
+            if (kk + PF < KSTEPS) ldsm_x4(k_addr(kk + PF), f[0], f[1], f[2], f[3]);
+        }
+#pragma unroll
+        for (int j = 0; j < PF; ++j) ldsm_x4_t(v_addr(j), fv[j][0], fv[j][1], fv[j][2], fv[j][3]);
+        // ---- online softmax. This thread holds, for heads 8*nbk + 2*qi + e, the raw
+        // scores of rows `quad` ([e]) and `quad + 8` ([2 + e]) of the block. m_run is
+        // kept in raw score units; sl2 = scale * log2(e) turns differences into ex2 arguments.
+        const int r_lo = wr * 16 + quad;
+        uint32_t pb[NBK][2];
+#pragma unroll
+        for (int nbk = 0; nbk < NBK; ++nbk) {
+            float plo[2], phi[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float v0 = sa[nbk][e] + sb[nbk][e];
+                float v1 = sa[nbk][2 + e] + sb[nbk][2 + e];
+                if constexpr (RAGGED) {
+                    if (r_lo >= rows_valid) v0 = neg_inf;
+                    if (r_lo + 8 >= rows_valid) v1 = neg_inf;
+                }
+                float mx = fmaxf(v0, v1);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                const float m_old = m_run[nbk][e];
+                const float m_new = fmaxf(m_old, mx);
+                const float m_safe = (m_new == neg_inf) ? 0.0f : m_new;
+                const float ms = -m_safe * sl2;
+                const float alpha = ex2(fmaf(m_old, sl2, ms));
+                plo[e] = ex2(fmaf(v0, sl2, ms));
+                phi[e] = ex2(fmaf(v1, sl2, ms));
+                l_run[nbk][e] = fmaf(l_run[nbk][e], alpha, plo[e] + phi[e]);
+                m_run[nbk][e] = m_new;
+                if (m_new != m_old) {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        acc[nbk][mt][e] *= alpha;
+                        acc[nbk][mt][2 + e] *= alpha;
+                    }
+                }
+            }
+            // P^T as the B operand: transpose the two 8x8 blocks (rows 0-7 / 8-15 of the block)
+            pb[nbk][0] = movmatrix_trans(pack2<T>(plo[0], plo[1]));
+            pb[nbk][1] = movmatrix_trans(pack2<T>(phi[0], phi[1]));
+        }
+        // ---- O^T += V^T P^T
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            uint32_t (&f)[4] = fv[mt % PF];
+#pragma unroll
+            for (int nbk = 0; nbk < NBK; ++nbk)
+                mma16816<T>(acc[nbk][mt], f[0], f[1], f[2], f[3], pb[nbk][0], pb[nbk][1]);
+            if (mt + PF < MT) ldsm_x4_t(v_addr(mt + PF), f[0], f[1], f[2], f[3]);
+        }
+    };
+
+    while (w.g < w.end) {
+        // ---- segment begins: its tiles are local indices [i0, i0 + n)
+        const long long left = w.end - w.g;
+        const int n = (int)(left < (long long)(w.nt - w.ti) ? left : (long long)(w.nt - w.ti));
+        seg_first = w.g;
+        {
+            // the unit's query rows as MMA B fragments
             const int kv = w.ub / upb_nch, ch = w.ub % upb_nch;
             const int gvalid = min(p.GC, p.G - ch * p.GC);
             const T* qbase = reinterpret_cast<const T*>(p.q) + ((size_t)w.b * p.Hq + kv * p.G + ch * p.GC) * D;
@@ -354,104 +509,28 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) acc[nbk][mt][0] = acc[nbk][mt][1] = acc[nbk][mt][2] = acc[nbk][mt][3] = 0.0f;
-                m_run[nbk][0] = m_run[nbk][1] = -INFINITY;
+                m_run[nbk][0] = m_run[nbk][1] = neg_inf;
                 l_run[nbk][0] = l_run[nbk][1] = 0.0f;
             }
         }
-
-        if ((i & 1) == cg) {
+        // ---- this group's tiles of the segment
+        for (; own < i0 + n; own += 2) {
             const bool ok = mbar_wait(bar_full + s * 8, ph, abort_flag, p.status, ST_WAIT_FULL_TIMEOUT);
-            const int rows_valid = w.len - w.ti * TILE;      // >= 1
-            if (ok && wr * 16 < rows_valid) {
-                const uint32_t st_k = smem_base + s * Cfg::STAGE_BYTES;
-                const uint32_t st_v = st_k + Cfg::KV_BYTES;
-                const bool ragged = rows_valid < wr * 16 + 16;
-                if (ragged) {
-                    // rows at and past the sequence end may hold anything
-                    // (stale or foreign data): clear the V rows so that a zero
-                    // weight times their contents stays zero
-                    uint8_t* vb = smem + s * Cfg::STAGE_BYTES + Cfg::KV_BYTES;
-                    for (int r = rows_valid; r < wr * 16 + 16; ++r)
-                        for (int h = 0; h < Cfg::NH; ++h)
-                            if (lane < 8)
-                                *reinterpret_cast<uint4*>(vb + row_off(r) + h * half_stride + lane * 16) = make_uint4(0, 0, 0, 0);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                }
-                // ---- S^T = K Q^T for 16 cache rows; even / odd k-steps in separate accumulators
-                float sa[NBK][4], sb[NBK][4];
-#pragma unroll
-                for (int nbk = 0; nbk < NBK; ++nbk)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) sa[nbk][e] = sb[nbk][e] = 0.0f;
-#pragma unroll
-                for (int kk = 0; kk < KSTEPS; ++kk) {
-                    const int chunk = kk * 2 + k_csel;
-                    const uint32_t addr = st_k + k_off + (chunk >> 3) * half_stride + (((chunk & 7) ^ lrow) << 4);
-                    uint32_t a0, a1, a2, a3;
-                    ldsm_x4(addr, a0, a1, a2, a3);
-#pragma unroll
-                    for (int nbk = 0; nbk < NBK; ++nbk) {
-                        if (kk & 1) mma16816<T>(sb[nbk], a0, a1, a2, a3, qb[nbk][kk][0], qb[nbk][kk][1]);
-                        else mma16816<T>(sa[nbk], a0, a1, a2, a3, qb[nbk][kk][0], qb[nbk][kk][1]);
-                    }
-                }
-                // ---- online softmax (log2 domain). This thread holds, for heads 8*nbk + 2*qi + e,
-                // the scores of rows `quad` ([e]) and `quad + 8` ([2 + e]) of the block.
-                const int r_lo = wr * 16 + quad;
-                uint32_t pb[NBK][2];
-#pragma unroll
-                for (int nbk = 0; nbk < NBK; ++nbk) {
-                    float plo[2], phi[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        float v0 = (sa[nbk][e] + sb[nbk][e]) * sl2;
-                        float v1 = (sa[nbk][2 + e] + sb[nbk][2 + e]) * sl2;
-                        if (ragged) {
-                            if (r_lo >= rows_valid) v0 = -INFINITY;
-                            if (r_lo + 8 >= rows_valid) v1 = -INFINITY;
-                        }
-                        float mx = fmaxf(v0, v1);
-                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                        const float m_new = fmaxf(m_run[nbk][e], mx);
-                        const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
-                        const float alpha = ex2(m_run[nbk][e] - m_safe);
-                        plo[e] = ex2(v0 - m_safe);
-                        phi[e] = ex2(v1 - m_safe);
-                        l_run[nbk][e] = l_run[nbk][e] * alpha + (plo[e] + phi[e]);
-                        m_run[nbk][e] = m_new;
-                        if (alpha != 1.0f) {
-#pragma unroll
-                            for (int mt = 0; mt < MT; ++mt) {
-                                acc[nbk][mt][e] *= alpha;
-                                acc[nbk][mt][2 + e] *= alpha;
-                            }
-                        }
-                    }
-                    // P^T as the B operand: transpose the two 8x8 blocks (rows 0-7 / 8-15 of the block)
-                    pb[nbk][0] = movmatrix_trans(pack2<T>(plo[0], plo[1]));
-                    pb[nbk][1] = movmatrix_trans(pack2<T>(phi[0], phi[1]));
-                }
-                // ---- O^T += V^T P^T
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const int chunk = mt * 2 + v_csel;
-                    const uint32_t addr = st_v + v_off + (chunk >> 3) * half_stride + (((chunk & 7) ^ lrow) << 4);
-                    uint32_t a0, a1, a2, a3;
-                    ldsm_x4_t(addr, a0, a1, a2, a3);
-#pragma unroll
-                    for (int nbk = 0; nbk < NBK; ++nbk)
-                        mma16816<T>(acc[nbk][mt], a0, a1, a2, a3, pb[nbk][0], pb[nbk][1]);
-                }
+            const int rows_valid = w.len - (w.ti + (own - i0)) * TILE;      // >= 1
+            if (ok) {
+                if (rows_valid >= TILE) process(std::false_type{}, TILE);
+                else if (wr * 16 < rows_valid) process(std::true_type{}, rows_valid);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + s * 8);
+            s += 2;
+            if (s >= Cfg::NS) { s -= Cfg::NS; ph ^= 1u; }
         }
-
-        const bool seg_end = (w.ti == w.nt - 1) || (w.g + 1 == w.end);
-        if (seg_end) {
+        i0 += n;
+        // move the walker to the segment's last tile (same unit, no roll-over)
+        w.g += n - 1;
+        w.ti += n - 1;
+        {
             // ---- fold the 8 warp states and emit
             const SegDest dst = seg_dest(p, w, total, seg_first);
 #pragma unroll
@@ -485,13 +564,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
                     for (int ww = 0; ww < NCW; ++ww) mg = fmaxf(mg, s_ml[ww * 8 + row].x);
                     const float mg_safe = (mg == -INFINITY) ? 0.0f : mg;
-                    s_scale[tc] = ex2(s_ml[tc].x - mg_safe);       // tc = (warp index) * 8 + row
+                    s_scale[tc] = ex2((s_ml[tc].x - mg_safe) * sl2);   // tc = (warp index) * 8 + row
                     if (tc < 8) {
                         float lg = 0.0f;
 #pragma unroll
                         for (int ww = 0; ww < NCW; ++ww)
-                            lg += s_ml[ww * 8 + row].y * ex2(s_ml[ww * 8 + row].x - mg_safe);
-                        s_glob[row] = make_float2(mg * LN2, lg);   // m back in natural-log units
+                            lg += s_ml[ww * 8 + row].y * ex2((s_ml[ww * 8 + row].x - mg_safe) * sl2);
+                        s_glob[row] = make_float2(mg * p.scale, lg);   // m from raw score units to natural-log units
                     }
                 }
                 bar_consumers();
@@ -531,7 +610,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             }
         }
         walker_advance(p, w);
-        if (++s == Cfg::NS) { s = 0; ph ^= 1u; }
     }
 }
 
