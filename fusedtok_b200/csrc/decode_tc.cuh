@@ -54,10 +54,12 @@ template <int D> struct TcCfg {
     // order. With an odd depth a group would wait on a stage it did not
     // consume the previous time round, and a parity wait cannot tell "not
     // filled yet" from "filled twice since".
+    // Depth 4 x 32 KB (128 KB in flight per SM) measured faster than 6 x 32 KB:
+    // more outstanding requests than that only lengthen the DRAM queues.
 #ifdef FTK_NS
     static constexpr int NS = FTK_NS;
 #else
-    static constexpr int NS = (D == 128) ? 6 : 8;
+    static constexpr int NS = (D == 128) ? 4 : 8;
 #endif
     static_assert(NS % 2 == 0, "ring depth must be even (see above)");
     static constexpr int ACC_STRIDE = D + 4;           // floats; rows stay 16-byte aligned
@@ -386,19 +388,16 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         constexpr bool RAGGED = decltype(ragged_tag)::value;
         const uint32_t st_k = smem_base + s * Cfg::STAGE_BYTES;
         const uint32_t st_v = st_k + Cfg::KV_BYTES;
+        // Rows at and past the sequence end may hold anything (stale or foreign
+        // data, NaN included). Their scores are forced to -inf below; their V
+        // values are cleared in the fragment registers (each register of a
+        // transposed V fragment holds rows 2*qi and 2*qi + 1 of its 8-row half),
+        // so that a zero weight times their contents stays zero.
+        uint32_t vmask_lo = 0xffffffffu, vmask_hi = 0xffffffffu;
         if constexpr (RAGGED) {
-            // rows at and past the sequence end may hold anything (stale or
-            // foreign data): clear the V rows so that a zero weight times
-            // their contents stays zero
-            if (rows_valid < wr * 16 + 16) {
-                uint8_t* vb = smem + s * Cfg::STAGE_BYTES + Cfg::KV_BYTES;
-                for (int r = rows_valid; r < wr * 16 + 16; ++r)
-                    for (int h = 0; h < Cfg::NH; ++h)
-                        if (lane < 8)
-                            *reinterpret_cast<uint4*>(vb + row_off(r) + h * half_stride + lane * 16) = make_uint4(0, 0, 0, 0);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-            }
+            const int t = wr * 16 + qi * 2;
+            vmask_lo = (t < rows_valid ? 0x0000ffffu : 0u) | (t + 1 < rows_valid ? 0xffff0000u : 0u);
+            vmask_hi = (t + 8 < rows_valid ? 0x0000ffffu : 0u) | (t + 9 < rows_valid ? 0xffff0000u : 0u);
         }
         // Shared-memory fragment loads are issued a few steps ahead of the MMAs
         // that use them (the asm statements keep source order, so the order
@@ -480,6 +479,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
             uint32_t (&f)[4] = fv[mt % PF];
+            if constexpr (RAGGED) {
+                f[0] &= vmask_lo; f[1] &= vmask_lo;     // rows 0-7 of the block
+                f[2] &= vmask_hi; f[3] &= vmask_hi;     // rows 8-15
+            }
 #pragma unroll
             for (int nbk = 0; nbk < NBK; ++nbk)
                 mma16816<T>(acc[nbk][mt], f[0], f[1], f[2], f[3], pb[nbk][0], pb[nbk][1]);
