@@ -251,66 +251,80 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 
     if (warp == NCW) {
         // ===================== producer warp =====================
+        // Everything a tile's copies need (row coordinates, block-table
+        // entries, byte count) is worked out BEFORE the wait for its ring
+        // stage, so that the copies go out the moment the stage is free.
         if (*abort_flag) return;
         const uint64_t pol = policy_evict_first();
         int issued = 0;
+        int kv = 0, unit_row0 = 0;          // of the current unit
+        int row = 0, npg = 0;               // of the prepared tile (row: per lane for small pages)
+        uint32_t bytes = 0;
         // paged cache: 32 consecutive block-table entries of the current sequence, one per lane,
         // fetched with one coalesced load and reused for the tiles they cover
         int tbl_b = -1, tbl_base = 0, tbl_val = 0;
-        int s = 0;                 // ring stage of tile i
-        uint32_t ph = 0;           // phase parity of that stage's current use
-        for (int i = 0; w.g < w.end; ++i) {
-            const bool ok = mbar_wait(bar_empty + s * 8, ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY_TIMEOUT);
-            if (!ok) break;
-            const int kv = w.ub / upb_nch;
-            const uint32_t dst_k = smem_base + s * Cfg::STAGE_BYTES;
-            const uint32_t dst_v = dst_k + Cfg::KV_BYTES;
-            const uint32_t fb = bar_full + s * 8;
-#ifdef FTK_EXP_NOLOAD
-            if (lane == 0) mbar_arrive(fb);
-            if (false) {
-#else
-            {
-#endif
+        bool new_unit = true;
+        auto prepare = [&]() {
+            if (new_unit) {
+                kv = w.ub / upb_nch;
+                unit_row0 = (w.b * p.Hkv + kv) * p.T;
+            }
             if constexpr (!PAGED) {
-                if (lane == 0) {
-                    const int row = (w.b * p.Hkv + kv) * p.T + w.ti * TILE;
-                    mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-                    tma_load_rows(dst_k, &tm_k, row, fb, pol);
-                    tma_load_rows(dst_v, &tm_v, row, fb, pol);
-                }
+                row = unit_row0 + w.ti * TILE;
+                bytes = 2 * Cfg::KV_BYTES;
             } else {
                 const int t0 = w.ti * TILE;
-                const int valid = min(TILE, w.len - t0);
                 if (p.page <= TILE) {
-                    const int npg = (valid + p.page - 1) / p.page;
-                    const int pg0 = t0 >> p.box_shift;                 // first page of the tile (page == box rows)
+                    const int valid = min(TILE, w.len - t0);
+                    npg = (valid + p.page - 1) >> p.box_shift;          // page == box rows, a power of two
+                    const int pg0 = t0 >> p.box_shift;
                     if (tbl_b != w.b || pg0 < tbl_base || pg0 + npg > tbl_base + 32) {
                         tbl_b = w.b;
                         tbl_base = pg0;
                         const int idx = pg0 + lane;
                         tbl_val = idx < p.tbl_width ? __ldg(p.table + (size_t)w.b * p.tbl_width + idx) : 0;
                     }
-                    if (lane == 0) mbar_expect_tx(fb, (uint32_t)(npg * p.page * D * 4));
                     const int blk = __shfl_sync(0xffffffffu, tbl_val, (pg0 - tbl_base + lane) & 31);
-                    if (lane < npg) {
-                        const int row = (blk * p.Hkv + kv) * p.page;
-                        const uint32_t off = (uint32_t)(lane * p.page) * (uint32_t)(D * 2);   // page-major stage
-                        tma_load_rows(dst_k + off, &tm_k, row, fb, pol);
-                        tma_load_rows(dst_v + off, &tm_v, row, fb, pol);
-                    }
-                } else if (lane == 0) {
+                    row = (blk * p.Hkv + kv) * p.page;
+                    bytes = (uint32_t)(npg * p.page * D * 4);
+                } else {
                     const int blk = __ldg(p.table + (size_t)w.b * p.tbl_width + t0 / p.page);
-                    const int row = (blk * p.Hkv + kv) * p.page + (t0 % p.page);
-                    mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+                    row = (blk * p.Hkv + kv) * p.page + (t0 % p.page);
+                    bytes = 2 * Cfg::KV_BYTES;
+                }
+            }
+        };
+        prepare();
+        int s = 0;                 // ring stage of tile i
+        uint32_t ph = 0;           // phase parity of that stage's current use
+        for (int i = 0; w.g < w.end; ++i) {
+            const bool ok = mbar_wait(bar_empty + s * 8, ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY_TIMEOUT);
+            if (!ok) break;
+            const uint32_t dst_k = smem_base + s * Cfg::STAGE_BYTES;
+            const uint32_t dst_v = dst_k + Cfg::KV_BYTES;
+            const uint32_t fb = bar_full + s * 8;
+            if (lane == 0) mbar_expect_tx(fb, bytes);
+            if (!PAGED || p.page > TILE) {
+                if (lane == 0) {
                     tma_load_rows(dst_k, &tm_k, row, fb, pol);
                     tma_load_rows(dst_v, &tm_v, row, fb, pol);
                 }
-            }
+            } else {
+                __syncwarp();                                            // expect_tx before any complete_tx
+                if (lane < npg) {
+                    const uint32_t off = (uint32_t)(lane * p.page) * (uint32_t)(D * 2);   // page-major stage
+                    tma_load_rows(dst_k + off, &tm_k, row, fb, pol);
+                    tma_load_rows(dst_v + off, &tm_v, row, fb, pol);
+                }
             }
             ++issued;
+            const int ub_before = w.ub, b_before = w.b;
             walker_advance(p, w);
             if (++s == Cfg::NS) { s = 0; ph ^= 1u; }
+            if (w.g < w.end) {
+                new_unit = (w.ub != ub_before) || (w.b != b_before);
+                prepare();
+            }
         }
         // If something went wrong, do not leave the CTA while our own copies
         // may still be landing in its shared memory: wait (bounded) for the
