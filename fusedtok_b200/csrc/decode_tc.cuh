@@ -241,8 +241,17 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             mbar_init(bar_empty + s * 8, 4);     // the 4 warps of the group that consumed the stage
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
     }
     __syncthreads();
+    // Programmatic dependent launch: everything above touched only this CTA's
+    // shared memory and kernel parameters, so it may overlap the tail of the
+    // previous kernel in the stream; from here on global memory is read and
+    // written, which must wait for that kernel to have completed. Letting our
+    // own dependents start early is always safe: they wait the same way.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     Walker w;
     if (!sched_init<T>(p, sh, w)) return;      // block-uniform

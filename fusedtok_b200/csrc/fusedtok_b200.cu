@@ -222,7 +222,19 @@ int encode_map(CUtensorMap* map, int dt, const void* base, unsigned long long ro
 
 template <typename T, int D, int GP, bool PG>
 void launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, cudaStream_t cs) {
-    decode_tc_kernel<T, D, GP, PG><<<p.ncta, TC_THREADS, TcCfg<D>::SMEM_BYTES, cs>>>(mk, mv, p);
+    // launched with programmatic stream serialization: the kernel's prologue may overlap the tail
+    // of the previous kernel in the stream (it waits with griddepcontrol.wait before touching memory)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p.ncta);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = TcCfg<D>::SMEM_BYTES;
+    cfg.stream = cs;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, decode_tc_kernel<T, D, GP, PG>, mk, mv, p);
 }
 template <typename T>
 void launch_tc_t(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, int gp, bool paged,
