@@ -279,6 +279,7 @@ def run_ours(args, w, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
+        os.environ["NCCL_DEBUG"] = "WARN"        # keep NCCL's version banner off stdout (one JSON line only)
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", device_id=device)

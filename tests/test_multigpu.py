@@ -1,0 +1,71 @@
+"""Multi-GPU layer on real GPUs (needs >= 2 devices, skipped otherwise): the
+KV-length split (partial kernel -> NCCL all-gather of raw triples -> merge)
+must give the single-GPU result, including a short sequence whose rows all live
+on rank 0 and an empty sequence; batch sharding is a pure concatenation.
+One process per GPU, NCCL without NVLS (plain ring/tree), as child processes."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _worker(rank, world, port, out_dir):
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    sys.path.insert(0, os.path.join(root, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", NCCL_DEBUG="WARN")
+    import torch.distributed as dist
+    import cases
+    import fusedtok_b200 as ft
+    from fusedtok_b200 import sharded
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        rng = np.random.default_rng(11)                       # same inputs on every rank
+        b, hq, hkv, t, d = 3, 16, 4, 4096, 128
+        q, k, v, _ = cases.make_case(rng, b, hq, hkv, t, d, False)
+        lens = np.array([4096, 900, 0], np.int32)
+        qt, kt, vt = (torch.from_numpy(x).to(dev).to(torch.bfloat16) for x in (q, k, v))
+        lens_t = torch.from_numpy(lens).to(dev)
+        full = ft.attention_decode(qt, kt, vt, lens_t)        # single-GPU reference on this rank
+        per = t // world
+        lo, hi = sharded.kv_row_slice(t, world, rank)
+        k_loc = kt[:, :, lo:hi].contiguous()
+        v_loc = vt[:, :, lo:hi].contiguous()
+        dec = sharded.SplitKVDecoder(b, hq, hkv, d, torch.bfloat16, dev, dist.group.WORLD)
+        out = torch.empty_like(qt)
+        for _ in range(2):                                    # twice: buffers are reused
+            dec.decode(qt, k_loc, v_loc, sharded.local_lens(lens_t, per, rank), out)
+        torch.cuda.synchronize()
+        err = (out.float() - full.float()).abs().max().item()
+        assert err <= 4e-3, err
+        assert torch.count_nonzero(out[2]) == 0
+        # batch sharding: each rank decodes its rows; concatenation equals the full result
+        blo, bhi = sharded.batch_slice(b, world, rank)
+        mine = ft.attention_decode(qt[blo:bhi].contiguous(), kt[blo:bhi].contiguous(), vt[blo:bhi].contiguous(),
+                                   lens_t[blo:bhi].contiguous()) if bhi > blo else qt[:0]
+        assert (mine.float() - full[blo:bhi].float()).abs().max().item() <= 4e-3 if bhi > blo else True
+        open(os.path.join(out_dir, "ok%d" % rank), "w").write("%g" % err)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs at least 2 GPUs")
+def test_kv_length_split_matches_single_gpu(tmp_path):
+    import torch.multiprocessing as mp
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert os.path.exists(str(tmp_path / ("ok%d" % r)))
