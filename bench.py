@@ -2,7 +2,7 @@
 """Benchmark of the decode-attention hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c2|c3|c4|c5|ref_b1] [--scaling weak|strong]
+                    [--workload c1|c2|c3|c4|c5|ref_b1|...] [--scaling weak|strong]
 
 One "step" is one decode-attention call over one batch of synthetic KV cache.
 The default workload is benchmark configuration 2 (Llama-3-8B-shaped GQA
@@ -61,6 +61,12 @@ WORKLOADS = {
                desc="config 4: long-context split-KV (KV length split across GPUs when N>1)"),
     "c5": dict(B=256, Hq=40, Hkv=8, D=128, T=32768, dtype="bf16", paged=True, kv_scale=1.0, lens="loguniform",
                desc="config 5: serving mix, paged, lengths log-uniform [1024,32768], graph replay"),
+    "c1": dict(B=1, Hq=8, Hkv=8, D=64, T=512, dtype="f32", paged=False, kv_scale=1.0,
+               desc="config 1: single sequence, MHA, fp32 (2 MB: launch-bound, L2-resident without rotation)"),
+    "ref_b1_f32": dict(B=1, Hq=32, Hkv=8, D=128, T=16384, dtype="f32", paged=False, kv_scale=1.0,
+                       desc="the reference's own benchmark shape in float32 (batch 1, T=16384)"),
+    "c2_f32": dict(B=32, Hq=32, Hkv=8, D=128, T=4096, dtype="f32", paged=False, kv_scale=0.5,
+                   desc="config 2's shape with a float32 cache (CUDA-core kernel)"),
     "ref_b1": dict(B=1, Hq=32, Hkv=8, D=128, T=16384, dtype="bf16", paged=False, kv_scale=1.0,
                    desc="the reference's own benchmark shape (batch 1, T=16384)"),
 }
