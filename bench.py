@@ -48,8 +48,8 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the split-KV
 # partial kernel on the default workload, from the ncu capture summarised in
-# profiles/decode_tc_bf16_d128_config2.md (537.18 MB read + 4.44 MB written).
-NCU_TRAFFIC_BYTES = {"c2": 541619968}
+# profiles/decode_tc_bf16_d128_config2.md (537.23 MB read + 4.13 MB written).
+NCU_TRAFFIC_BYTES = {"c2": 541363712}
 
 WORKLOADS = {
     # name: (batch, q heads, kv heads, dim, rows, dtype, paged, description)
@@ -485,6 +485,7 @@ def run_ours(args, w, rank, world, local_rank):
         gbs, sps, kind, sample, _ = cpu_baseline(w, 12.0, threads)
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": kind,
                                 "sample": sample, "seq_steps_per_s": sps}
+    if world == 1:
         # the reference's own GPU kernels on the same inputs (informational)
         try:
             import oracle
