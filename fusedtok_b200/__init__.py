@@ -25,7 +25,7 @@ except ImportError:  # pragma: no cover - torch is optional, as in the reference
     _HAS_TORCH = False
 
 __version__ = "0.1.0"
-__all__ = ["attention_decode", "attention_decode_paged", "cuda_available"]
+__all__ = ["attention_decode", "attention_decode_paged", "kv_append", "kv_append_paged", "cuda_available"]
 
 _PAGED_GROUPS = (1, 2, 4, 8, 16)
 
@@ -83,15 +83,19 @@ def _host_int_array(t, name="values"):
     return host
 
 
-def _host_lens_checked(lens, batch, limit):
+def _host_lens_checked(lens, batch, limit, upper_inclusive=True):
+    """Host lens values in [0, limit] - or [0, limit) for kv_append, which
+    writes AT lens[b] (reference: _host_lens_checked, :258-275)."""
     host = _host_int_array(lens, "lens")
     if host is None:
         return None
     host = np.ascontiguousarray(host, dtype=np.int32)
     if host.ndim != 1 or host.shape[0] != batch:
         raise ValueError("lens must be 1-D with batch entries")
-    if host.size and (host.min() < 0 or host.max() > limit):
-        raise ValueError(f"lens entries must be in [0, {limit}]")
+    bracket = "]" if upper_inclusive else ")"
+    if host.size and (host.min() < 0 or host.max() > limit
+                      or (not upper_inclusive and host.max() == limit)):
+        raise ValueError(f"lens entries must be in [0, {limit}{bracket}")
     return host
 
 
@@ -103,10 +107,10 @@ def _i32_cuda(t):
     return t
 
 
-def _lens_arg(lens, batch, limit, device):
+def _lens_arg(lens, batch, limit, device, upper_inclusive=True):
     """Host values are validated then uploaded; a device tensor is trusted
     (reference: _lens_arg, :278-290)."""
-    host = _host_lens_checked(lens, batch, limit)
+    host = _host_lens_checked(lens, batch, limit, upper_inclusive)
     if host is not None:
         return torch.from_numpy(host).to(device)
     lt = _i32_cuda(lens)
@@ -287,3 +291,111 @@ def attention_decode_paged(q, k_pool, v_pool, block_table, lens=None, *, cuda=Fa
     res = _fusedtok.attention_decode_paged(arr_q, arr_k, arr_v, arr_t, arr_lens, b, hq, hkv, page,
                                            arr_t.shape[1], nb, d)
     return torch.from_numpy(res) if _is_torch(q) else res
+
+
+def _inplace_host_f32(arr, name):
+    """Host caches of the in-place appends must already be float32
+    C-contiguous: a converted copy would silently drop the writes."""
+    raw = arr.numpy() if _is_torch(arr) else arr
+    if not isinstance(raw, np.ndarray) or raw.dtype != np.float32 or not raw.flags["C_CONTIGUOUS"]:
+        raise TypeError(f"{name} must be a float32 C-contiguous array "
+                        "(in-place op; conversion would drop writes)")
+    return raw
+
+
+def kv_append(k_cache, v_cache, k_new, v_new, lens, *, cuda=False):
+    """Append ONE fresh token's k/v rows per sequence into the contiguous cache,
+    in place: ``k_new[b]`` / ``v_new[b]`` ([Hkv, D]) land at row ``lens[b]`` of
+    ``k_cache[b]`` / ``v_cache[b]`` ([B, Hkv, T, D]). lens is required; host values
+    are validated in [0, T), a CUDA lens tensor is trusted. Returns None.
+    Reference: python/fusedtok/__init__.py:1029-1112."""
+    if _is_torch(k_cache) and k_cache.is_cuda:
+        for name, t in (("k_cache", k_cache), ("v_cache", v_cache), ("k_new", k_new), ("v_new", v_new)):
+            _check_torch_att(t, name)
+        for name, t in (("v_cache", v_cache), ("k_new", k_new), ("v_new", v_new)):
+            if t.dtype is not k_cache.dtype:
+                raise TypeError(f"{name} must have the cache dtype")
+        if k_cache.ndim != 4 or v_cache.ndim != 4:
+            raise ValueError("caches must be [B, Hkv, T, D]")
+        if k_new.ndim != 3 or v_new.ndim != 3:
+            raise ValueError("k_new/v_new must be [B, Hkv, D]")
+        b, hkv, t_rows, d = k_cache.shape
+        if tuple(k_new.shape) != (b, hkv, d) or v_cache.shape != k_cache.shape or v_new.shape != k_new.shape:
+            raise ValueError("k/v operands must match the cache layout")
+        if b == 0:
+            return None
+        lt = _lens_arg(lens, b, t_rows, k_cache.device, upper_inclusive=False)
+        with torch.cuda.device(k_cache.device):
+            _att_launch_fn(k_cache, "kv_append_launch")(
+                k_new.data_ptr(), v_new.data_ptr(), lt.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                b, hkv, d, t_rows, _cuda_stream())
+        return None
+    arr_kc = _inplace_host_f32(k_cache, "k_cache")
+    arr_vc = _inplace_host_f32(v_cache, "v_cache")
+    if not cuda:
+        _no_cpu_path()
+    arr_kn = _as_numpy(k_new, "k_new")
+    arr_vn = _as_numpy(v_new, "v_new")
+    if arr_kc.ndim != 4 or arr_kn.ndim != 3:
+        raise ValueError("caches [B,Hkv,T,D]; k_new [B,Hkv,D]")
+    b, hkv, t_rows, d = arr_kc.shape
+    if arr_kn.shape != (b, hkv, d) or arr_vc.shape != arr_kc.shape or arr_vn.shape != arr_kn.shape:
+        raise ValueError("k/v operands must match the cache layout")
+    arr_l = _host_lens_checked(lens, b, t_rows, upper_inclusive=False)
+    if arr_l is None:
+        raise TypeError("lens must be a host array on this path")
+    _fusedtok.kv_append(arr_kn, arr_vn, arr_l, arr_kc, arr_vc, b, hkv, d, t_rows)
+    return None
+
+
+def kv_append_paged(k_pool, v_pool, block_table, k_new, v_new, lens, *, cuda=False):
+    """Append ONE fresh token's k/v rows per sequence into the paged cache, in
+    place: rows land at pool block ``block_table[b, lens[b] // P]``, offset
+    ``lens[b] % P``. Pools [Nb, Hkv, P, D]; k_new / v_new [B, Hkv, D]; lens
+    required. The table is never modified. Host table / lens values are
+    validated, device tensors trusted. Returns None.
+    Reference: python/fusedtok/__init__.py:943-1026."""
+    if _is_torch(k_pool) and k_pool.is_cuda:
+        for name, t in (("k_pool", k_pool), ("v_pool", v_pool), ("k_new", k_new), ("v_new", v_new)):
+            _check_torch_att(t, name)
+        for name, t in (("v_pool", v_pool), ("k_new", k_new), ("v_new", v_new)):
+            if t.dtype is not k_pool.dtype:
+                raise TypeError(f"{name} must have the pool dtype")
+        if k_pool.ndim != 4 or v_pool.ndim != 4:
+            raise ValueError("pools must be [Nb, Hkv, P, D]")
+        if k_new.ndim != 3 or v_new.ndim != 3:
+            raise ValueError("k_new/v_new must be [B, Hkv, D]")
+        nb, hkv, page, d = k_pool.shape
+        b = k_new.shape[0]
+        if tuple(k_new.shape[1:]) != (hkv, d) or v_pool.shape != k_pool.shape or v_new.shape != k_new.shape:
+            raise ValueError("k/v operands must match the pool layout")
+        if b == 0:
+            return None
+        bt = _table_arg(block_table, b, nb, k_pool.device)
+        lt = _lens_arg(lens, b, bt.shape[1] * page, k_pool.device, upper_inclusive=False)
+        with torch.cuda.device(k_pool.device):
+            _att_launch_fn(k_pool, "kv_append_paged_launch")(
+                k_new.data_ptr(), v_new.data_ptr(), bt.data_ptr(), lt.data_ptr(), k_pool.data_ptr(),
+                v_pool.data_ptr(), b, hkv, d, page, bt.shape[1], _cuda_stream())
+        return None
+    arr_kp = _inplace_host_f32(k_pool, "k_pool")
+    arr_vp = _inplace_host_f32(v_pool, "v_pool")
+    if not cuda:
+        _no_cpu_path()
+    arr_kn = _as_numpy(k_new, "k_new")
+    arr_vn = _as_numpy(v_new, "v_new")
+    if arr_kp.ndim != 4 or arr_kn.ndim != 3:
+        raise ValueError("pools [Nb,Hkv,P,D]; k_new [B,Hkv,D]")
+    nb, hkv, page, d = arr_kp.shape
+    b = arr_kn.shape[0]
+    if arr_kn.shape != (b, hkv, d) or arr_vp.shape != arr_kp.shape or arr_vn.shape != arr_kn.shape:
+        raise ValueError("k/v operands must match the pool layout")
+    arr_t = _host_table_checked(block_table, b, nb)
+    if arr_t is None:
+        raise TypeError("block_table must be a host array on this path")
+    arr_l = _host_lens_checked(lens, b, arr_t.shape[1] * page, upper_inclusive=False)
+    if arr_l is None:
+        raise TypeError("lens must be a host array on this path")
+    _fusedtok.kv_append_paged(arr_kn, arr_vn, arr_t, arr_l, arr_kp, arr_vp, b, hkv, d, page,
+                              arr_t.shape[1], nb)
+    return None

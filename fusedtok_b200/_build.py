@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfusedtok_b200.so")
 SOURCES = ["fusedtok_b200.cu"]
-HEADERS = ["common.cuh", "decode_tc.cuh", "decode_simt.cuh", "merge.cuh",
+HEADERS = ["common.cuh", "decode_tc.cuh", "decode_simt.cuh", "merge.cuh", "kv_append.cuh",
            os.path.join("..", "..", "include", "fusedtok_b200.h")]
 
 NVCC_FLAGS = [

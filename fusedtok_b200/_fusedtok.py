@@ -38,6 +38,11 @@ _lib.fusedtok_cuda_available.restype = _i
 for _n in ("", "_bf16", "_fp16"):
     getattr(_lib, "fusedtok_attention_decode_launch" + _n).argtypes = [_vp] * 5 + [_i] * 5 + [_sz]
     getattr(_lib, "fusedtok_attention_decode_paged_launch" + _n).argtypes = [_vp] * 6 + [_i] * 6 + [_sz]
+for _n in ("", "_bf16", "_fp16"):
+    getattr(_lib, "fusedtok_kv_append_launch" + _n).argtypes = [_vp] * 5 + [_i] * 4 + [_sz]
+    getattr(_lib, "fusedtok_kv_append_paged_launch" + _n).argtypes = [_vp] * 6 + [_i] * 5 + [_sz]
+_lib.fusedtok_kv_append.argtypes = [_vp] * 5 + [_i] * 4
+_lib.fusedtok_kv_append_paged.argtypes = [_vp] * 6 + [_i] * 6
 _lib.fusedtok_attention_decode.argtypes = [_vp] * 5 + [_i] * 5
 _lib.fusedtok_attention_decode_paged.argtypes = [_vp] * 6 + [_i] * 7
 _lib.fusedtok_attention_decode_partial_launch.argtypes = [_i] + [_vp] * 5 + [_i] * 5 + [_sz]
@@ -57,6 +62,9 @@ EXPORTS = (
     "fusedtok_attention_decode_paged_launch", "fusedtok_attention_decode_paged_launch_bf16",
     "fusedtok_attention_decode_paged_launch_fp16",
     "fusedtok_attention_decode", "fusedtok_attention_decode_paged",
+    "fusedtok_kv_append_launch", "fusedtok_kv_append_launch_bf16", "fusedtok_kv_append_launch_fp16",
+    "fusedtok_kv_append_paged_launch", "fusedtok_kv_append_paged_launch_bf16",
+    "fusedtok_kv_append_paged_launch_fp16", "fusedtok_kv_append", "fusedtok_kv_append_paged",
     "fusedtok_attention_decode_partial_launch", "fusedtok_attention_partial_floats",
     "fusedtok_attention_merge_partials_launch",
     "fusedtok_attention_decode_launch_noalloc",
@@ -110,6 +118,36 @@ attention_decode_paged_launch_bf16 = _make_paged_launch("_bf16")
 attention_decode_paged_launch_fp16 = _make_paged_launch("_fp16")
 
 
+def _make_append(suffix):
+    fn = getattr(_lib, "fusedtok_kv_append_launch" + suffix)
+
+    def kv_append_launch(k_new, v_new, lens, k_cache, v_cache, batch, hkv, dim, t_rows, stream=0):
+        _check(fn(int(k_new), int(v_new), int(lens), int(k_cache), int(v_cache), batch, hkv, dim,
+                  t_rows, int(stream)))
+    kv_append_launch.__name__ = "kv_append_launch" + suffix
+    return kv_append_launch
+
+
+def _make_append_paged(suffix):
+    fn = getattr(_lib, "fusedtok_kv_append_paged_launch" + suffix)
+
+    def kv_append_paged_launch(k_new, v_new, table, lens, k_pool, v_pool, batch, hkv, dim, page,
+                               tbl_width, stream=0):
+        _check(fn(int(k_new), int(v_new), int(table), int(lens), int(k_pool), int(v_pool), batch,
+                  hkv, dim, page, tbl_width, int(stream)))
+    kv_append_paged_launch.__name__ = "kv_append_paged_launch" + suffix
+    return kv_append_paged_launch
+
+
+# reference: src/bindings.cpp:2698-2748 (paged) and :2802-2845 (contiguous)
+kv_append_launch = _make_append("")
+kv_append_launch_bf16 = _make_append("_bf16")
+kv_append_launch_fp16 = _make_append("_fp16")
+kv_append_paged_launch = _make_append_paged("")
+kv_append_paged_launch_bf16 = _make_append_paged("_bf16")
+kv_append_paged_launch_fp16 = _make_append_paged("_fp16")
+
+
 def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 
@@ -151,6 +189,31 @@ def attention_decode_paged(q, k_pool, v_pool, table, lens, batch, hq, hkv, page,
                                                 _ptr(lens), _ptr(out), batch, hq, hkv, page,
                                                 tbl_width, num_blocks, dim))
     return out
+
+
+def kv_append(k_new, v_new, lens, k_cache, v_cache, batch, hkv, dim, t_rows):
+    """Staged append into float32 C-contiguous host caches, in place
+    (reference: src/bindings.cpp:2766-2800)."""
+    k_new, v_new, lens = _f32(k_new), _f32(v_new), _i32(lens)
+    if k_new.size != batch * hkv * dim or v_new.size != k_new.size or lens.size != batch \
+            or k_cache.size != batch * hkv * t_rows * dim or v_cache.size != k_cache.size:
+        raise ValueError("kv append operand size mismatch")
+    _check(_lib.fusedtok_kv_append(_ptr(k_new), _ptr(v_new), _ptr(lens), _ptr(k_cache), _ptr(v_cache),
+                                   batch, hkv, dim, t_rows))
+
+
+def kv_append_paged(k_new, v_new, table, lens, k_pool, v_pool, batch, hkv, dim, page, tbl_width,
+                    num_blocks):
+    """Staged paged append into float32 C-contiguous host pools, in place
+    (reference: src/bindings.cpp:2636-2696)."""
+    k_new, v_new, table, lens = _f32(k_new), _f32(v_new), _i32(table), _i32(lens)
+    if k_new.size != batch * hkv * dim or v_new.size != k_new.size or lens.size != batch \
+            or table.size != batch * tbl_width \
+            or k_pool.size != num_blocks * hkv * page * dim or v_pool.size != k_pool.size:
+        raise ValueError("kv append operand size mismatch")
+    _check(_lib.fusedtok_kv_append_paged(_ptr(k_new), _ptr(v_new), _ptr(table), _ptr(lens),
+                                         _ptr(k_pool), _ptr(v_pool), batch, hkv, dim, page,
+                                         tbl_width, num_blocks))
 
 
 def attention_decode_partial_launch(dtype, q, k, v, lens, partial, batch, hq, hkv, t_seq, dim,

@@ -20,6 +20,7 @@
 #include "common.cuh"
 #include "decode_simt.cuh"
 #include "decode_tc.cuh"
+#include "kv_append.cuh"
 #include "merge.cuh"
 
 namespace {
@@ -380,6 +381,37 @@ int decode_paged(int dt, const void* q, const void* kp, const void* vp, const in
                          dim, stream);
 }
 
+// reference: kv_append_launch_t / kv_append_paged_launch_t, src/attention.cu:1924-1941, 1989-2005
+int kv_append_common(int dt, const void* k_new, const void* v_new, const int* table, const int* lens,
+                     void* k_dst, void* v_dst, int batch, int hkv, int dim, int rows, int tbl_width,
+                     uintptr_t stream) {
+    if (batch <= 0) return FUSEDTOK_OK;                       // nothing to append
+    if (dim % 4 != 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "dim must be a multiple of 4");
+    if (table && rows < 1) return fail(FUSEDTOK_INVALID_ARGUMENT, "page size must be >= 1");
+    if (hkv < 1 || dim < 1 || rows < 0 || tbl_width < 0)
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "kv append shapes must satisfy heads>=1, dim>=1, rows>=0");
+    if (!lens) return fail(FUSEDTOK_INVALID_ARGUMENT, "lens is required (it is the write position)");
+    AppendParams p;
+    p.k_new = static_cast<const uint8_t*>(k_new);
+    p.v_new = static_cast<const uint8_t*>(v_new);
+    p.k_dst = static_cast<uint8_t*>(k_dst);
+    p.v_dst = static_cast<uint8_t*>(v_dst);
+    p.lens = lens; p.table = table;
+    p.B = batch; p.Hkv = hkv;
+    p.row_bytes = dim * (int)dtype_size(dt);
+    p.rows = rows; p.tbl_width = tbl_width;
+    const uintptr_t all = reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new) |
+                          reinterpret_cast<uintptr_t>(k_dst) | reinterpret_cast<uintptr_t>(v_dst);
+    const bool wide = (p.row_bytes % 16 == 0) && (all & 15u) == 0;
+    const int vec = wide ? 16 : 8;
+    const int chunks = hkv * (p.row_bytes / vec);
+    dim3 grid((unsigned)batch, (unsigned)((chunks + 255) / 256));
+    cudaStream_t cs = (cudaStream_t)stream;
+    if (wide) kv_append_kernel<uint4><<<grid, 256, 0, cs>>>(p);
+    else kv_append_kernel<uint2><<<grid, 256, 0, cs>>>(p);
+    return check_launch("kv append kernel launch");
+}
+
 // RAII device buffer for the staged paths (reference: DevBuf, src/bindings.cpp:47-66)
 struct DevBuf {
     void* p = nullptr;
@@ -518,6 +550,110 @@ int fusedtok_attention_decode_paged(const float* q, const float* k_pool, const f
     if (rc) return rc;
     if ((e = cudaMemcpy(out, dy.p, q_b, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("D2H copy failed", e);
     if ((e = cudaDeviceSynchronize()) != cudaSuccess) return cuda_fail("attention decode paged kernel failed", e);
+    return FUSEDTOK_OK;
+}
+
+int fusedtok_kv_append_launch(const float* k_new, const float* v_new, const int* lens, float* k_cache,
+                              float* v_cache, int batch, int kv_heads, int dim, int cache_rows, uintptr_t stream) {
+    return kv_append_common(F32, k_new, v_new, nullptr, lens, k_cache, v_cache, batch, kv_heads, dim, cache_rows, 0, stream);
+}
+int fusedtok_kv_append_launch_bf16(const void* k_new, const void* v_new, const int* lens, void* k_cache,
+                                   void* v_cache, int batch, int kv_heads, int dim, int cache_rows, uintptr_t stream) {
+    return kv_append_common(BF16, k_new, v_new, nullptr, lens, k_cache, v_cache, batch, kv_heads, dim, cache_rows, 0, stream);
+}
+int fusedtok_kv_append_launch_fp16(const void* k_new, const void* v_new, const int* lens, void* k_cache,
+                                   void* v_cache, int batch, int kv_heads, int dim, int cache_rows, uintptr_t stream) {
+    return kv_append_common(F16, k_new, v_new, nullptr, lens, k_cache, v_cache, batch, kv_heads, dim, cache_rows, 0, stream);
+}
+int fusedtok_kv_append_paged_launch(const float* k_new, const float* v_new, const int* table, const int* lens,
+                                    float* k_pool, float* v_pool, int batch, int kv_heads, int dim, int page,
+                                    int tbl_width, uintptr_t stream) {
+    if (!table) return fail(FUSEDTOK_INVALID_ARGUMENT, "block table must not be null");
+    return kv_append_common(F32, k_new, v_new, table, lens, k_pool, v_pool, batch, kv_heads, dim, page, tbl_width, stream);
+}
+int fusedtok_kv_append_paged_launch_bf16(const void* k_new, const void* v_new, const int* table, const int* lens,
+                                         void* k_pool, void* v_pool, int batch, int kv_heads, int dim, int page,
+                                         int tbl_width, uintptr_t stream) {
+    if (!table) return fail(FUSEDTOK_INVALID_ARGUMENT, "block table must not be null");
+    return kv_append_common(BF16, k_new, v_new, table, lens, k_pool, v_pool, batch, kv_heads, dim, page, tbl_width, stream);
+}
+int fusedtok_kv_append_paged_launch_fp16(const void* k_new, const void* v_new, const int* table, const int* lens,
+                                         void* k_pool, void* v_pool, int batch, int kv_heads, int dim, int page,
+                                         int tbl_width, uintptr_t stream) {
+    if (!table) return fail(FUSEDTOK_INVALID_ARGUMENT, "block table must not be null");
+    return kv_append_common(F16, k_new, v_new, table, lens, k_pool, v_pool, batch, kv_heads, dim, page, tbl_width, stream);
+}
+
+// Staged appends: HOST buffers; the caches are updated in place on the host
+// (reference: pybind `kv_append` / `kv_append_paged`, src/bindings.cpp:2766-2800, 2636-2696):
+// host values are validated, everything is copied to the device, the float32
+// launcher runs on the default stream and the caches are copied back.
+int fusedtok_kv_append(const float* k_new, const float* v_new, const int* lens, float* k_cache, float* v_cache,
+                       int batch, int kv_heads, int dim, int cache_rows) {
+    if (batch <= 0) return FUSEDTOK_OK;
+    if (dim % 4 != 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "dim must be a multiple of 4");
+    if (kv_heads < 1 || dim < 1 || cache_rows < 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "kv append operand size mismatch");
+    if (!lens) return fail(FUSEDTOK_INVALID_ARGUMENT, "lens is required (it is the write position)");
+    for (int i = 0; i < batch; ++i)
+        if (lens[i] < 0 || lens[i] >= cache_rows)
+            return fail(FUSEDTOK_INVALID_ARGUMENT, "lens entries must be within [0, cache rows)");
+    const size_t new_b = (size_t)batch * kv_heads * dim * 4;
+    const size_t cache_b = (size_t)batch * kv_heads * cache_rows * dim * 4;
+    DevBuf dkn(new_b), dvn(new_b), dl((size_t)batch * 4), dk(cache_b), dv(cache_b);
+    for (const DevBuf* b : {&dkn, &dvn, &dl, &dk, &dv})
+        if (b->err != cudaSuccess) return cuda_fail("cudaMalloc failed", b->err);
+    cudaError_t e;
+    if ((e = cudaMemcpy(dkn.p, k_new, new_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if ((e = cudaMemcpy(dvn.p, v_new, new_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if ((e = cudaMemcpy(dl.p, lens, (size_t)batch * 4, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if ((e = cudaMemcpy(dk.p, k_cache, cache_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if ((e = cudaMemcpy(dv.p, v_cache, cache_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    const int rc = fusedtok_kv_append_launch((const float*)dkn.p, (const float*)dvn.p, (const int*)dl.p, (float*)dk.p,
+                                             (float*)dv.p, batch, kv_heads, dim, cache_rows, 0);
+    if (rc) return rc;
+    if ((e = cudaMemcpy(k_cache, dk.p, cache_b, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("D2H copy failed", e);
+    if ((e = cudaMemcpy(v_cache, dv.p, cache_b, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("D2H copy failed", e);
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return cuda_fail("kv append kernel failed", e);
+    return FUSEDTOK_OK;
+}
+
+int fusedtok_kv_append_paged(const float* k_new, const float* v_new, const int* table, const int* lens,
+                             float* k_pool, float* v_pool, int batch, int kv_heads, int dim, int page,
+                             int tbl_width, int num_blocks) {
+    if (batch <= 0) return FUSEDTOK_OK;
+    if (dim % 4 != 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "dim must be a multiple of 4");
+    if (page < 1) return fail(FUSEDTOK_INVALID_ARGUMENT, "page size must be >= 1");
+    if (kv_heads < 1 || dim < 1 || tbl_width < 0 || num_blocks < 0 || !table)
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "kv append operand size mismatch");
+    if ((long long)tbl_width * page > (1LL << 30)) return fail(FUSEDTOK_INVALID_ARGUMENT, "table capacity too large");
+    if (!lens) return fail(FUSEDTOK_INVALID_ARGUMENT, "lens is required (it is the write position)");
+    for (int i = 0; i < batch; ++i) {
+        if (lens[i] < 0 || lens[i] >= tbl_width * page)
+            return fail(FUSEDTOK_INVALID_ARGUMENT, "lens entries must be within [0, table width * page)");
+        const int blk = table[(size_t)i * tbl_width + lens[i] / page];
+        if (blk < 0 || blk >= num_blocks)
+            return fail(FUSEDTOK_INVALID_ARGUMENT, "block table entries must be valid pool block ids");
+    }
+    const size_t new_b = (size_t)batch * kv_heads * dim * 4;
+    const size_t pool_b = (size_t)num_blocks * kv_heads * page * dim * 4;
+    const size_t tbl_b = (size_t)batch * tbl_width * 4;
+    DevBuf dkn(new_b), dvn(new_b), dl((size_t)batch * 4), dt(tbl_b), dk(pool_b), dv(pool_b);
+    for (const DevBuf* b : {&dkn, &dvn, &dl, &dt, &dk, &dv})
+        if (b->err != cudaSuccess) return cuda_fail("cudaMalloc failed", b->err);
+    cudaError_t e;
+    if ((e = cudaMemcpy(dkn.p, k_new, new_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if ((e = cudaMemcpy(dvn.p, v_new, new_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if ((e = cudaMemcpy(dl.p, lens, (size_t)batch * 4, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if ((e = cudaMemcpy(dt.p, table, tbl_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if ((e = cudaMemcpy(dk.p, k_pool, pool_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if ((e = cudaMemcpy(dv.p, v_pool, pool_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    const int rc = fusedtok_kv_append_paged_launch((const float*)dkn.p, (const float*)dvn.p, (const int*)dt.p,
+                                                   (const int*)dl.p, (float*)dk.p, (float*)dv.p, batch, kv_heads, dim,
+                                                   page, tbl_width, 0);
+    if (rc) return rc;
+    if ((e = cudaMemcpy(k_pool, dk.p, pool_b, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("D2H copy failed", e);
+    if ((e = cudaMemcpy(v_pool, dv.p, pool_b, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("D2H copy failed", e);
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return cuda_fail("kv append paged kernel failed", e);
     return FUSEDTOK_OK;
 }
 

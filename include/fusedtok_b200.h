@@ -99,6 +99,46 @@ int fusedtok_attention_decode_paged(const float* q, const float* k_pool, const f
                                     int q_heads, int kv_heads, int page, int tbl_width,
                                     int num_blocks, int dim);
 
+/* ---- kv-cache append: the write side of the decode loop --------------------
+ * Scatter ONE fresh token's K and V rows per sequence (k_new, v_new
+ * [B, Hkv, D]) into the cache at position lens[b] (lens is required):
+ * contiguous caches [B, Hkv, T, D] at row lens[b]; paged pools at block
+ * table[b][lens[b] / P], offset lens[b] % P. In place, asynchronous on `stream`,
+ * capturable, no workspace. Replace fusedtok::kv_append_launch / _bf16 / _fp16
+ * and kv_append_paged_launch / _bf16 / _fp16, include/fusedtok/cuda_launch.hpp:
+ * 416-430 and 443-454 (src/attention.cu:1924-2035). Device lens / table values
+ * are trusted; a position outside the cache is skipped instead of written. */
+int fusedtok_kv_append_launch(const float* k_new, const float* v_new, const int* lens,
+                              float* k_cache, float* v_cache, int batch, int kv_heads, int dim,
+                              int cache_rows, uintptr_t stream);
+int fusedtok_kv_append_launch_bf16(const void* k_new, const void* v_new, const int* lens,
+                                   void* k_cache, void* v_cache, int batch, int kv_heads, int dim,
+                                   int cache_rows, uintptr_t stream);
+int fusedtok_kv_append_launch_fp16(const void* k_new, const void* v_new, const int* lens,
+                                   void* k_cache, void* v_cache, int batch, int kv_heads, int dim,
+                                   int cache_rows, uintptr_t stream);
+int fusedtok_kv_append_paged_launch(const float* k_new, const float* v_new, const int* table,
+                                    const int* lens, float* k_pool, float* v_pool, int batch,
+                                    int kv_heads, int dim, int page, int tbl_width,
+                                    uintptr_t stream);
+int fusedtok_kv_append_paged_launch_bf16(const void* k_new, const void* v_new, const int* table,
+                                         const int* lens, void* k_pool, void* v_pool, int batch,
+                                         int kv_heads, int dim, int page, int tbl_width,
+                                         uintptr_t stream);
+int fusedtok_kv_append_paged_launch_fp16(const void* k_new, const void* v_new, const int* table,
+                                         const int* lens, void* k_pool, void* v_pool, int batch,
+                                         int kv_heads, int dim, int page, int tbl_width,
+                                         uintptr_t stream);
+/* Staged appends: HOST float32 buffers, caches updated in place on the host,
+ * lens / table values validated (lens in [0, rows), used table entries in
+ * [0, num_blocks)). Replace the pybind bindings `kv_append` / `kv_append_paged`,
+ * src/bindings.cpp:2766-2800 and :2636-2696. */
+int fusedtok_kv_append(const float* k_new, const float* v_new, const int* lens, float* k_cache,
+                       float* v_cache, int batch, int kv_heads, int dim, int cache_rows);
+int fusedtok_kv_append_paged(const float* k_new, const float* v_new, const int* table,
+                             const int* lens, float* k_pool, float* v_pool, int batch,
+                             int kv_heads, int dim, int page, int tbl_width, int num_blocks);
+
 /* ---- KV-length split across GPUs (no counterpart in the reference, which is
  * single-GPU; the exchanged triple and the merge rule are the reference's
  * intra-GPU ones, src/attention.cu:434-463 and :503-548) --------------------

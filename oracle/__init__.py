@@ -40,6 +40,8 @@ def _load():
             [_fp, _fp, _fp, _ip, _ip, _fp] + [_i] * 7)
         _lib.oracle_attention_partial.argtypes = [_fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i]
         _lib.oracle_attention_merge.argtypes = [_fp, _fp, _i, _i, _fp]
+        _lib.oracle_kv_append.argtypes = [_fp, _fp, _ip, _fp, _fp] + [_i] * 4
+        _lib.oracle_kv_append_paged.argtypes = [_fp, _fp, _ip, _ip, _fp, _fp] + [_i] * 6
     return _lib
 
 
@@ -58,6 +60,9 @@ def _load_ref():
         _ref.ref_attention_decode_cpu.argtypes = [_fp, _fp, _fp, _ip, _fp] + [_i] * 5
         _ref.ref_attention_decode_paged_cpu.argtypes = (
             [_fp, _fp, _fp, _ip, _ip, _fp] + [_i] * 7)
+        if hasattr(_ref, "ref_kv_append_cpu"):
+            _ref.ref_kv_append_cpu.argtypes = [_fp, _fp, _ip, _fp, _fp] + [_i] * 4
+            _ref.ref_kv_append_paged_cpu.argtypes = [_fp, _fp, _ip, _ip, _fp, _fp] + [_i] * 6
         vp = ctypes.c_void_p
         _ref.ref_attention_decode_launch.argtypes = (
             [_i, vp, vp, vp, vp, vp] + [_i] * 5 + [ctypes.c_size_t])
@@ -174,3 +179,45 @@ def ref_gpu_decode_paged_launch(dtype_code, q_ptr, k_ptr, v_ptr, table_ptr,
                                              d, stream)
     if rc:
         raise RuntimeError(r.ref_last_error().decode())
+
+
+def _append(fn, k_cache, v_cache, k_new, v_new, lens):
+    k_new, v_new, lens = _f32(k_new), _f32(v_new), _i32(lens)
+    kc, vc = _f32(k_cache).copy(), _f32(v_cache).copy()
+    b, hkv, t, d = kc.shape
+    rc = fn(_pf(k_new), _pf(v_new), _pi(lens), _pf(kc), _pf(vc), b, hkv, d, t)
+    if rc:
+        raise ValueError("oracle rejected the arguments (code %d)" % rc)
+    return kc, vc
+
+
+def _append_paged(fn, k_pool, v_pool, table, k_new, v_new, lens):
+    k_new, v_new, lens, table = _f32(k_new), _f32(v_new), _i32(lens), _i32(table)
+    kp, vp = _f32(k_pool).copy(), _f32(v_pool).copy()
+    nb, hkv, page, d = kp.shape
+    b = k_new.shape[0]
+    rc = fn(_pf(k_new), _pf(v_new), _pi(table), _pi(lens), _pf(kp), _pf(vp), b, hkv, d, page,
+            table.shape[1], nb)
+    if rc:
+        raise ValueError("oracle rejected the arguments (code %d)" % rc)
+    return kp, vp
+
+
+def kv_append(k_cache, v_cache, k_new, v_new, lens):
+    """Contiguous append through the C restatement; returns the updated copies."""
+    return _append(_load().oracle_kv_append, k_cache, v_cache, k_new, v_new, lens)
+
+
+def kv_append_paged(k_pool, v_pool, table, k_new, v_new, lens):
+    """Paged append through the C restatement; returns the updated copies."""
+    return _append_paged(_load().oracle_kv_append_paged, k_pool, v_pool, table, k_new, v_new, lens)
+
+
+def ref_kv_append(k_cache, v_cache, k_new, v_new, lens):
+    """The reference's own kv_append_cpu (src/attention.cu:2064-2099)."""
+    return _append(_load_ref().ref_kv_append_cpu, k_cache, v_cache, k_new, v_new, lens)
+
+
+def ref_kv_append_paged(k_pool, v_pool, table, k_new, v_new, lens):
+    """The reference's own kv_append_paged_cpu (src/attention.cu:2037-2062)."""
+    return _append_paged(_load_ref().ref_kv_append_paged_cpu, k_pool, v_pool, table, k_new, v_new, lens)

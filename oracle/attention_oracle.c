@@ -245,3 +245,63 @@ int oracle_attention_merge(const float *ml, const float *acc, int n, int dim,
         out[d] = out[d] / l;
     return 0;
 }
+
+/*
+ * kv-cache append, contiguous: one fresh token's K and V rows per sequence are
+ * copied to cache row lens[b]. reference: kv_append_cpu,
+ * src/attention.cu:2064-2099. Caches [B,Hkv,T,D] are updated in place.
+ */
+int oracle_kv_append(const float *k_new, const float *v_new, const int *lens,
+                     float *k_cache, float *v_cache, int batch, int hkv,
+                     int dim, int t_rows)
+{
+    if (dim % 4 != 0)
+        return 1;
+    for (int bi = 0; bi < batch; ++bi)
+        if (lens[bi] < 0 || lens[bi] >= t_rows)
+            return 1;
+    for (int bi = 0; bi < batch; ++bi) {
+        const int pos = lens[bi];
+        for (int h = 0; h < hkv; ++h) {
+            const size_t dst = (((size_t)bi * hkv + h) * t_rows + pos) * dim;
+            const size_t src = ((size_t)bi * hkv + h) * dim;
+            memcpy(k_cache + dst, k_new + src, sizeof(float) * dim);
+            memcpy(v_cache + dst, v_new + src, sizeof(float) * dim);
+        }
+    }
+    return 0;
+}
+
+/*
+ * kv-cache append, paged: rows land in pool block table[b][lens[b] / P] at
+ * offset lens[b] % P. reference: kv_append_paged_cpu,
+ * src/attention.cu:2037-2062 (lens in [0, S*P), used block ids in [0, Nb)).
+ */
+int oracle_kv_append_paged(const float *k_new, const float *v_new,
+                           const int *table, const int *lens, float *k_pool,
+                           float *v_pool, int batch, int hkv, int dim,
+                           int page, int tbl_width, int num_blocks)
+{
+    if (dim % 4 != 0 || page < 1)
+        return 1;
+    for (int bi = 0; bi < batch; ++bi) {
+        const int pos = lens[bi];
+        if (pos < 0 || pos >= tbl_width * page)
+            return 1;
+        const int blk = table[(size_t)bi * tbl_width + pos / page];
+        if (blk < 0 || blk >= num_blocks)
+            return 1;
+    }
+    for (int bi = 0; bi < batch; ++bi) {
+        const int pos = lens[bi];
+        const int blk = table[(size_t)bi * tbl_width + pos / page];
+        const int off = pos % page;
+        for (int h = 0; h < hkv; ++h) {
+            const size_t dst = (((size_t)blk * hkv + h) * page + off) * dim;
+            const size_t src = ((size_t)bi * hkv + h) * dim;
+            memcpy(k_pool + dst, k_new + src, sizeof(float) * dim);
+            memcpy(v_pool + dst, v_new + src, sizeof(float) * dim);
+        }
+    }
+    return 0;
+}

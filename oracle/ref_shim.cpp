@@ -82,6 +82,34 @@ int ref_attention_decode_paged_cpu(const float* q, const float* k_pool,
     });
 }
 
+// reference: fusedtok::kv_append_cpu / kv_append_paged_cpu, src/attention.cu:2037-2099.
+// The caches are updated in place.
+int ref_kv_append_cpu(const float* k_new, const float* v_new, const int* lens, float* k_cache,
+                      float* v_cache, int batch, int hkv, int dim, int t_rows) {
+    return guarded([&] {
+        const size_t nn = (size_t)batch * hkv * dim, nc = (size_t)batch * hkv * t_rows * dim;
+        std::vector<float> kn(k_new, k_new + nn), vn(v_new, v_new + nn), kc(k_cache, k_cache + nc),
+            vc(v_cache, v_cache + nc);
+        std::vector<int> lv(lens, lens + batch);
+        fusedtok::kv_append_cpu(kn, vn, lv, kc, vc, batch, hkv, dim, t_rows);
+        std::memcpy(k_cache, kc.data(), nc * sizeof(float));
+        std::memcpy(v_cache, vc.data(), nc * sizeof(float));
+    });
+}
+int ref_kv_append_paged_cpu(const float* k_new, const float* v_new, const int* table, const int* lens,
+                            float* k_pool, float* v_pool, int batch, int hkv, int dim, int page,
+                            int tbl_width, int num_blocks) {
+    return guarded([&] {
+        const size_t nn = (size_t)batch * hkv * dim, np = (size_t)num_blocks * hkv * page * dim;
+        std::vector<float> kn(k_new, k_new + nn), vn(v_new, v_new + nn), kp(k_pool, k_pool + np),
+            vp(v_pool, v_pool + np);
+        std::vector<int> lv(lens, lens + batch), tv(table, table + (size_t)batch * tbl_width);
+        fusedtok::kv_append_paged_cpu(kn, vn, tv, lv, kp, vp, batch, hkv, dim, page, tbl_width, num_blocks);
+        std::memcpy(k_pool, kp.data(), np * sizeof(float));
+        std::memcpy(v_pool, vp.data(), np * sizeof(float));
+    });
+}
+
 // The reference GPU launchers, device pointers in, asynchronous on `stream`.
 // dtype: 0 = float32, 1 = bfloat16, 2 = float16.
 int ref_attention_decode_launch(int dtype, const void* q, const void* k,
