@@ -314,7 +314,10 @@ def run_ours(args, w, rank, world, local_rank):
 
     if split_kv:
         from fusedtok_b200 import sharded
-        dec = sharded.SplitKVDecoder(batch, w["Hq"], w["Hkv"], w["D"], q.dtype, device, dist.group.WORLD)
+        if args.exchange == "p2p":
+            dec = sharded.PeerSplitKVDecoder(batch, w["Hq"], w["Hkv"], w["D"], q.dtype, device, dist.group.WORLD)
+        else:
+            dec = sharded.SplitKVDecoder(batch, w["Hq"], w["Hkv"], w["D"], q.dtype, device, dist.group.WORLD)
 
     def step(i):
         k, v = sets[i % n_sets]
@@ -335,7 +338,7 @@ def run_ours(args, w, rank, world, local_rank):
     for i in range(max(args.warmup, 3)):
         step(i)
     torch.cuda.synchronize()
-    if use_graph and not split_kv:
+    if use_graph and not (split_kv and args.exchange == "nccl"):      # (capturing the collective is left to the caller)
         graphs = []
         for i in range(n_sets):
             g = torch.cuda.CUDAGraph()
@@ -368,7 +371,7 @@ def run_ours(args, w, rank, world, local_rank):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    launches = _fusedtok.attention_launch_count() if not graphs else args.steps
+    launches = _fusedtok.attention_launch_count() if not graphs else args.steps * (2 if split_kv else 1)
     if args.profile:
         print(json.dumps({"profile_run": True, "ms_per_step": ms / args.steps, "workload": args.workload,
                           "GBps": bytes_step / (ms / args.steps * 1e-3) / 1e9}), flush=True)
@@ -463,7 +466,7 @@ def run_ours(args, w, rank, world, local_rank):
             "algorithmic_bytes_per_step_per_gpu": bytes_step,
             "l2": ("inputs larger than L2 (%.0f MB of K/V per step)" % (kv_bytes / 1e6)) if n_sets == 1 else
                   ("rotating over %d independent K/V sets (%.0f MB each) so reads come from HBM" % (n_sets, kv_bytes / 1e6)),
-            "parallelism": ("kv-length split x%d + all-gather merge" % world) if split_kv else
+            "parallelism": ("kv-length split x%d, %s exchange of (m,l,acc) + merge" % (world, args.exchange)) if split_kv else
                            ("batch-sharded x%d, no communication" % world),
             "cuda_graph": bool(graphs),
         },
@@ -524,14 +527,22 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="KV-length split (c4, N>1): the library's own peer exchange or an NCCL all-gather")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE",
+                    help="override a field of the workload (e.g. --set T=32768), for experiments")
     ap.add_argument("--profile", action="store_true",
                     help="profiler run: warm-up and timed steps only (no clock sampling, no end-to-end or CPU legs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    for kv in args.set:
+        key, val = kv.split("=", 1)
+        w[key] = int(val) if val.lstrip("-").isdigit() else val
+        w["desc"] += " [%s]" % kv
     if args.impl == "reference":
         run_reference_arm(args, w, rank)
         return

@@ -50,6 +50,13 @@ _lib.fusedtok_attention_merge_partials_launch.argtypes = [_i, _vp, _i, _vp, _i, 
 _lib.fusedtok_attention_partial_floats.argtypes = [_i, _i, _i]
 _lib.fusedtok_attention_partial_floats.restype = ctypes.c_longlong
 _lib.fusedtok_attention_decode_launch_noalloc.argtypes = [_i] + [_vp] * 5 + [_i] * 5 + [_sz]
+_lib.fusedtok_exchange_alloc.argtypes = [_i, _i, _i, _i, ctypes.POINTER(_vp), ctypes.POINTER(ctypes.c_longlong)]
+_lib.fusedtok_exchange_free.argtypes = [_vp]
+_lib.fusedtok_exchange_export.argtypes = [_vp, ctypes.c_char_p]
+_lib.fusedtok_exchange_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(_vp)]
+_lib.fusedtok_exchange_close.argtypes = [_vp]
+_lib.fusedtok_attention_decode_exchange_launch.argtypes = (
+    [_i] + [_vp] * 5 + [ctypes.POINTER(_vp)] + [_i] * 7 + [_sz])
 _lib.fusedtok_attention_device_status.argtypes = [ctypes.POINTER(_i)]
 _lib.fusedtok_attention_launch_count.argtypes = [_i]
 _lib.fusedtok_attention_launch_count.restype = ctypes.c_longlong
@@ -67,6 +74,8 @@ EXPORTS = (
     "fusedtok_kv_append_paged_launch_fp16", "fusedtok_kv_append", "fusedtok_kv_append_paged",
     "fusedtok_attention_decode_partial_launch", "fusedtok_attention_partial_floats",
     "fusedtok_attention_merge_partials_launch",
+    "fusedtok_exchange_alloc", "fusedtok_exchange_free", "fusedtok_exchange_export",
+    "fusedtok_exchange_open", "fusedtok_exchange_close", "fusedtok_attention_decode_exchange_launch",
     "fusedtok_attention_decode_launch_noalloc",
     "fusedtok_attention_device_status", "fusedtok_attention_launch_count",
 )
@@ -234,6 +243,47 @@ def attention_merge_partials_launch(dtype, partials, n_parts, out, batch, hq, di
     """Fold n_parts gathered triple blocks into the normalised output."""
     _check(_lib.fusedtok_attention_merge_partials_launch(
         dtype, int(partials), n_parts, int(out), batch, hq, dim, int(stream)))
+
+
+def exchange_alloc(n_ranks, batch, hq, dim):
+    """Allocate this rank's exchange buffer for the direct peer exchange;
+    returns (device pointer, bytes)."""
+    ptr, nbytes = _vp(), ctypes.c_longlong()
+    _check(_lib.fusedtok_exchange_alloc(n_ranks, batch, hq, dim, ctypes.byref(ptr), ctypes.byref(nbytes)))
+    return ptr.value, nbytes.value
+
+
+def exchange_free(ptr):
+    _check(_lib.fusedtok_exchange_free(ptr))
+
+
+def exchange_export(ptr):
+    """64-byte CUDA IPC handle of an exchange buffer (bytes)."""
+    buf = ctypes.create_string_buffer(64)
+    _check(_lib.fusedtok_exchange_export(ptr, buf))
+    return buf.raw
+
+
+def exchange_open(handle):
+    """Map a peer's exchange buffer from its IPC handle; returns the device pointer."""
+    ptr = _vp()
+    _check(_lib.fusedtok_exchange_open(handle, ctypes.byref(ptr)))
+    return ptr.value
+
+
+def exchange_close(ptr):
+    _check(_lib.fusedtok_exchange_close(ptr))
+
+
+def attention_decode_exchange_launch(dtype, q, k, v, lens, out, buffers, rank, batch, hq, hkv, t_seq,
+                                     dim, stream=0):
+    """KV-length split step with direct peer exchange: `buffers` lists every
+    rank's exchange buffer pointer (own at index `rank`)."""
+    n = len(buffers)
+    arr = (_vp * n)(*buffers)
+    _check(_lib.fusedtok_attention_decode_exchange_launch(
+        dtype, int(q), int(k), int(v), _opt(lens), int(out), arr, n, rank, batch, hq, hkv, t_seq, dim,
+        int(stream)))
 
 
 def attention_decode_launch_noalloc(dtype, q, k, v, lens, out, batch, hq, hkv, t_seq, dim, stream=0):

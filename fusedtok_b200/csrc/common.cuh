@@ -51,8 +51,15 @@ struct DecodeParams {
     float* ws_acc;        // [slots][GC][D]  unnormalised
     int* counters;        // [units] arrival counters, zero between launches (the last arriver resets)
     int* status;          // device status word
-    float* triple_ml;     // when non-null: emit (m, l) here [B, Hq, 2] ...
-    float* triple_acc;    // ... and unnormalised acc here [B, Hq, D]
+    float* triple_ml;     // when non-null: emit raw triples instead of `out`: one block
+                          // [B*Hq*2 (m, l), padded | B*Hq*D unnormalised acc] starting here ...
+    size_t triple_acc_off;  // ... with the acc part at this float offset
+    // KV-length split with direct peer exchange: when n_peers > 0 the triple block is written
+    // into EVERY rank's exchange buffer (plain stores over NVLink) instead of triple_ml.
+    float* peer_blocks[16];          // data region of each rank's exchange buffer (own included)
+    const unsigned int* peer_epoch;  // this rank's count of completed exchange steps
+    int n_peers, peer_rank;
+    long long peer_nf;               // floats per triple block
     int B, Hq, Hkv, G;    // G = Hq / Hkv
     int GC, NCH;          // heads per unit, units per (b, kv)
     int T;                // cache rows (contiguous) or tbl_width * page
@@ -68,6 +75,13 @@ struct DecodeParams {
 __host__ __device__ __forceinline__ size_t triple_acc_offset(long long rows) {
     return ((size_t)rows * 2 + 3) & ~(size_t)3;
 }
+
+constexpr int MAX_PEERS = 16;
+
+// Where destination j of a raw triple block lives. Exchange buffers are double-buffered by the
+// parity of the step number, so a rank that runs one step ahead never overwrites a block its
+// peer is still merging.
+__device__ __forceinline__ float* triple_block(const struct DecodeParams& p, int j);
 
 // ---- storage types ---------------------------------------------------------
 template <typename T> struct Store;
@@ -121,6 +135,12 @@ template <> struct Store<__half> {
     }
 };
 
+__device__ __forceinline__ float* triple_block(const DecodeParams& p, int j) {
+    if (!p.n_peers) return p.triple_ml;
+    const unsigned int parity = (__ldg(p.peer_epoch) + 1u) & 1u;
+    return p.peer_blocks[j] + ((size_t)parity * p.n_peers + p.peer_rank) * (size_t)p.peer_nf;
+}
+
 // ---- scheduler -------------------------------------------------------------
 __device__ __forceinline__ int seq_len(const DecodeParams& p, int b) {
     if (!p.lens) return p.T;
@@ -162,12 +182,16 @@ __device__ __forceinline__ long long block_sum(long long v, long long* red) {
 template <typename T>
 __device__ void zero_rows(const DecodeParams& p, int b) {
     if (p.triple_ml) {
-        for (int h = 0; h < p.Hq; ++h) {
-            const size_t r = (size_t)b * p.Hq + h;
-            p.triple_ml[r * 2] = -INFINITY;
-            p.triple_ml[r * 2 + 1] = 0.0f;
-            for (int d = 0; d < p.D; d += 4)
-                *reinterpret_cast<float4*>(p.triple_acc + r * p.D + d) = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int nd = p.n_peers ? p.n_peers : 1;
+        for (int j = 0; j < nd; ++j) {
+            float* blk = triple_block(p, j);
+            for (int h = 0; h < p.Hq; ++h) {
+                const size_t r = (size_t)b * p.Hq + h;
+                blk[r * 2] = -INFINITY;
+                blk[r * 2 + 1] = 0.0f;
+                for (int d = 0; d < p.D; d += 4)
+                    *reinterpret_cast<float4*>(blk + p.triple_acc_off + r * p.D + d) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
         return;
     }
@@ -324,10 +348,11 @@ __device__ __forceinline__ void emit_final2(const DecodeParams& p, int b, int h,
                                             float l, float a0, float a1, bool write_ml) {
     const size_t r = (size_t)b * p.Hq + h;
     if (p.triple_ml) {
-        *reinterpret_cast<float2*>(p.triple_acc + r * p.D + d) = make_float2(a0, a1);
-        if (write_ml) {
-            p.triple_ml[r * 2] = m_nat;
-            p.triple_ml[r * 2 + 1] = l;
+        const int nd = p.n_peers ? p.n_peers : 1;
+        for (int j = 0; j < nd; ++j) {
+            float* blk = triple_block(p, j);
+            *reinterpret_cast<float2*>(blk + p.triple_acc_off + r * p.D + d) = make_float2(a0, a1);
+            if (write_ml) *reinterpret_cast<float2*>(blk + r * 2) = make_float2(m_nat, l);
         }
     } else {
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;

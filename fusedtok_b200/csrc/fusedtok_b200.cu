@@ -264,21 +264,28 @@ inline bool is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
 // table == nullptr: contiguous cache with `rows` cache rows per (b, kv).
 // table != nullptr: paged pools, page rows per block, tbl_width entries per sequence.
 // partial != nullptr: emit raw triples instead of the normalised output.
+struct PeerDest {                    // direct peer exchange of the raw triples (KV-length split)
+    void* const* bases;              // host array: every rank's exchange buffer, own included
+    int n, rank;
+};
+
 int decode_common(int dt, const void* q, const void* k, const void* v, const int* table, const int* lens,
                   void* out, float* partial, int batch, int hq, int hkv, int rows, int page, int tbl_width,
-                  int dim, uintptr_t stream) {
+                  int dim, uintptr_t stream, const PeerDest* peers = nullptr) {
     cudaStream_t cs = (cudaStream_t)stream;
     if (batch == 0) return FUSEDTOK_OK;                       // nothing to compute (src/attention.cu:1474)
     const long long out_rows = (long long)batch * hq;
     const int G = hq / hkv;
     float* tr_ml = partial;
-    float* tr_acc = partial ? partial + triple_acc_offset(out_rows) : nullptr;
 
+    if (rows == 0 && peers)
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "the peer exchange needs at least one cache row per rank");
     if (rows == 0) {
         // empty cache: zero rows (src/attention.cu:211-216) or empty triples
         if (partial) {
             const long long n = out_rows * dim;
-            fill_empty_triple_kernel<<<(unsigned)((n + 255) / 256), 256, 0, cs>>>(tr_ml, tr_acc, out_rows, dim);
+            fill_empty_triple_kernel<<<(unsigned)((n + 255) / 256), 256, 0, cs>>>(
+                tr_ml, tr_ml + triple_acc_offset(out_rows), out_rows, dim);
             return check_launch("attention empty-triple kernel launch");
         }
         const cudaError_t e = cudaMemsetAsync(out, 0, (size_t)out_rows * dim * dtype_size(dt), cs);
@@ -303,7 +310,17 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
     DecodeParams p;
     memset(&p, 0, sizeof(p));
     p.q = q; p.k = k; p.v = v; p.out = out; p.lens = lens; p.table = table;
-    p.triple_ml = tr_ml; p.triple_acc = tr_acc;
+    p.triple_ml = tr_ml;
+    p.triple_acc_off = triple_acc_offset(out_rows);
+    if (peers) {
+        p.n_peers = peers->n;
+        p.peer_rank = peers->rank;
+        p.peer_nf = (long long)p.triple_acc_off + out_rows * dim;
+        for (int j = 0; j < peers->n; ++j)
+            p.peer_blocks[j] = reinterpret_cast<float*>(static_cast<unsigned char*>(peers->bases[j]) + XCHG_DATA_BYTES);
+        p.peer_epoch = static_cast<const unsigned int*>(peers->bases[peers->rank]);
+        p.triple_ml = p.peer_blocks[peers->rank];     // non-null: "emit raw triples"
+    }
     p.B = batch; p.Hq = hq; p.Hkv = hkv; p.G = G; p.T = rows; p.D = dim;
     p.page = page; p.tbl_width = tbl_width;
     p.scale = 1.0f / sqrtf((float)dim);
@@ -686,6 +703,77 @@ int fusedtok_attention_merge_partials_launch(int dtype, const float* partials, i
     else
         ftk::merge_parts_kernel<__half><<<grid, ftk::MERGE_WARPS * 32, 0, cs>>>(partials, n_parts, (__half*)out, rows, dim);
     return check_launch("attention partial-merge kernel launch");
+}
+
+// ---- direct peer exchange for the KV-length split ---------------------------------
+int fusedtok_exchange_alloc(int n_ranks, int batch, int q_heads, int dim, void** buffer, long long* bytes) {
+    if (!buffer || n_ranks < 1 || n_ranks > ftk::MAX_PEERS || batch < 0 || q_heads < 1 || dim < 1)
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "exchange buffer: 1..16 ranks, batch>=0, heads>=1, dim>=1");
+    const long long nf = fusedtok_attention_partial_floats(batch, q_heads, dim);
+    const size_t total = ftk::XCHG_DATA_BYTES + (size_t)2 * n_ranks * (size_t)nf * sizeof(float);
+    void* mem = nullptr;
+    cudaError_t e = cudaMalloc(&mem, total);
+    if (e != cudaSuccess) return cuda_fail("exchange buffer allocation failed", e);
+    if ((e = cudaMemset(mem, 0, total)) != cudaSuccess) return cuda_fail("exchange buffer clear failed", e);
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return cuda_fail("exchange buffer clear failed", e);
+    *buffer = mem;
+    if (bytes) *bytes = (long long)total;
+    return FUSEDTOK_OK;
+}
+int fusedtok_exchange_free(void* buffer) {
+    if (buffer && cudaFree(buffer) != cudaSuccess) return cuda_fail("exchange buffer free failed", cudaGetLastError());
+    return FUSEDTOK_OK;
+}
+int fusedtok_exchange_export(const void* buffer, unsigned char handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void*>(buffer));
+    if (e != cudaSuccess) return cuda_fail("cudaIpcGetMemHandle failed", e);
+    memcpy(handle, &h, 64);
+    return FUSEDTOK_OK;
+}
+int fusedtok_exchange_open(const unsigned char handle[64], void** buffer) {
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    const cudaError_t e = cudaIpcOpenMemHandle(buffer, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail("cudaIpcOpenMemHandle failed", e);
+    return FUSEDTOK_OK;
+}
+int fusedtok_exchange_close(void* buffer) {
+    if (buffer && cudaIpcCloseMemHandle(buffer) != cudaSuccess) return cuda_fail("cudaIpcCloseMemHandle failed", cudaGetLastError());
+    return FUSEDTOK_OK;
+}
+
+int fusedtok_attention_decode_exchange_launch(int dtype, const void* q, const void* k, const void* v, const int* lens,
+                                              void* out, void* const* buffers, int n_ranks, int rank, int batch,
+                                              int q_heads, int kv_heads, int cache_rows, int dim, uintptr_t stream) {
+    if (dtype < 0 || dtype > 2) return fail(FUSEDTOK_INVALID_ARGUMENT, "dtype must be 0 (f32), 1 (bf16) or 2 (fp16)");
+    if (!buffers || n_ranks < 1 || n_ranks > ftk::MAX_PEERS || rank < 0 || rank >= n_ranks)
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "exchange needs 1..16 ranks and 0 <= rank < ranks");
+    for (int j = 0; j < n_ranks; ++j)
+        if (!buffers[j]) return fail(FUSEDTOK_INVALID_ARGUMENT, "exchange buffer pointers must not be null");
+    int rc = attention_check(batch, q_heads, kv_heads, cache_rows, dim);
+    if (rc) return rc;
+    if (batch == 0) return FUSEDTOK_OK;
+    PeerDest pd{buffers, n_ranks, rank};
+    rc = decode_common(dtype, q, k, v, nullptr, lens, nullptr, nullptr, batch, q_heads, kv_heads, cache_rows, 0, 0, dim,
+                       stream, &pd);
+    if (rc) return rc;
+    DeviceState* dev = nullptr;
+    if ((rc = device_state(&dev))) return rc;
+    ftk::ExchangeParams x;
+    memset(&x, 0, sizeof(x));
+    for (int j = 0; j < n_ranks; ++j) x.base[j] = static_cast<unsigned int*>(buffers[j]);
+    x.n = n_ranks; x.rank = rank;
+    x.nf = fusedtok_attention_partial_floats(batch, q_heads, dim);
+    x.status = dev->status;
+    const long long rows = (long long)batch * q_heads;
+    const unsigned grid = (unsigned)((rows + ftk::MERGE_WARPS - 1) / ftk::MERGE_WARPS);
+    cudaStream_t cs = (cudaStream_t)stream;
+    if (dtype == F32) ftk::merge_peers_kernel<float><<<grid, ftk::MERGE_WARPS * 32, 0, cs>>>(x, (float*)out, rows, dim);
+    else if (dtype == BF16) ftk::merge_peers_kernel<__nv_bfloat16><<<grid, ftk::MERGE_WARPS * 32, 0, cs>>>(x, (__nv_bfloat16*)out, rows, dim);
+    else ftk::merge_peers_kernel<__half><<<grid, ftk::MERGE_WARPS * 32, 0, cs>>>(x, (__half*)out, rows, dim);
+    return check_launch("attention peer-exchange merge kernel launch");
 }
 
 int fusedtok_attention_device_status(int* status) {

@@ -19,6 +19,11 @@ Two ways to use several GPUs:
   puts the n blocks in every rank's HBM; the merge kernel folds them with the
   reference's log-sum-exp rule. All three steps are stream-ordered and can be
   captured in one CUDA graph.
+  ``PeerSplitKVDecoder`` does the same exchange without a collective library:
+  the split-KV kernel stores each rank's triple block straight into every
+  peer's buffer (CUDA IPC mapping, plain stores over NVLink) and the merge
+  kernel synchronises on per-step flags - two launches per step instead of
+  three, and no collective latency.
 """
 
 import torch
@@ -97,3 +102,41 @@ class SplitKVDecoder:
         _fusedtok.attention_merge_partials_launch(self.code, self.gathered.data_ptr(), self.world,
                                                   out.data_ptr(), b, hq, d, st)
         return out
+
+
+class PeerSplitKVDecoder:
+    """KV-length split with the exchange done by the library's own kernels over
+    peer memory. Construction is collective (it swaps IPC handles through
+    ``torch.distributed``); every rank must then call ``decode`` the same number
+    of times with the same shapes."""
+
+    def __init__(self, batch, q_heads, kv_heads, dim, dtype, device, group=None):
+        import torch.distributed as dist
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.shape = (batch, q_heads, kv_heads, dim)
+        self.code = _DT_CODE[dtype]
+        with torch.cuda.device(device):
+            self.mine, self.bytes = _fusedtok.exchange_alloc(self.world, batch, q_heads, dim)
+            handle = _fusedtok.exchange_export(self.mine)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle, group=group)
+            self.buffers = [self.mine if r == self.rank else _fusedtok.exchange_open(handles[r])
+                            for r in range(self.world)]
+        dist.barrier(group)           # every rank has mapped every buffer before anyone writes
+
+    def decode(self, q, k_local, v_local, lens_local, out):
+        b, hq, hkv, d = self.shape
+        _fusedtok.attention_decode_exchange_launch(
+            self.code, q.data_ptr(), k_local.data_ptr(), v_local.data_ptr(),
+            lens_local.data_ptr() if lens_local is not None else 0, out.data_ptr(), self.buffers,
+            self.rank, b, hq, hkv, k_local.shape[2], d, torch.cuda.current_stream().cuda_stream)
+        return out
+
+    def close(self):
+        """Unmap the peers' buffers and free this rank's (after a device sync on every rank)."""
+        for r, ptr in enumerate(self.buffers):
+            if r != self.rank:
+                _fusedtok.exchange_close(ptr)
+        _fusedtok.exchange_free(self.mine)
+        self.buffers = []

@@ -160,6 +160,35 @@ int fusedtok_attention_merge_partials_launch(int dtype, const float* partials, i
                                              void* out, int batch, int q_heads, int dim,
                                              uintptr_t stream);
 
+/* ---- KV-length split with direct peer exchange (no counterpart in the
+ * reference) ------------------------------------------------------------------
+ * The same split as above, but the ranks exchange their raw triples themselves
+ * instead of through a collective library: every rank owns an exchange buffer
+ * (fusedtok_exchange_alloc), exports it (fusedtok_exchange_export: a 64-byte
+ * CUDA IPC handle to hand to the other processes by any means) and maps its
+ * peers' buffers (fusedtok_exchange_open). One call then runs two kernels on
+ * `stream`: the split-KV kernel stores this rank's triple block into EVERY
+ * rank's buffer with plain stores over NVLink, and a merge kernel raises this
+ * rank's "landed" flag on every peer, waits - bounded, on local memory - for
+ * the n flags of the step and folds the n blocks into `out` on every rank.
+ * `buffers` is a HOST array of n device pointers, entry `rank` being the rank's
+ * own buffer. All ranks must make the same sequence of calls with the same
+ * shapes. The step number lives in the buffer, so a captured CUDA graph can be
+ * replayed. A peer that never delivers makes the wait expire after 2 s: the
+ * call's output is then invalid, fusedtok_attention_device_status reports 5,
+ * the context stays usable. */
+int fusedtok_exchange_alloc(int n_ranks, int batch, int q_heads, int dim, void** buffer,
+                            long long* bytes);
+int fusedtok_exchange_free(void* buffer);
+int fusedtok_exchange_export(const void* buffer, unsigned char handle[64]);
+int fusedtok_exchange_open(const unsigned char handle[64], void** buffer);
+int fusedtok_exchange_close(void* buffer);
+int fusedtok_attention_decode_exchange_launch(int dtype, const void* q, const void* k, const void* v,
+                                              const int* lens, void* out, void* const* buffers,
+                                              int n_ranks, int rank, int batch, int q_heads,
+                                              int kv_heads, int cache_rows, int dim,
+                                              uintptr_t stream);
+
 /* ---- allocation-free launcher (no counterpart in the reference, whose split
  * path always owns a cudaMalloc'ed workspace) -------------------------------
  * For hosts that must not allocate device memory after start-up (a server that

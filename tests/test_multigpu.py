@@ -49,6 +49,19 @@ def _worker(rank, world, port, out_dir):
         err = (out.float() - full.float()).abs().max().item()
         assert err <= 4e-3, err
         assert torch.count_nonzero(out[2]) == 0
+        # the same split with the library's own peer exchange: same result as the NCCL path
+        from fusedtok_b200 import _fusedtok
+        peer = sharded.PeerSplitKVDecoder(b, hq, hkv, d, torch.bfloat16, dev, dist.group.WORLD)
+        out2 = torch.full_like(qt, float("nan"))
+        for step in range(5):                                 # several steps: both buffer parities, flags reused
+            qs = (qt.float() * (1.0 + 0.1 * step)).to(torch.bfloat16)
+            dec.decode(qs, k_loc, v_loc, sharded.local_lens(lens_t, per, rank), out)
+            peer.decode(qs, k_loc, v_loc, sharded.local_lens(lens_t, per, rank), out2)
+            torch.cuda.synchronize()
+            assert torch.equal(out, out2), (out.float() - out2.float()).abs().max().item()
+        assert _fusedtok.attention_device_status() == 0
+        dist.barrier()
+        peer.close()
         # batch sharding: each rank decodes its rows; concatenation equals the full result
         blo, bhi = sharded.batch_slice(b, world, rank)
         mine = ft.attention_decode(qt[blo:bhi].contiguous(), kt[blo:bhi].contiguous(), vt[blo:bhi].contiguous(),
