@@ -68,6 +68,23 @@ def _cuda_stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+class _on_device:
+    """Make `device` current for the launch (the library works on the current
+    device); free when it already is."""
+
+    def __init__(self, device):
+        self.ctx = None if device.index is None or device.index == torch.cuda.current_device() \
+            else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
+
+
 def _host_int_array(t, name="values"):
     """Host-origin value -> int numpy array; None for a device tensor (whose
     values are never read back). Non-integral host input is rejected
@@ -195,7 +212,7 @@ def attention_decode(q, k_cache, v_cache, lens=None, *, cuda=False):
             lens_ptr = lt.data_ptr()
         out = torch.empty((b, hq, d), dtype=q.dtype, device=q.device)
         if b * hq > 0:
-            with torch.cuda.device(q.device):
+            with _on_device(q.device):
                 _att_launch_fn(q, "attention_decode_launch")(
                     q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), lens_ptr,
                     out.data_ptr(), b, hq, hkv, t_rows, d, _cuda_stream())
@@ -258,7 +275,7 @@ def attention_decode_paged(q, k_pool, v_pool, block_table, lens=None, *, cuda=Fa
             lens_ptr = lt.data_ptr()
         out = torch.empty((b, hq, d), dtype=q.dtype, device=q.device)
         if b * hq > 0:
-            with torch.cuda.device(q.device):
+            with _on_device(q.device):
                 _att_launch_fn(q, "attention_decode_paged_launch")(
                     q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), bt.data_ptr(), lens_ptr,
                     out.data_ptr(), b, hq, hkv, page, s_width, d, _cuda_stream())
@@ -325,7 +342,7 @@ def kv_append(k_cache, v_cache, k_new, v_new, lens, *, cuda=False):
         if b == 0:
             return None
         lt = _lens_arg(lens, b, t_rows, k_cache.device, upper_inclusive=False)
-        with torch.cuda.device(k_cache.device):
+        with _on_device(k_cache.device):
             _att_launch_fn(k_cache, "kv_append_launch")(
                 k_new.data_ptr(), v_new.data_ptr(), lt.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                 b, hkv, d, t_rows, _cuda_stream())
@@ -373,7 +390,7 @@ def kv_append_paged(k_pool, v_pool, block_table, k_new, v_new, lens, *, cuda=Fal
             return None
         bt = _table_arg(block_table, b, nb, k_pool.device)
         lt = _lens_arg(lens, b, bt.shape[1] * page, k_pool.device, upper_inclusive=False)
-        with torch.cuda.device(k_pool.device):
+        with _on_device(k_pool.device):
             _att_launch_fn(k_pool, "kv_append_paged_launch")(
                 k_new.data_ptr(), v_new.data_ptr(), bt.data_ptr(), lt.data_ptr(), k_pool.data_ptr(),
                 v_pool.data_ptr(), b, hkv, d, page, bt.shape[1], _cuda_stream())

@@ -21,6 +21,37 @@ namespace ftk {
 constexpr int SIMT_WARPS = 8;
 constexpr int SIMT_THREADS = SIMT_WARPS * 32;
 
+template <int N> struct Log2 { static constexpr int v = (N <= 1) ? 0 : 1 + Log2<N / 2>::v; };
+template <> struct Log2<0> { static constexpr int v = 0; };
+
+// Sum N per-lane values across the warp, all N at once: in every step a lane
+// hands half of its values to its partner and keeps (and sums) the other half,
+// so the N reductions cost N - 1 + (5 - log2 N) shuffles instead of 5 N. On
+// return v[0] is the complete sum of value number `lane >> (5 - log2 N)`.
+template <int N>
+__device__ __forceinline__ float lane_transpose_reduce(float (&v)[N], int lane) {
+    constexpr int K = Log2<N>::v;
+#pragma unroll
+    for (int s = 0; s < 5; ++s) {
+        const int off = 16 >> s;
+        if (s < K) {
+            const int half = N >> (s + 1);
+            const bool up = (lane & off) != 0;
+#pragma unroll
+            for (int j = 0; j < (N > 1 ? N / 2 : 1); ++j) {
+                if (j < half) {
+                    const float send = up ? v[j] : v[j + half];
+                    const float keep = up ? v[j + half] : v[j];
+                    v[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            }
+        } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+        }
+    }
+    return v[0];
+}
+
 // GC: query heads per unit (1, 2, 4, 8); LC: 4-element chunks per lane
 // (head dim <= 128 * LC).
 template <typename T, int GC, int LC>
@@ -44,8 +75,15 @@ decode_simt_kernel(const DecodeParams p) {
     const T* kbase = reinterpret_cast<const T*>(p.k);
     const T* vbase = reinterpret_cast<const T*>(p.v);
 
+    // The R x GC scores of a step are reduced all at once (lane_transpose_reduce), after which lane
+    // L owns score number L >> SH = g * R + r. The softmax state is kept the same way: a lane
+    // carries (m, l) of its own head g only (l: the share of its own row slot r), computes ONE
+    // weight and ONE rescale factor per step, and the warp shares them by shuffle.
+    constexpr int NV = GC * R;                       // scores per step
+    constexpr int SH = 5 - Log2<NV>::v;              // lane -> score number
+    const int my_idx = lane >> SH, my_g = my_idx / R, my_r = my_idx % R;
     float4 qv[GC][LC], acc[GC][LC];
-    float m[GC], l[GC];
+    float m_own = -INFINITY, l_own = 0.0f;
     long long seg_first = w.g;
 
     for (long long i = 0; w.g < w.end; ++i) {
@@ -54,10 +92,10 @@ decode_simt_kernel(const DecodeParams p) {
         if (i == 0 || w.ti == 0) {
             seg_first = w.g;
             const T* qb = reinterpret_cast<const T*>(p.q) + ((size_t)w.b * p.Hq + kv * p.G + ch * p.GC) * D;
+            m_own = -INFINITY;
+            l_own = 0.0f;
 #pragma unroll
             for (int g = 0; g < GC; ++g) {
-                m[g] = -INFINITY;
-                l[g] = 0.0f;
 #pragma unroll
                 for (int j = 0; j < LC; ++j) {
                     const int c = lane + 32 * j;
@@ -96,38 +134,35 @@ decode_simt_kernel(const DecodeParams p) {
                     }
                 }
             }
+            float sc[NV];
 #pragma unroll
-            for (int g = 0; g < GC; ++g) {
-                float dot[R];
+            for (int g = 0; g < GC; ++g)
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    float s = 0.0f;
+                    float d = 0.0f;
 #pragma unroll
                     for (int j = 0; j < LC; ++j)
-                        s += qv[g][j].x * kc[r][j].x + qv[g][j].y * kc[r][j].y +
+                        d += qv[g][j].x * kc[r][j].x + qv[g][j].y * kc[r][j].y +
                              qv[g][j].z * kc[r][j].z + qv[g][j].w * kc[r][j].w;
-                    dot[r] = s;
+                    sc[g * R + r] = d;
                 }
+            // my score: head my_g, row t0 + my_r
+            float s_own = lane_transpose_reduce<NV>(sc, lane) * p.scale;
+            if (t0 + my_r >= t_end) s_own = -INFINITY;
+            float mx = s_own;                                   // max over the R rows of my head
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1)
+            for (int o = 1; o < R; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o << SH));
+            const float m_new = fmaxf(m_own, mx);               // finite: row t0 is always live
+            const float r_own = expf(m_own - m_new);
+            const float p_own = expf(s_own - m_new);
+            l_own = l_own * r_own + p_own;
+            m_own = m_new;
 #pragma unroll
-                    for (int r = 0; r < R; ++r) dot[r] += __shfl_xor_sync(0xffffffffu, dot[r], o);
-                float mx = -INFINITY;
+            for (int g = 0; g < GC; ++g) {
+                const float r_old = __shfl_sync(0xffffffffu, r_own, (g * R) << SH);
+                float pr[R];
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    dot[r] = (t0 + r < t_end) ? dot[r] * p.scale : -INFINITY;
-                    mx = fmaxf(mx, dot[r]);
-                }
-                const float m_new = fmaxf(m[g], mx);          // finite: row t0 is always live
-                const float r_old = expf(m[g] - m_new);
-                float pr[R], psum = 0.0f;
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    pr[r] = expf(dot[r] - m_new);
-                    psum += pr[r];
-                }
-                l[g] = l[g] * r_old + psum;
-                m[g] = m_new;
+                for (int r = 0; r < R; ++r) pr[r] = __shfl_sync(0xffffffffu, p_own, (g * R + r) << SH);
 #pragma unroll
                 for (int j = 0; j < LC; ++j) {
                     float4 a = acc[g][j];
@@ -155,7 +190,12 @@ decode_simt_kernel(const DecodeParams p) {
                     const int c = lane + 32 * j;
                     if (c < chunks) *reinterpret_cast<float4*>(&s_acc[warp][g][c * 4]) = acc[g][j];
                 }
-                if (lane == 0) s_ml[warp][g] = make_float2(m[g], l[g]);
+            }
+            {
+                float l_g = l_own;                               // total over the R row slots of my head
+#pragma unroll
+                for (int o = 1; o < R; o <<= 1) l_g += __shfl_xor_sync(0xffffffffu, l_g, o << SH);
+                if ((lane & ((1 << SH) - 1)) == 0 && my_r == 0) s_ml[warp][my_g] = make_float2(m_own, l_g);
             }
             __syncthreads();
             if (threadIdx.x < SIMT_WARPS * GC) {

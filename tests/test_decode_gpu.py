@@ -272,6 +272,25 @@ def test_config2_full_size_properties():
     assert_status_ok()
 
 
+def test_many_back_to_back_launches_stay_bit_identical():
+    """600 launches queued without any host synchronisation (the regime in which
+    a producer/consumer phase hazard of the TMA ring once showed up): every
+    launch must give the bits of the first and the status word must stay 0."""
+    rng = np.random.default_rng(17)
+    q, k, v, lens = cases.make_case(rng, 8, 32, 8, 3000, 128, True)
+    qt, kt, vt, _ = half_case(torch.bfloat16, q, k, v)
+    lt = torch.from_numpy(lens).cuda()
+    outs = [torch.empty_like(qt) for _ in range(4)]
+    st = torch.cuda.current_stream().cuda_stream
+    for i in range(600):
+        _fusedtok.attention_decode_launch_bf16(qt.data_ptr(), kt.data_ptr(), vt.data_ptr(), lt.data_ptr(),
+                                               outs[i % 4].data_ptr(), 8, 32, 8, 3000, 128, st)
+    torch.cuda.synchronize()
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    assert_status_ok()
+
+
 # ---- CUDA graph capture (reference: tests/test_attention.py:482-550, 763-792)
 
 def _capture(run):
