@@ -149,6 +149,13 @@ __device__ __forceinline__ int seq_len(const DecodeParams& p, int b) {
 }
 __device__ __forceinline__ int tiles_of(int len) { return (len + TILE - 1) / TILE; }
 
+// a / b for non-negative operands; 32-bit hardware path when both fit (a 64-bit divide is a
+// long subroutine on the GPU and these sit on every CTA's start-up path)
+__device__ __forceinline__ long long qdiv(long long a, long long b) {
+    if (((unsigned long long)a | (unsigned long long)b) >> 32) return a / b;
+    return (long long)((unsigned int)a / (unsigned int)b);
+}
+
 struct SchedShared {
     long long total;     // tiles in the whole launch
     long long red[33];   // block-reduction scratch
@@ -221,15 +228,15 @@ __device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w) {
         total_nt = block_sum(loc, sh->red);
     }
     const long long total = total_nt * upb;
-    const long long start = (total * c) / p.ncta;
-    const long long end = (total * (c + 1)) / p.ncta;
+    const long long start = qdiv(total * c, p.ncta);
+    const long long end = qdiv(total * (c + 1), p.ncta);
     if (start >= end) return false;
-    const long long x = start / upb;    // tiles-per-unit prefix we look for
+    const long long x = qdiv(start, upb);    // tiles-per-unit prefix we look for
     int b0;
     long long pb;
     if (!p.lens) {
         const int nt = tiles_of(p.T);
-        b0 = (int)(x / nt);
+        b0 = (int)qdiv(x, nt);
         pb = (long long)b0 * nt;
     } else {
         // chunked block scan over tiles_of(len_b) to find P_b <= x < P_{b+1}
@@ -272,8 +279,8 @@ __device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w) {
     w.len = seq_len(p, b0);
     w.nt = tiles_of(w.len);
     const long long rem = start - pb * upb;
-    w.ub = (int)(rem / w.nt);
-    w.ti = (int)(rem % w.nt);
+    w.ub = (int)qdiv(rem, w.nt);
+    w.ti = (int)(rem - (long long)w.ub * w.nt);
     if (threadIdx.x == 0) sh->total = total;
     __syncthreads();
     return true;
@@ -296,7 +303,7 @@ __device__ __forceinline__ void walker_advance(const DecodeParams& p, Walker& w)
 
 // CTA that owns global tile x when `total` tiles are split over n CTAs.
 __device__ __forceinline__ int owner_of(long long x, long long total, int n) {
-    return (int)(((x + 1) * n - 1) / total);
+    return (int)qdiv((x + 1) * n - 1, total);
 }
 
 // Where a finished segment goes.
@@ -311,7 +318,7 @@ struct SegDest {
 };
 
 __device__ __forceinline__ bool cta_range_empty(long long total, int n, int c) {
-    return (total * c) / n == (total * (c + 1)) / n;
+    return qdiv(total * c, n) == qdiv(total * (c + 1), n);
 }
 
 __device__ __forceinline__ SegDest seg_dest(const DecodeParams& p, const Walker& w, long long total,
