@@ -518,13 +518,98 @@ def run_ours(args, w, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_reference_rows(args):
+    """The reference's own attention-decode benchmark rows (benchmarks/bench.py:468-516) on this
+    GPU: batch 1, 32/8 heads, head dim 128, T in {4096, 16384}, fp32 and bf16, plus the paged fp32
+    row (page 16), each through the public operator, beside torch SDPA with pre-expanded heads
+    (the reference's comparison) and the reference's own kernels compiled for sm_100a. Protocol as
+    in the reference: 3 rounds, each with its own warm-up, CUDA events, mean; the same tensors every
+    iteration (at these sizes they can stay L2-resident: this is the reference's protocol, not the
+    HBM-roofline one used for `value` elsewhere). GB/s counts (2*K.numel + 2*q.numel)*sizeof."""
+    import numpy as np
+    import torch
+    import fusedtok_b200 as ft
+    import oracle
+
+    torch.cuda.set_device(0)
+
+    def timeit(fn, iters):
+        vals = []
+        for _ in range(3):
+            for _ in range(5):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            vals.append(e0.elapsed_time(e1) / iters * 1e3)
+        return sum(vals) / len(vals)
+
+    rows = []
+    have_ref = oracle.ref_available()
+    b, hq, hkv, d = 1, 32, 8, 128
+    for t_rows in (4096, 16384):
+        q = torch.randn(b, hq, d, device="cuda")
+        k = torch.randn(b, hkv, t_rows, d, device="cuda")
+        v = torch.randn(b, hkv, t_rows, d, device="cuda")
+        for dt, code, name in ((torch.float32, 0, "attn decode"), (torch.bfloat16, 1, "attn decode bf16")):
+            qd, kd, vd = q.to(dt), k.to(dt), v.to(dt)
+            kk = kd.repeat_interleave(hq // hkv, dim=1)
+            vv = vd.repeat_interleave(hq // hkv, dim=1)
+            nbytes = (2 * kd.numel() + 2 * qd.numel()) * kd.element_size()
+            ours = timeit(lambda: ft.attention_decode(qd, kd, vd), args.steps)
+            sdpa = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(qd.unsqueeze(2), kk, vv).squeeze(2),
+                          args.steps)
+            row = {"op": name, "shape": "T=%d" % t_rows, "us": ours, "GBps": nbytes / ours / 1e3,
+                   "sdpa_us": sdpa, "speedup_vs_sdpa": sdpa / ours}
+            if have_ref:
+                out = torch.empty_like(qd)
+                st = torch.cuda.current_stream().cuda_stream
+                ref = timeit(lambda: oracle.ref_gpu_decode_launch(code, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), 0,
+                                                                  out.data_ptr(), b, hq, hkv, t_rows, d, st), args.steps)
+                row["reference_kernel_us"] = ref
+                row["speedup_vs_reference_kernel"] = ref / ours
+            rows.append(row)
+        if t_rows == 16384:
+            page = 16
+            nblk = t_rows // page
+            perm = torch.randperm(nblk, device="cuda").to(torch.int32)
+            kp = k.view(b, hkv, nblk, page, d)[0].permute(1, 0, 2, 3).contiguous()[perm.argsort().long()]
+            vp = v.view(b, hkv, nblk, page, d)[0].permute(1, 0, 2, 3).contiguous()[perm.argsort().long()]
+            table = perm.argsort().argsort().to(torch.int32).view(1, nblk).contiguous()
+            ours = timeit(lambda: ft.attention_decode_paged(q, kp, vp, table), args.steps)
+            kk = k.repeat_interleave(hq // hkv, dim=1)
+            vv = v.repeat_interleave(hq // hkv, dim=1)
+            sdpa = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(q.unsqueeze(2), kk, vv).squeeze(2),
+                          args.steps)
+            nbytes = (2 * k.numel() + 2 * q.numel()) * 4
+            err = (ft.attention_decode_paged(q, kp, vp, table) - ft.attention_decode(q, k, v)).abs().max().item()
+            row = {"op": "attn decode paged", "shape": "T=16384 P=16", "us": ours, "GBps": nbytes / ours / 1e3,
+                   "sdpa_us": sdpa, "speedup_vs_sdpa": sdpa / ours, "max_abs_vs_contiguous": err}
+            if have_ref:
+                out = torch.empty_like(q)
+                st = torch.cuda.current_stream().cuda_stream
+                ref = timeit(lambda: oracle.ref_gpu_decode_paged_launch(0, q.data_ptr(), kp.data_ptr(), vp.data_ptr(),
+                                                                        table.data_ptr(), 0, out.data_ptr(), b, hq, hkv,
+                                                                        page, nblk, d, st), args.steps)
+                row["reference_kernel_us"] = ref
+                row["speedup_vs_reference_kernel"] = ref / ours
+            rows.append(row)
+    print(json.dumps({"benchmark": "reference attention-decode rows on this GPU", "protocol":
+                      "3 rounds x own warm-up, CUDA events, mean; public Python operator; same tensors every iteration",
+                      "gpu": torch.cuda.get_device_name(0), "rows": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["refrows"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
@@ -538,6 +623,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload == "refrows":
+        if rank == 0:
+            run_reference_rows(args)
+        return
     w = dict(WORKLOADS[args.workload])
     for kv in args.set:
         key, val = kv.split("=", 1)
