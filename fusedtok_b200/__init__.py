@@ -25,7 +25,8 @@ except ImportError:  # pragma: no cover - torch is optional, as in the reference
     _HAS_TORCH = False
 
 __version__ = "0.1.0"
-__all__ = ["attention_decode", "attention_decode_paged", "kv_append", "kv_append_paged", "cuda_available"]
+__all__ = ["attention_decode", "attention_decode_paged", "attention_prefill", "kv_append", "kv_append_paged",
+           "cuda_available"]
 
 _PAGED_GROUPS = (1, 2, 4, 8, 16)
 
@@ -237,6 +238,56 @@ def attention_decode(q, k_cache, v_cache, lens=None, *, cuda=False):
         if arr_lens is None:
             raise TypeError("lens must be a host array on this path")
     res = _fusedtok.attention_decode(arr_q, arr_k, arr_v, arr_lens, b, hq, hkv, t_rows, d)
+    return torch.from_numpy(res) if _is_torch(q) else res
+
+
+def attention_prefill(q, k, v, causal=True, *, cuda=False):
+    """Prefill (fresh-sequence) attention over S query rows:
+
+    ``out[b, h, i] = softmax(q[b,h,i] . K[b,kv(h)]^T / sqrt(D)) . V[b,kv(h)]`` where query row i attends key
+    rows ``[0, i]`` (``causal=True``) or all S rows (``causal=False``).
+
+    q: [B, Hq, S, D]; k / v: [B, Hkv, S, D]; out: [B, Hq, S, D]; same GQA mapping and dim rules as
+    :func:`attention_decode`. CUDA tensors may be float32, bfloat16 or float16 (output dtype = input dtype,
+    float32 accumulation). Reference: python/fusedtok/__init__.py:791-846.
+    """
+    if _is_torch(q) and q.is_cuda:
+        for name, t in (("q", q), ("k", k), ("v", v)):
+            _check_torch_att(t, name)
+        for name, t in (("k", k), ("v", v)):
+            if t.dtype is not q.dtype:
+                raise TypeError(f"{name} must have the same dtype as q")
+        if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+            raise ValueError("q/k/v must be [B, heads, S, D]")
+        b, hq, s, d = q.shape
+        b2, hkv, s2, d2 = k.shape
+        if (b2, s2, d2) != (b, s, d) or v.shape != k.shape:
+            raise ValueError("k/v must match q's batch, seq and dim")
+        if hq < 1 or hkv < 1:
+            raise ValueError("head counts must be >= 1")
+        if hq % hkv:
+            raise ValueError("q heads must be a multiple of kv heads")
+        out = torch.empty((b, hq, s, d), dtype=q.dtype, device=q.device)
+        if b * hq * s > 0:
+            with _on_device(q.device):
+                _att_launch_fn(q, "attention_prefill_launch")(
+                    q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), b, hq, hkv, s, d, bool(causal),
+                    _cuda_stream())
+        return out
+    if not cuda:
+        _no_cpu_path()
+    arr_q = _as_numpy(q, "q")
+    arr_k = _as_numpy(k, "k")
+    arr_v = _as_numpy(v, "v")
+    if arr_q.ndim != 4 or arr_k.ndim != 4 or arr_v.ndim != 4:
+        raise ValueError("q/k/v must be [B, heads, S, D]")
+    b, hq, s, d = arr_q.shape
+    b2, hkv, s2, d2 = arr_k.shape
+    if (b2, s2, d2) != (b, s, d) or arr_v.shape != arr_k.shape:
+        raise ValueError("k/v must match q's batch, seq and dim")
+    if hq % hkv:
+        raise ValueError("q heads must be a multiple of kv heads")
+    res = _fusedtok.attention_prefill(arr_q, arr_k, arr_v, b, hq, hkv, s, d, bool(causal))
     return torch.from_numpy(res) if _is_torch(q) else res
 
 

@@ -41,6 +41,8 @@ for _n in ("", "_bf16", "_fp16"):
 for _n in ("", "_bf16", "_fp16"):
     getattr(_lib, "fusedtok_kv_append_launch" + _n).argtypes = [_vp] * 5 + [_i] * 4 + [_sz]
     getattr(_lib, "fusedtok_kv_append_paged_launch" + _n).argtypes = [_vp] * 6 + [_i] * 5 + [_sz]
+    getattr(_lib, "fusedtok_attention_prefill_launch" + _n).argtypes = [_vp] * 4 + [_i] * 6 + [_sz]
+_lib.fusedtok_attention_prefill.argtypes = [_vp] * 4 + [_i] * 6
 _lib.fusedtok_kv_append.argtypes = [_vp] * 5 + [_i] * 4
 _lib.fusedtok_kv_append_paged.argtypes = [_vp] * 6 + [_i] * 6
 _lib.fusedtok_attention_decode.argtypes = [_vp] * 5 + [_i] * 5
@@ -69,6 +71,8 @@ EXPORTS = (
     "fusedtok_attention_decode_paged_launch", "fusedtok_attention_decode_paged_launch_bf16",
     "fusedtok_attention_decode_paged_launch_fp16",
     "fusedtok_attention_decode", "fusedtok_attention_decode_paged",
+    "fusedtok_attention_prefill_launch", "fusedtok_attention_prefill_launch_bf16",
+    "fusedtok_attention_prefill_launch_fp16", "fusedtok_attention_prefill",
     "fusedtok_kv_append_launch", "fusedtok_kv_append_launch_bf16", "fusedtok_kv_append_launch_fp16",
     "fusedtok_kv_append_paged_launch", "fusedtok_kv_append_paged_launch_bf16",
     "fusedtok_kv_append_paged_launch_fp16", "fusedtok_kv_append", "fusedtok_kv_append_paged",
@@ -125,6 +129,20 @@ attention_decode_launch_fp16 = _make_launch("_fp16")
 attention_decode_paged_launch = _make_paged_launch("")
 attention_decode_paged_launch_bf16 = _make_paged_launch("_bf16")
 attention_decode_paged_launch_fp16 = _make_paged_launch("_fp16")
+
+
+def _make_prefill(suffix):
+    fn = getattr(_lib, "fusedtok_attention_prefill_launch" + suffix)
+
+    def attention_prefill_launch(q, k, v, out, batch, hq, hkv, seq, dim, causal, stream=0):
+        _check(fn(int(q), int(k), int(v), int(out), batch, hq, hkv, seq, dim, 1 if causal else 0, int(stream)))
+    attention_prefill_launch.__name__ = "attention_prefill_launch" + suffix
+    return attention_prefill_launch
+
+
+attention_prefill_launch = _make_prefill("")
+attention_prefill_launch_bf16 = _make_prefill("_bf16")
+attention_prefill_launch_fp16 = _make_prefill("_fp16")
 
 
 def _make_append(suffix):
@@ -197,6 +215,18 @@ def attention_decode_paged(q, k_pool, v_pool, table, lens, batch, hq, hkv, page,
     _check(_lib.fusedtok_attention_decode_paged(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table),
                                                 _ptr(lens), _ptr(out), batch, hq, hkv, page,
                                                 tbl_width, num_blocks, dim))
+    return out
+
+
+def attention_prefill(q, k, v, batch, hq, hkv, seq, dim, causal):
+    """Staged prefill: float32 host arrays in, host array out
+    (reference: src/bindings.cpp:2863-2886)."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    if q.size != batch * hq * seq * dim or k.size != batch * hkv * seq * dim or v.size != k.size:
+        raise ValueError("attention operand size mismatch")
+    out = np.empty((batch, hq, seq, dim), np.float32)
+    _check(_lib.fusedtok_attention_prefill(_ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, hq, hkv, seq, dim,
+                                           1 if causal else 0))
     return out
 
 

@@ -21,6 +21,7 @@
 #include "decode_simt.cuh"
 #include "decode_tc.cuh"
 #include "kv_append.cuh"
+#include "prefill_simt.cuh"
 #include "merge.cuh"
 
 namespace {
@@ -67,6 +68,7 @@ struct DeviceState {
     int* counters = nullptr;                 // per-unit arrival counters, zero between launches
     size_t counters_cap = 0;                 // in units
     bool smem_attr_set = false;
+    bool prefill_attr_set = false;
 };
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mutex;
@@ -105,6 +107,19 @@ int set_all_smem_attrs() {
     FTK_SET_ALL(__half)
 #undef FTK_SET_ALL
 #undef FTK_SET
+    return rc;
+}
+
+int set_prefill_smem_attrs() {
+    int rc = 0;
+#define FTK_SET_PF(T)                                                                                       \
+    if ((rc = set_smem(prefill_simt_kernel<T, 64, 64>, prefill_simt_smem_floats<64, 64>(128) * 4))) return rc; \
+    if ((rc = set_smem(prefill_simt_kernel<T, 32, 32>, prefill_simt_smem_floats<32, 32>(256) * 4))) return rc; \
+    if ((rc = set_smem(prefill_simt_kernel<T, 16, 16>, prefill_simt_smem_floats<16, 16>(512) * 4))) return rc;
+    FTK_SET_PF(float)
+    FTK_SET_PF(__nv_bfloat16)
+    FTK_SET_PF(__half)
+#undef FTK_SET_PF
     return rc;
 }
 
@@ -429,6 +444,56 @@ int kv_append_common(int dt, const void* k_new, const void* v_new, const int* ta
     return check_launch("kv append kernel launch");
 }
 
+// Prefill launcher. reference: attention_prefill_launch_t, src/attention.cu:1649-1712.
+template <typename T> void launch_prefill_simt_t(const PrefillParams& p0, cudaStream_t cs) {
+    PrefillParams p = p0;
+    const long long nbh = (long long)p.B * p.Hq;
+    if (p.D <= 128) {
+        p.q_tiles = (p.S + 63) / 64;
+        prefill_simt_kernel<T, 64, 64><<<(unsigned)(nbh * p.q_tiles), 256, prefill_simt_smem_floats<64, 64>(p.D) * 4, cs>>>(p);
+    } else if (p.D <= 256) {
+        p.q_tiles = (p.S + 31) / 32;
+        prefill_simt_kernel<T, 32, 32><<<(unsigned)(nbh * p.q_tiles), 256, prefill_simt_smem_floats<32, 32>(p.D) * 4, cs>>>(p);
+    } else {
+        p.q_tiles = (p.S + 15) / 16;
+        prefill_simt_kernel<T, 16, 16><<<(unsigned)(nbh * p.q_tiles), 256, prefill_simt_smem_floats<16, 16>(p.D) * 4, cs>>>(p);
+    }
+}
+
+int prefill_common(int dt, const void* q, const void* k, const void* v, void* out, int batch, int hq, int hkv,
+                   int seq, int dim, int causal, uintptr_t stream) {
+    int rc = attention_check(batch, hq, hkv, seq, dim);
+    if (rc) return rc;
+    if (batch == 0 || seq == 0) return FUSEDTOK_OK;           // nothing to compute (src/attention.cu:1654)
+    if (!q || !k || !v || !out) return fail(FUSEDTOK_INVALID_ARGUMENT, "null attention operand");
+    const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                          reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out);
+    if (all & (4 * dtype_size(dt) - 1))
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "prefill operands must be aligned to 4 elements");
+    const long long q_tiles_min = ((long long)seq + 63) / 64;
+    if ((long long)batch * hq * q_tiles_min * 4 > 0x7fffffffLL || (long long)seq * dim > 0x7fffffffLL)
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "prefill shape too large for one launch");
+    DeviceState* dev = nullptr;
+    if ((rc = device_state(&dev))) return rc;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (!dev->prefill_attr_set) {
+            if ((rc = set_prefill_smem_attrs())) return rc;
+            dev->prefill_attr_set = true;
+        }
+    }
+    cudaStream_t cs = (cudaStream_t)stream;
+    PrefillParams p{};
+    p.q = q; p.k = k; p.v = v; p.out = out;
+    p.B = batch; p.Hq = hq; p.Hkv = hkv; p.G = hq / hkv; p.S = seq; p.D = dim;
+    p.causal = causal ? 1 : 0;
+    p.scale = 1.0f / sqrtf((float)dim);
+    if (dt == F32) launch_prefill_simt_t<float>(p, cs);
+    else if (dt == BF16) launch_prefill_simt_t<__nv_bfloat16>(p, cs);
+    else launch_prefill_simt_t<__half>(p, cs);
+    return check_launch("attention prefill kernel launch");
+}
+
 // RAII device buffer for the staged paths (reference: DevBuf, src/bindings.cpp:47-66)
 struct DevBuf {
     void* p = nullptr;
@@ -567,6 +632,43 @@ int fusedtok_attention_decode_paged(const float* q, const float* k_pool, const f
     if (rc) return rc;
     if ((e = cudaMemcpy(out, dy.p, q_b, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("D2H copy failed", e);
     if ((e = cudaDeviceSynchronize()) != cudaSuccess) return cuda_fail("attention decode paged kernel failed", e);
+    return FUSEDTOK_OK;
+}
+
+int fusedtok_attention_prefill_launch(const float* q, const float* k, const float* v, float* out, int batch,
+                                      int q_heads, int kv_heads, int seq, int dim, int causal, uintptr_t stream) {
+    return prefill_common(F32, q, k, v, out, batch, q_heads, kv_heads, seq, dim, causal, stream);
+}
+int fusedtok_attention_prefill_launch_bf16(const void* q, const void* k, const void* v, void* out, int batch,
+                                           int q_heads, int kv_heads, int seq, int dim, int causal,
+                                           uintptr_t stream) {
+    return prefill_common(BF16, q, k, v, out, batch, q_heads, kv_heads, seq, dim, causal, stream);
+}
+int fusedtok_attention_prefill_launch_fp16(const void* q, const void* k, const void* v, void* out, int batch,
+                                           int q_heads, int kv_heads, int seq, int dim, int causal,
+                                           uintptr_t stream) {
+    return prefill_common(F16, q, k, v, out, batch, q_heads, kv_heads, seq, dim, causal, stream);
+}
+
+int fusedtok_attention_prefill(const float* q, const float* k, const float* v, float* out, int batch, int q_heads,
+                               int kv_heads, int seq, int dim, int causal) {
+    int rc = attention_check(batch, q_heads, kv_heads, seq, dim);
+    if (rc) return rc;
+    const size_t q_b = (size_t)batch * q_heads * seq * dim * 4;
+    const size_t kv_b = (size_t)batch * kv_heads * seq * dim * 4;
+    if (q_b == 0) return FUSEDTOK_OK;
+    DevBuf dq(q_b), dk(kv_b), dv(kv_b), dy(q_b);
+    for (const DevBuf* b : {&dq, &dk, &dv, &dy})
+        if (b->err != cudaSuccess) return cuda_fail("cudaMalloc failed", b->err);
+    cudaError_t e;
+    if ((e = cudaMemcpy(dq.p, q, q_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if ((e = cudaMemcpy(dk.p, k, kv_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if ((e = cudaMemcpy(dv.p, v, kv_b, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    rc = fusedtok_attention_prefill_launch((const float*)dq.p, (const float*)dk.p, (const float*)dv.p, (float*)dy.p,
+                                           batch, q_heads, kv_heads, seq, dim, causal, 0);
+    if (rc) return rc;
+    if ((e = cudaMemcpy(out, dy.p, q_b, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("D2H copy failed", e);
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return cuda_fail("attention prefill kernel failed", e);
     return FUSEDTOK_OK;
 }
 

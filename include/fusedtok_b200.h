@@ -99,6 +99,26 @@ int fusedtok_attention_decode_paged(const float* q, const float* k_pool, const f
                                     int q_heads, int kv_heads, int page, int tbl_width,
                                     int num_blocks, int dim);
 
+/* ---- prefill: fresh-sequence self-attention over S query rows ---------------
+ * q / out [B, Hq, S, D]; k / v [B, Hkv, S, D]; query row i attends key rows
+ * [0, i] when causal != 0, all S rows otherwise; same GQA mapping and shape
+ * rules as decode. Device pointers (aligned to 4 elements), asynchronous on
+ * `stream`, capturable, no workspace. Replace fusedtok::attention_prefill_launch
+ * / _bf16 / _fp16, include/fusedtok/cuda_launch.hpp:362-379
+ * (src/attention.cu:1649-1739). The staged form takes HOST float32 buffers
+ * and returns after the result is back (src/bindings.cpp:2863-2886). */
+int fusedtok_attention_prefill_launch(const float* q, const float* k, const float* v, float* out,
+                                      int batch, int q_heads, int kv_heads, int seq, int dim,
+                                      int causal, uintptr_t stream);
+int fusedtok_attention_prefill_launch_bf16(const void* q, const void* k, const void* v, void* out,
+                                           int batch, int q_heads, int kv_heads, int seq, int dim,
+                                           int causal, uintptr_t stream);
+int fusedtok_attention_prefill_launch_fp16(const void* q, const void* k, const void* v, void* out,
+                                           int batch, int q_heads, int kv_heads, int seq, int dim,
+                                           int causal, uintptr_t stream);
+int fusedtok_attention_prefill(const float* q, const float* k, const float* v, float* out,
+                               int batch, int q_heads, int kv_heads, int seq, int dim, int causal);
+
 /* ---- kv-cache append: the write side of the decode loop --------------------
  * Scatter ONE fresh token's K and V rows per sequence (k_new, v_new
  * [B, Hkv, D]) into the cache at position lens[b] (lens is required):

@@ -40,6 +40,7 @@ def _load():
             [_fp, _fp, _fp, _ip, _ip, _fp] + [_i] * 7)
         _lib.oracle_attention_partial.argtypes = [_fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i]
         _lib.oracle_attention_merge.argtypes = [_fp, _fp, _i, _i, _fp]
+        _lib.oracle_attention_prefill.argtypes = [_fp, _fp, _fp, _fp] + [_i] * 6
         _lib.oracle_kv_append.argtypes = [_fp, _fp, _ip, _fp, _fp] + [_i] * 4
         _lib.oracle_kv_append_paged.argtypes = [_fp, _fp, _ip, _ip, _fp, _fp] + [_i] * 6
     return _lib
@@ -64,6 +65,9 @@ def _load_ref():
             _ref.ref_kv_append_cpu.argtypes = [_fp, _fp, _ip, _fp, _fp] + [_i] * 4
             _ref.ref_kv_append_paged_cpu.argtypes = [_fp, _fp, _ip, _ip, _fp, _fp] + [_i] * 6
         vp = ctypes.c_void_p
+        if hasattr(_ref, "ref_attention_prefill_cpu"):
+            _ref.ref_attention_prefill_cpu.argtypes = [_fp, _fp, _fp, _fp] + [_i] * 6
+            _ref.ref_attention_prefill_launch.argtypes = [_i, vp, vp, vp, vp] + [_i] * 6 + [ctypes.c_size_t]
         _ref.ref_attention_decode_launch.argtypes = (
             [_i, vp, vp, vp, vp, vp] + [_i] * 5 + [ctypes.c_size_t])
         _ref.ref_attention_decode_paged_launch.argtypes = (
@@ -132,6 +136,36 @@ def ref_decode_paged(q, k_pool, v_pool, table, lens=None):
     """The reference's own attention_decode_paged_cpu (src/attention.cu:1382-1456)."""
     return _decode_paged(_load_ref().ref_attention_decode_paged_cpu, q, k_pool,
                          v_pool, table, lens)
+
+
+def _prefill(fn, q, k, v, causal):
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    b, hq, s, d = q.shape
+    hkv = k.shape[1]
+    out = np.empty((b, hq, s, d), np.float32)
+    rc = fn(_pf(q), _pf(k), _pf(v), _pf(out), b, hq, hkv, s, d, 1 if causal else 0)
+    if rc:
+        raise ValueError("oracle rejected the arguments (code %d)" % rc)
+    return out
+
+
+def prefill(q, k, v, causal=True):
+    """Fresh-sequence prefill attention through the C restatement."""
+    return _prefill(_load().oracle_attention_prefill, q, k, v, causal)
+
+
+def ref_prefill(q, k, v, causal=True):
+    """The reference's own attention_prefill_cpu (src/attention.cu:1591-1638)."""
+    return _prefill(_load_ref().ref_attention_prefill_cpu, q, k, v, causal)
+
+
+def ref_gpu_prefill_launch(dtype_code, q_ptr, k_ptr, v_ptr, out_ptr, b, hq, hkv, s, d, causal, stream):
+    """The reference's prefill GPU launcher on raw device pointers (timing only)."""
+    r = _load_ref()
+    rc = r.ref_attention_prefill_launch(dtype_code, q_ptr, k_ptr, v_ptr, out_ptr, b, hq, hkv, s, d,
+                                        1 if causal else 0, stream)
+    if rc:
+        raise RuntimeError(r.ref_last_error().decode())
 
 
 def partial(q_row, k_rows, v_rows, t0, t1):

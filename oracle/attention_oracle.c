@@ -305,3 +305,55 @@ int oracle_kv_append_paged(const float *k_new, const float *v_new,
     }
     return 0;
 }
+
+/*
+ * Prefill (fresh-sequence self-attention over S query rows), restating
+ * attention_prefill_cpu (reference: src/attention.cu:1591-1638).
+ * q / out [B, Hq, S, D]; k / v [B, Hkv, S, D]. Query row i attends key rows
+ * [0, i] when causal, all S rows otherwise. Per row the same three passes as
+ * decode: scores and max, sum of expf, then out += (expf(s - m) / l) * V[t].
+ */
+int oracle_attention_prefill(const float *q, const float *k, const float *v,
+                             float *out, int batch, int hq, int hkv, int seq,
+                             int dim, int causal)
+{
+    if (oracle_check(batch, hq, hkv, seq, dim))
+        return 1;
+    const int group = hq / hkv;
+    const float scale = 1.0f / sqrtf((float)dim);
+    const size_t qn = (size_t)batch * hq * seq * dim;
+    memset(out, 0, qn * sizeof(float));
+    float *scores = (float *)malloc(sizeof(float) * (seq > 0 ? seq : 1));
+    if (!scores)
+        return 2;
+    for (int bi = 0; bi < batch; ++bi)
+        for (int h = 0; h < hq; ++h) {
+            const int kv = h / group;
+            const float *qp = q + (((size_t)bi * hq + h) * seq) * dim;
+            const float *kp = k + (((size_t)bi * hkv + kv) * seq) * dim;
+            const float *vp = v + (((size_t)bi * hkv + kv) * seq) * dim;
+            for (int i = 0; i < seq; ++i) {
+                const int lim = causal ? i + 1 : seq;
+                const float *qr = qp + (size_t)i * dim;
+                float m = -INFINITY;
+                for (int t = 0; t < lim; ++t) {
+                    float dot = 0.0f;
+                    for (int d = 0; d < dim; ++d)
+                        dot += qr[d] * kp[(size_t)t * dim + d];
+                    scores[t] = dot * scale;
+                    m = fmaxf(m, scores[t]);
+                }
+                float l = 0.0f;
+                for (int t = 0; t < lim; ++t)
+                    l += expf(scores[t] - m);
+                float *op = out + (((size_t)bi * hq + h) * seq + i) * dim;
+                for (int t = 0; t < lim; ++t) {
+                    const float p = expf(scores[t] - m) / l;
+                    for (int d = 0; d < dim; ++d)
+                        op[d] += p * vp[(size_t)t * dim + d];
+                }
+            }
+        }
+    free(scores);
+    return 0;
+}

@@ -110,6 +110,19 @@ int ref_kv_append_paged_cpu(const float* k_new, const float* v_new, const int* t
     });
 }
 
+// reference: fusedtok::attention_prefill_cpu, src/attention.cu:1591-1638
+int ref_attention_prefill_cpu(const float* q, const float* k, const float* v, float* out, int batch,
+                              int hq, int hkv, int seq, int dim, int causal) {
+    return guarded([&] {
+        if (batch < 0 || hq < 0 || hkv < 0 || seq < 0 || dim < 0)
+            throw std::invalid_argument("negative shape");
+        const size_t nq = (size_t)batch * hq * seq * dim, nkv = (size_t)batch * hkv * seq * dim;
+        std::vector<float> qv(q, q + nq), kv(k, k + nkv), vv(v, v + nkv);
+        std::vector<float> y = fusedtok::attention_prefill_cpu(qv, kv, vv, batch, hq, hkv, seq, dim, causal != 0);
+        if (!y.empty()) std::memcpy(out, y.data(), y.size() * sizeof(float));
+    });
+}
+
 // The reference GPU launchers, device pointers in, asynchronous on `stream`.
 // dtype: 0 = float32, 1 = bfloat16, 2 = float16.
 int ref_attention_decode_launch(int dtype, const void* q, const void* k,
@@ -150,6 +163,21 @@ int ref_attention_decode_paged_launch(int dtype, const void* q,
             fusedtok::attention_decode_paged_launch_fp16(
                 q, k_pool, v_pool, table, lens, out, batch, hq, hkv, page,
                 tbl_width, dim, stream);
+    });
+}
+
+// reference: attention_prefill_launch{,_bf16,_fp16}, include/fusedtok/cuda_launch.hpp:362-379
+int ref_attention_prefill_launch(int dtype, const void* q, const void* k, const void* v, void* out,
+                                 int batch, int hq, int hkv, int seq, int dim, int causal,
+                                 std::uintptr_t stream) {
+    return guarded([&] {
+        if (dtype == 0)
+            fusedtok::attention_prefill_launch((const float*)q, (const float*)k, (const float*)v, (float*)out,
+                                               batch, hq, hkv, seq, dim, causal != 0, stream);
+        else if (dtype == 1)
+            fusedtok::attention_prefill_launch_bf16(q, k, v, out, batch, hq, hkv, seq, dim, causal != 0, stream);
+        else
+            fusedtok::attention_prefill_launch_fp16(q, k, v, out, batch, hq, hkv, seq, dim, causal != 0, stream);
     });
 }
 

@@ -70,6 +70,28 @@ PAGED_CASES = {
 }
 
 
+# (batch, q heads, kv heads, seq, dim) - the reference's PREFILL_SHAPES,
+# tests/test_attention.py:176-184
+PREFILL_SHAPES = [
+    (1, 4, 2, 1, 32),
+    (1, 8, 8, 5, 64),
+    (2, 6, 3, 17, 16),
+    (1, 32, 8, 40, 128),
+    (1, 4, 1, 33, 8),
+    (1, 8, 2, 64, 256),
+    (1, 4, 2, 9, 512),
+]
+
+
+def make_prefill_case(b, hq, hkv, s, d, causal):
+    """Seed and generators of tests/test_attention.py:191-196."""
+    rng = np.random.default_rng(b * 100 + hq * 17 + s * 3 + d + int(causal))
+    q = rng.standard_normal((b, hq, s, d)).astype(np.float32)
+    k = rng.standard_normal((b, hkv, s, d)).astype(np.float32)
+    v = rng.standard_normal((b, hkv, s, d)).astype(np.float32)
+    return q, k, v
+
+
 def round_to(x, dtype):
     """Round float32 values to bf16 / fp16 storage and widen back to float32:
     the 'half-rounded inputs' the oracle is fed for half-precision cases."""

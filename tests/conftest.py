@@ -18,3 +18,10 @@ def golden():
     import numpy as np
     path = os.path.join(ROOT, "tests", "golden", "decode_golden.npz")
     return dict(np.load(path))
+
+
+@pytest.fixture(scope="session")
+def prefill_golden():
+    import numpy as np
+    path = os.path.join(ROOT, "tests", "golden", "prefill_golden.npz")
+    return dict(np.load(path))

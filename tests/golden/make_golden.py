@@ -62,6 +62,22 @@ def main():
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes,", len(out), "entries")
 
+    # prefill: full outputs for the small shapes, a digest of the output bytes for the large ones
+    # (parity of the restatement is bit-exact, so a digest pins it just as well)
+    pre = {}
+    for (b, hq, hkv, s, d) in cases.PREFILL_SHAPES:
+        for causal in (True, False):
+            q, k, v = cases.make_prefill_case(b, hq, hkv, s, d, causal)
+            y = oracle.ref_prefill(q, k, v, causal)
+            name = "prefill_%d_%d_%d_%d_%d_%d" % (b, hq, hkv, s, d, int(causal))
+            if y.size <= 20000:
+                pre[name] = y
+            pre[name + "_out_sum"] = digest(y)
+            pre[name + "_sum"] = digest(q, k, v)
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "prefill_golden.npz")
+    np.savez_compressed(path, **pre)
+    print("wrote", path, os.path.getsize(path), "bytes,", len(pre), "entries")
+
 
 if __name__ == "__main__":
     main()
