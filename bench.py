@@ -598,7 +598,35 @@ def run_reference_rows(args):
                 row["reference_kernel_us"] = ref
                 row["speedup_vs_reference_kernel"] = ref / ours
             rows.append(row)
-    print(json.dumps({"benchmark": "reference attention-decode rows on this GPU", "protocol":
+    # prefill rows (benchmarks/bench.py:518-541: batch 1, 32/8 heads, D=128, S=1024, causal), plus longer
+    # sequences where the operator is compute-bound; FLOPs = 4*S*S*D*Hq/2 (causal half)
+    for s_len, batch in ((1024, 1), (4096, 1), (8192, 2)):
+        for dt, code, name in ((torch.float32, 0, "attn prefill"), (torch.bfloat16, 1, "attn prefill bf16")):
+            if dt is torch.float32 and s_len > 4096:
+                continue
+            qp = torch.randn(batch, hq, s_len, d, device="cuda").to(dt)
+            kp_ = torch.randn(batch, hkv, s_len, d, device="cuda").to(dt)
+            vp_ = torch.randn(batch, hkv, s_len, d, device="cuda").to(dt)
+            kk = kp_.repeat_interleave(hq // hkv, dim=1)
+            vv = vp_.repeat_interleave(hq // hkv, dim=1)
+            iters = max(3, args.steps // 8) if s_len <= 1024 else 3
+            flops = 4.0 * s_len * s_len * d * hq * batch / 2
+            ours = timeit(lambda: ft.attention_prefill(qp, kp_, vp_, causal=True), iters)
+            sdpa = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(qp, kk, vv, is_causal=True), iters)
+            row = {"op": name, "shape": "B=%d S=%d" % (batch, s_len), "us": ours, "TFLOPs": flops / ours / 1e6,
+                   "sdpa_us": sdpa, "speedup_vs_sdpa": sdpa / ours}
+            if have_ref:
+                out = torch.empty_like(qp)
+                st = torch.cuda.current_stream().cuda_stream
+                ref = timeit(lambda: oracle.ref_gpu_prefill_launch(code, qp.data_ptr(), kp_.data_ptr(), vp_.data_ptr(),
+                                                                   out.data_ptr(), batch, hq, hkv, s_len, d, True, st),
+                             iters)
+                row["reference_kernel_us"] = ref
+                row["speedup_vs_reference_kernel"] = ref / ours
+                row["max_abs_vs_reference_kernel"] = (out.float() - ft.attention_prefill(qp, kp_, vp_).float()).abs().max().item()
+            rows.append(row)
+            del qp, kp_, vp_, kk, vv
+    print(json.dumps({"benchmark": "reference attention decode / prefill rows on this GPU", "protocol":
                       "3 rounds x own warm-up, CUDA events, mean; public Python operator; same tensors every iteration",
                       "gpu": torch.cuda.get_device_name(0), "rows": rows}), flush=True)
 

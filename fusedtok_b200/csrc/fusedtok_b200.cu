@@ -13,6 +13,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -22,6 +23,7 @@
 #include "decode_tc.cuh"
 #include "kv_append.cuh"
 #include "prefill_simt.cuh"
+#include "prefill_tc.cuh"
 #include "merge.cuh"
 
 namespace {
@@ -120,6 +122,10 @@ int set_prefill_smem_attrs() {
     FTK_SET_PF(__nv_bfloat16)
     FTK_SET_PF(__half)
 #undef FTK_SET_PF
+    if ((rc = set_smem(prefill_tc_kernel<__nv_bfloat16, 64>, PfCfg<64>::SMEM_BYTES))) return rc;
+    if ((rc = set_smem(prefill_tc_kernel<__nv_bfloat16, 128>, PfCfg<128>::SMEM_BYTES))) return rc;
+    if ((rc = set_smem(prefill_tc_kernel<__half, 64>, PfCfg<64>::SMEM_BYTES))) return rc;
+    if ((rc = set_smem(prefill_tc_kernel<__half, 128>, PfCfg<128>::SMEM_BYTES))) return rc;
     return rc;
 }
 
@@ -444,6 +450,39 @@ int kv_append_common(int dt, const void* k_new, const void* v_new, const int* ta
     return check_launch("kv append kernel launch");
 }
 
+// FUSEDTOK_PREFILL_SIMT=1 in the environment keeps half-precision prefill on the CUDA-core kernel
+// (diagnostics: the two kernels can then be compared on the same inputs).
+const bool g_prefill_force_simt = [] {
+    const char* e = std::getenv("FUSEDTOK_PREFILL_SIMT");
+    return e && e[0] == '1';
+}();
+
+// One head's rows as a rank-4 tensor: (64 elements, S rows, D/64 column blocks of 128 bytes, heads). A box
+// [64, 128, D/64, 1] is one tile of one head; rows past S are zero-filled by the copy.
+int encode_head_map(CUtensorMap* map, int dt, const void* base, int seq, int dim, long long heads) {
+    const cuuint64_t gdim[4] = {64u, (cuuint64_t)seq, (cuuint64_t)(dim / 64), (cuuint64_t)heads};
+    const cuuint64_t gstride[3] = {(cuuint64_t)dim * 2, 128u, (cuuint64_t)seq * dim * 2};
+    const cuuint32_t box[4] = {64u, 128u, (cuuint32_t)(dim / 64), 1u};
+    const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    const CUresult r = g_encode(map, dt == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                4, const_cast<void*>(base), gdim, gstride, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(FUSEDTOK_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed (code " + std::to_string((int)r) + ")");
+    return FUSEDTOK_OK;
+}
+
+template <typename T>
+void launch_prefill_tc_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
+                         int* status, cudaStream_t cs) {
+    const unsigned grid = (unsigned)((long long)p.B * p.Hq * p.q_tiles);
+    if (p.D == 64)
+        prefill_tc_kernel<T, 64><<<grid, PF_THREADS, PfCfg<64>::SMEM_BYTES, cs>>>(mq, mk, mv, p, status);
+    else
+        prefill_tc_kernel<T, 128><<<grid, PF_THREADS, PfCfg<128>::SMEM_BYTES, cs>>>(mq, mk, mv, p, status);
+}
+
 // Prefill launcher. reference: attention_prefill_launch_t, src/attention.cu:1649-1712.
 template <typename T> void launch_prefill_simt_t(const PrefillParams& p0, cudaStream_t cs) {
     PrefillParams p = p0;
@@ -488,6 +527,32 @@ int prefill_common(int dt, const void* q, const void* k, const void* v, void* ou
     p.B = batch; p.Hq = hq; p.Hkv = hkv; p.G = hq / hkv; p.S = seq; p.D = dim;
     p.causal = causal ? 1 : 0;
     p.scale = 1.0f / sqrtf((float)dim);
+    // tensor-core path: half storage, head dim 64 / 128, 16-byte aligned operands
+    const bool use_tc = dt != F32 && (dim == 64 || dim == 128) && (all & 15u) == 0 && !g_prefill_force_simt;
+    if (use_tc) {
+        if ((rc = get_encode_fn())) return rc;
+        {
+            std::lock_guard<std::mutex> lock(g_mutex);
+            if (!dev->status) {
+                if (stream_is_capturing(cs))
+                    return fail(FUSEDTOK_RUNTIME_ERROR,
+                                "the status word must be allocated outside a CUDA graph capture - warm the "
+                                "shape up once before capturing");
+                cudaError_t e = cudaMalloc(&dev->status, 256);
+                if (e != cudaSuccess) return cuda_fail("status word allocation failed", e);
+                e = cudaMemset(dev->status, 0, 256);
+                if (e != cudaSuccess) return cuda_fail("status word clear failed", e);
+            }
+        }
+        CUtensorMap mq, mk, mv;
+        if ((rc = encode_head_map(&mq, dt, q, seq, dim, (long long)batch * hq))) return rc;
+        if ((rc = encode_head_map(&mk, dt, k, seq, dim, (long long)batch * hkv))) return rc;
+        if ((rc = encode_head_map(&mv, dt, v, seq, dim, (long long)batch * hkv))) return rc;
+        p.q_tiles = (seq + 127) / 128;
+        if (dt == BF16) launch_prefill_tc_t<__nv_bfloat16>(mq, mk, mv, p, dev->status, cs);
+        else launch_prefill_tc_t<__half>(mq, mk, mv, p, dev->status, cs);
+        return check_launch("attention prefill kernel launch");
+    }
     if (dt == F32) launch_prefill_simt_t<float>(p, cs);
     else if (dt == BF16) launch_prefill_simt_t<__nv_bfloat16>(p, cs);
     else launch_prefill_simt_t<__half>(p, cs);

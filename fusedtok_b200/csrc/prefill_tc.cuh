@@ -1,0 +1,330 @@
+// Prefill (fresh-sequence self-attention) on the 5th-generation tensor cores: bf16 / fp16 storage,
+// head dim 64 or 128.
+//
+// Operator: see prefill_simt.cuh (reference: attention_prefill_launch_bf16 / _fp16,
+// include/fusedtok/cuda_launch.hpp:370-379; the reference's own tensor-core path is the mma.sync kernel at
+// src/attention.cu:951-1217).
+//
+// One CTA owns 128 query rows of one (batch, query head) and walks the key/value rows in tiles of 128:
+//
+//   warp 5  (producer)   TMA: the Q tile once, then K and V tiles into a 2-stage ring. Rank-4 tensor maps
+//                        (64 elements, S rows, D/64 column blocks, B*H heads): rows past the end of a head are
+//                        zero-filled by the copy engine, tiles land as [column block][row][128 B], 128-byte
+//                        swizzled - exactly the K-major (Q, K) and MN-major (V) operand layouts of tcgen05.mma.
+//   warp 4  (MMA issue)  one elected thread: S = Q.K^T (M=128, N=128, K=D) into tensor memory, and after the
+//                        softmax warps have produced P: O_tile = P.V (M=128, N=D, K=128) into tensor memory;
+//                        completion is signalled by tcgen05.commit on mbarriers.
+//   warps 0-3 (softmax)  thread t owns query row t = tensor-memory lane t: reads its S row with tcgen05.ld
+//                        (no shuffles), online softmax in fp32, writes P as bf16/fp16 into shared memory in the
+//                        swizzled K-major operand layout, then folds O_tile into its fp32 output row
+//                        (acc = acc*alpha + O_tile) and finally stores the row divided by the softmax sum.
+//
+// Tensor memory: 256 columns (S: 128, O_tile: D). Every wait is bounded (2 s): on expiry the kernel records a
+// status code, all roles leave their loops, tensor memory is released and the kernel returns.
+#pragma once
+
+#include "decode_tc.cuh"
+#include "prefill_simt.cuh"
+
+namespace ftk {
+
+constexpr int PF_THREADS = 192;
+constexpr int ST_PREFILL_TIMEOUT = 6;
+
+template <int D> struct PfCfg {
+    static_assert(D == 64 || D == 128, "tensor-core prefill: head dim 64 or 128");
+    static constexpr int BM = 128, BN = 128, NST = 2;
+    static constexpr int PANEL = 128 * 128;                    // bytes: 128 rows x 128 B
+    static constexpr int TILE_BYTES = (D / 64) * PANEL;        // one Q, K or V tile
+    static constexpr int P_BYTES = 2 * PANEL;                  // 128 x 128 probabilities
+    static constexpr int OFF_Q = 0;
+    static constexpr int OFF_K = OFF_Q + TILE_BYTES;
+    static constexpr int OFF_V = OFF_K + NST * TILE_BYTES;
+    static constexpr int OFF_P = OFF_V + NST * TILE_BYTES;
+    static constexpr int OFF_BAR = OFF_P + P_BYTES;            // 10 mbarriers
+    static constexpr int OFF_TMEM = OFF_BAR + 16 * 8;
+    static constexpr int OFF_ABORT = OFF_TMEM + 8;
+    static constexpr int SMEM_BYTES = OFF_ABORT + 8 + 1024;    // + slack to align the base to 1024 B
+    static constexpr uint32_t TMEM_COLS = 256;
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
+};
+
+// ---- tcgen05 wrappers -------------------------------------------------------
+// Shared-memory matrix descriptor, 128-byte swizzle: start address, leading/stride byte offsets (all >> 4),
+// descriptor version 1 (bits 46-47), layout type 2 = SWIZZLE_128B (bits 61-63).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: fp32 accumulate (bits 4-5 = 1), A/B format (bits 7-9 / 10-12: 0 = f16,
+// 1 = bf16), A/B major (bits 15 / 16: 0 = K-major, 1 = MN-major), N >> 3 (bits 17-22), M >> 4 (bits 24-28).
+__host__ __device__ constexpr uint32_t umma_idesc(int fmt, int a_mn, int b_mn, int m, int n) {
+    return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)a_mn << 15) |
+           ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// 32 consecutive fp32 columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&x)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(r[i]);
+}
+// Wait that ignores the abort flag: used on the way out, so that no copy or MMA of this CTA is still in
+// flight when its shared and tensor memory are given back. Bounded all the same.
+__device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return;
+    const unsigned long long t0 = global_ns();
+    while (!mbar_try_wait(bar, parity))
+        if (global_ns() - t0 > WAIT_LIMIT_NS) return;
+}
+// Box [64 elements, 128 rows, D/64 column blocks, 1 head] at (row, head).
+__device__ __forceinline__ void tma_load_tile4(uint32_t dst, const CUtensorMap* map, int row, int head, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(map), "r"(0), "r"(row), "r"(0), "r"(head), "r"(bar)
+        : "memory");
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(PF_THREADS, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const PrefillParams p, int* status) {
+    using C = PfCfg<D>;
+    extern __shared__ uint8_t pf_smem_raw[];
+    const uint32_t raw = smem_u32(pf_smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gbase = pf_smem_raw + (base - raw);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + C::OFF_ABORT);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + C::OFF_TMEM);
+    auto bar = [&](int i) { return base + C::OFF_BAR + 8u * i; };
+    enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_EMPTY = 5, B_SFULL = 7, B_PREADY = 8, B_OFULL = 9, B_DRAIN = 10 };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nbh = p.B * p.Hq;
+    const int qt = p.q_tiles - 1 - (int)(blockIdx.x / nbh);     // long (late) row tiles first
+    const int bh = blockIdx.x % nbh;
+    const int b = bh / p.Hq, h = bh - b * p.Hq;
+    const int kv_head = b * p.Hkv + h / p.G;
+    const int q0 = qt * C::BM;
+    const int kv_end = p.causal ? min(p.S, q0 + C::BM) : p.S;
+    const int n_tiles = (kv_end + C::BN - 1) / C::BN;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(bar(B_QFULL), 1);
+        for (int s = 0; s < C::NST; ++s) {
+            mbar_init(bar(B_KFULL + s), 1);
+            mbar_init(bar(B_VFULL + s), 1);
+            mbar_init(bar(B_EMPTY + s), 1);
+        }
+        mbar_init(bar(B_SFULL), 1);
+        mbar_init(bar(B_PREADY), 128);
+        mbar_init(bar(B_OFULL), 1);
+        mbar_init(bar(B_DRAIN), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(base + C::OFF_TMEM), "r"(C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
+
+    if (warp == 5) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            mbar_expect_tx(bar(B_QFULL), C::TILE_BYTES);
+            tma_load_tile4(base + C::OFF_Q, &tm_q, q0, bh, bar(B_QFULL));
+            int issued = 0;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                if (j >= C::NST &&
+                    !mbar_wait(bar(B_EMPTY + s), ((j / C::NST) - 1) & 1, abort_flag, status, ST_PREFILL_TIMEOUT))
+                    break;
+                mbar_expect_tx(bar(B_KFULL + s), C::TILE_BYTES);
+                tma_load_tile4(base + C::OFF_K + s * C::TILE_BYTES, &tm_k, j * C::BN, kv_head, bar(B_KFULL + s));
+                mbar_expect_tx(bar(B_VFULL + s), C::TILE_BYTES);
+                tma_load_tile4(base + C::OFF_V + s * C::TILE_BYTES, &tm_v, j * C::BN, kv_head, bar(B_VFULL + s));
+                issued = j + 1;
+            }
+            // every copy issued has landed before the CTA gives its shared memory back
+            mbar_wait_drain(bar(B_QFULL), 0);
+            for (int j = max(0, issued - C::NST); j < issued; ++j) {
+                mbar_wait_drain(bar(B_KFULL + (j & 1)), (j / C::NST) & 1);
+                mbar_wait_drain(bar(B_VFULL + (j & 1)), (j / C::NST) & 1);
+            }
+        }
+    } else if (warp == 4) {
+        // ------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+            constexpr uint32_t IDESC_S = umma_idesc(FMT, 0, 0, 128, 128);     // Q (K-major) x K^T (K-major)
+            constexpr uint32_t IDESC_O = umma_idesc(FMT, 0, 1, 128, D);       // P (K-major) x V (MN-major)
+            bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, status, ST_PREFILL_TIMEOUT);
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                const int s = j & 1;
+                const uint32_t ph = (j / C::NST) & 1;
+                if (!(ok = mbar_wait(bar(B_KFULL + s), ph, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
+                tc_fence_after();
+                const uint32_t qa = base + C::OFF_Q, ka = base + C::OFF_K + s * C::TILE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * C::PANEL + (ks & 3) * 32;
+                    umma_f16(tmem_s, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024),
+                             IDESC_S, ks > 0);
+                }
+                umma_commit(bar(B_SFULL));
+                if (!(ok = mbar_wait(bar(B_PREADY), j & 1, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
+                if (!(ok = mbar_wait(bar(B_VFULL + s), ph, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
+                tc_fence_after();
+                const uint32_t pa = base + C::OFF_P, va = base + C::OFF_V + s * C::TILE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < C::BN / 16; ++ks) {
+                    const uint32_t aoff = (ks >> 2) * C::PANEL + (ks & 3) * 32;
+                    umma_f16(tmem_o, umma_desc_sw128(pa + aoff, 16, 1024),
+                             umma_desc_sw128(va + ks * 2048, C::PANEL, 1024), IDESC_O, ks > 0);
+                }
+                umma_commit(bar(B_EMPTY + s));
+                umma_commit(bar(B_OFULL));
+            }
+            // every MMA issued has completed before tensor memory is released
+            umma_commit(bar(B_DRAIN));
+            mbar_wait_drain(bar(B_DRAIN), 0);
+        }
+    } else {
+        // ------------------------------------------------------------ softmax, accumulate, store
+        const int row = threadIdx.x;                        // 0..127 = tensor-memory lane
+        const int r_glob = q0 + row;
+        const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
+        const float sl2 = p.scale * 1.4426950408889634f;
+        float acc[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) acc[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int k0 = j * C::BN;
+            if (!(ok = mbar_wait(bar(B_SFULL), j & 1, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
+            tc_fence_after();
+            const bool need_mask = (k0 + C::BN > p.S) || (p.causal && k0 + C::BN - 1 > q0);
+            const int lim = p.causal ? min(p.S - 1, r_glob) : p.S - 1;   // last live column of this row
+            float x[32];
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld32(tmem_s + lane_base + c * 32, x);
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (k0 + c * 32 + i > lim) x[i] = -INFINITY;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, x[i]);
+            }
+            const float m_new = fmaxf(m_run, mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = ex2((m_run - m_use) * sl2);
+            const float neg_ms = -m_use * sl2;
+            m_run = m_new;
+            float psum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld32(tmem_s + lane_base + c * 32, x);
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (k0 + c * 32 + i > lim) x[i] = -INFINITY;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    x[i] = ex2(fmaf(x[i], sl2, neg_ms));
+                    psum += x[i];
+                }
+                // 32 probabilities = four 16-byte chunks of this row in the swizzled K-major layout
+                const uint32_t prow = base + C::OFF_P + (c >> 1) * C::PANEL + row * 128;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const uint32_t chunk = (uint32_t)((c & 1) * 4 + q4);
+                    const uint32_t addr = prow + ((chunk ^ (uint32_t)(row & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(addr), "r"(pack2<T>(x[q4 * 8 + 0], x[q4 * 8 + 1])),
+                                   "r"(pack2<T>(x[q4 * 8 + 2], x[q4 * 8 + 3])),
+                                   "r"(pack2<T>(x[q4 * 8 + 4], x[q4 * 8 + 5])),
+                                   "r"(pack2<T>(x[q4 * 8 + 6], x[q4 * 8 + 7]))
+                                 : "memory");
+                }
+            }
+            l_run = l_run * alpha + psum;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the tensor core
+            tc_fence_before();
+            mbar_arrive(bar(B_PREADY));
+
+            if (!(ok = mbar_wait(bar(B_OFULL), j & 1, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                tmem_ld32(tmem_o + lane_base + c * 32, x);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, x[i]);
+            }
+            tc_fence_before();
+        }
+        if (ok && r_glob < p.S) {
+            const float inv = 1.0f / l_run;
+            T* orow = static_cast<T*>(p.out) + ((size_t)bh * p.S + r_glob) * D;
+#pragma unroll
+            for (int i = 0; i < D; i += 8) {
+                uint4 u;
+                u.x = pack2<T>(acc[i] * inv, acc[i + 1] * inv);
+                u.y = pack2<T>(acc[i + 2] * inv, acc[i + 3] * inv);
+                u.z = pack2<T>(acc[i + 4] * inv, acc[i + 5] * inv);
+                u.w = pack2<T>(acc[i + 6] * inv, acc[i + 7] * inv);
+                *reinterpret_cast<uint4*>(orow + i) = u;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace ftk
