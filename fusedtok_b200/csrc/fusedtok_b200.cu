@@ -458,11 +458,11 @@ const bool g_prefill_force_simt = [] {
 }();
 
 // One head's rows as a rank-4 tensor: (64 elements, S rows, D/64 column blocks of 128 bytes, heads). A box
-// [64, 128, D/64, 1] is one tile of one head; rows past S are zero-filled by the copy.
-int encode_head_map(CUtensorMap* map, int dt, const void* base, int seq, int dim, long long heads) {
+// [64, box rows, D/64, 1] is one tile of one head; rows past S are zero-filled by the copy.
+int encode_head_map(CUtensorMap* map, int dt, const void* base, int seq, int dim, long long heads, int box_rows) {
     const cuuint64_t gdim[4] = {64u, (cuuint64_t)seq, (cuuint64_t)(dim / 64), (cuuint64_t)heads};
     const cuuint64_t gstride[3] = {(cuuint64_t)dim * 2, 128u, (cuuint64_t)seq * dim * 2};
-    const cuuint32_t box[4] = {64u, 128u, (cuuint32_t)(dim / 64), 1u};
+    const cuuint32_t box[4] = {64u, (cuuint32_t)box_rows, (cuuint32_t)(dim / 64), 1u};
     const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
     const CUresult r = g_encode(map, dt == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                                 4, const_cast<void*>(base), gdim, gstride, box, estr,
@@ -545,9 +545,9 @@ int prefill_common(int dt, const void* q, const void* k, const void* v, void* ou
             }
         }
         CUtensorMap mq, mk, mv;
-        if ((rc = encode_head_map(&mq, dt, q, seq, dim, (long long)batch * hq))) return rc;
-        if ((rc = encode_head_map(&mk, dt, k, seq, dim, (long long)batch * hkv))) return rc;
-        if ((rc = encode_head_map(&mv, dt, v, seq, dim, (long long)batch * hkv))) return rc;
+        if ((rc = encode_head_map(&mq, dt, q, seq, dim, (long long)batch * hq, 128))) return rc;
+        if ((rc = encode_head_map(&mk, dt, k, seq, dim, (long long)batch * hkv, 64))) return rc;
+        if ((rc = encode_head_map(&mv, dt, v, seq, dim, (long long)batch * hkv, 64))) return rc;
         p.q_tiles = (seq + 127) / 128;
         if (dt == BF16) launch_prefill_tc_t<__nv_bfloat16>(mq, mk, mv, p, dev->status, cs);
         else launch_prefill_tc_t<__half>(mq, mk, mv, p, dev->status, cs);

@@ -5,22 +5,26 @@
 // include/fusedtok/cuda_launch.hpp:370-379; the reference's own tensor-core path is the mma.sync kernel at
 // src/attention.cu:951-1217).
 //
-// One CTA owns 128 query rows of one (batch, query head) and walks the key/value rows in tiles of 128:
+// One CTA owns 128 query rows of one (batch, query head) and walks the key/value rows in tiles of 64; two
+// CTAs share an SM (112 KB of shared memory, 256 tensor-memory columns and half the register file each), so
+// one CTA's softmax overlaps the other's MMAs:
 //
-//   warp 5  (producer)   TMA: the Q tile once, then K and V tiles into a 2-stage ring. Rank-4 tensor maps
+//   warp 5  (producer)   TMA: the Q tile once, then K and V tiles into two 2-stage rings. Rank-4 tensor maps
 //                        (64 elements, S rows, D/64 column blocks, B*H heads): rows past the end of a head are
 //                        zero-filled by the copy engine, tiles land as [column block][row][128 B], 128-byte
 //                        swizzled - exactly the K-major (Q, K) and MN-major (V) operand layouts of tcgen05.mma.
-//   warp 4  (MMA issue)  one elected thread: S = Q.K^T (M=128, N=128, K=D) into tensor memory, and after the
-//                        softmax warps have produced P: O_tile = P.V (M=128, N=D, K=128) into tensor memory;
+//   warp 4  (MMA issue)  one elected thread: S = Q.K^T (M=128, N=64, K=D) into one of two S buffers in tensor
+//                        memory (the next tile's scores are computed while the softmax warps work on this
+//                        one), and after the softmax warps have produced P: O_tile = P.V (M=128, N=D, K=64);
 //                        completion is signalled by tcgen05.commit on mbarriers.
 //   warps 0-3 (softmax)  thread t owns query row t = tensor-memory lane t: reads its S row with tcgen05.ld
 //                        (no shuffles), online softmax in fp32, writes P as bf16/fp16 into shared memory in the
 //                        swizzled K-major operand layout, then folds O_tile into its fp32 output row
 //                        (acc = acc*alpha + O_tile) and finally stores the row divided by the softmax sum.
+//                        These warps raise their register allowance (setmaxnreg), warps 4-7 lower theirs.
 //
-// Tensor memory: 256 columns (S: 128, O_tile: D). Every wait is bounded (2 s): on expiry the kernel records a
-// status code, all roles leave their loops, tensor memory is released and the kernel returns.
+// Tensor memory: 256 columns (S: 2 x 64, O_tile: D). Every wait is bounded (2 s): on expiry the kernel records
+// a status code, all roles leave their loops, tensor memory is released and the kernel returns.
 #pragma once
 
 #include "decode_tc.cuh"
@@ -28,25 +32,27 @@
 
 namespace ftk {
 
-constexpr int PF_THREADS = 192;
+constexpr int PF_THREADS = 256;
 constexpr int ST_PREFILL_TIMEOUT = 6;
 
 template <int D> struct PfCfg {
     static_assert(D == 64 || D == 128, "tensor-core prefill: head dim 64 or 128");
-    static constexpr int BM = 128, BN = 128, NST = 2;
-    static constexpr int PANEL = 128 * 128;                    // bytes: 128 rows x 128 B
-    static constexpr int TILE_BYTES = (D / 64) * PANEL;        // one Q, K or V tile
-    static constexpr int P_BYTES = 2 * PANEL;                  // 128 x 128 probabilities
+    static constexpr int BM = 128, BN = 64, NST = 2;
+    static constexpr int Q_PANEL = BM * 128;                   // bytes: 128 rows x 128 B
+    static constexpr int KV_PANEL = BN * 128;                  // 64 rows x 128 B
+    static constexpr int Q_BYTES = (D / 64) * Q_PANEL;
+    static constexpr int KV_BYTES = (D / 64) * KV_PANEL;       // one K or V tile
+    static constexpr int P_BYTES = BM * BN * 2;                // 128 x 64 probabilities: one panel
     static constexpr int OFF_Q = 0;
-    static constexpr int OFF_K = OFF_Q + TILE_BYTES;
-    static constexpr int OFF_V = OFF_K + NST * TILE_BYTES;
-    static constexpr int OFF_P = OFF_V + NST * TILE_BYTES;
-    static constexpr int OFF_BAR = OFF_P + P_BYTES;            // 10 mbarriers
+    static constexpr int OFF_K = OFF_Q + Q_BYTES;
+    static constexpr int OFF_V = OFF_K + NST * KV_BYTES;
+    static constexpr int OFF_P = OFF_V + NST * KV_BYTES;
+    static constexpr int OFF_BAR = OFF_P + P_BYTES;            // 16 mbarrier slots
     static constexpr int OFF_TMEM = OFF_BAR + 16 * 8;
     static constexpr int OFF_ABORT = OFF_TMEM + 8;
-    static constexpr int SMEM_BYTES = OFF_ABORT + 8 + 1024;    // + slack to align the base to 1024 B
-    static constexpr uint32_t TMEM_COLS = 256;
-    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
+    static constexpr int SMEM_BYTES = OFF_ABORT + 8;
+    static constexpr uint32_t TMEM_COLS = 256;                 // S0 [0,64), S1 [64,128), O [128,128+D)
+    static_assert(2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs must fit the 228 KB of one SM");
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------
@@ -105,7 +111,7 @@ __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
     while (!mbar_try_wait(bar, parity))
         if (global_ns() - t0 > WAIT_LIMIT_NS) return;
 }
-// Box [64 elements, 128 rows, D/64 column blocks, 1 head] at (row, head).
+// Box [64 elements, box rows, D/64 column blocks, 1 head] at (row, head).
 __device__ __forceinline__ void tma_load_tile4(uint32_t dst, const CUtensorMap* map, int row, int head, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
@@ -114,18 +120,21 @@ __device__ __forceinline__ void tma_load_tile4(uint32_t dst, const CUtensorMap* 
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(PF_THREADS, 1)
+__global__ void __launch_bounds__(PF_THREADS, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const PrefillParams p, int* status) {
     using C = PfCfg<D>;
-    extern __shared__ uint8_t pf_smem_raw[];
-    const uint32_t raw = smem_u32(pf_smem_raw);
-    const uint32_t base = (raw + 1023u) & ~1023u;
-    uint8_t* gbase = pf_smem_raw + (base - raw);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + C::OFF_ABORT);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + C::OFF_TMEM);
+    extern __shared__ __align__(1024) uint8_t pf_smem[];
+    const uint32_t base = smem_u32(pf_smem);
+    if (base & 1023u) {                                         // the swizzled operand layouts need it
+        if (threadIdx.x == 0) atomicCAS(status, ST_OK, ST_SMEM_MISALIGNED);
+        return;
+    }
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(pf_smem + C::OFF_ABORT);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(pf_smem + C::OFF_TMEM);
     auto bar = [&](int i) { return base + C::OFF_BAR + 8u * i; };
-    enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_EMPTY = 5, B_SFULL = 7, B_PREADY = 8, B_OFULL = 9, B_DRAIN = 10 };
+    enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KEMPTY = 5, B_VEMPTY = 7, B_SFULL = 9, B_PREADY = 11,
+           B_OFULL = 12, B_DRAIN = 13 };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nbh = p.B * p.Hq;
@@ -143,9 +152,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int s = 0; s < C::NST; ++s) {
             mbar_init(bar(B_KFULL + s), 1);
             mbar_init(bar(B_VFULL + s), 1);
-            mbar_init(bar(B_EMPTY + s), 1);
+            mbar_init(bar(B_KEMPTY + s), 1);
+            mbar_init(bar(B_VEMPTY + s), 1);
+            mbar_init(bar(B_SFULL + s), 1);
         }
-        mbar_init(bar(B_SFULL), 1);
         mbar_init(bar(B_PREADY), 128);
         mbar_init(bar(B_OFULL), 1);
         mbar_init(bar(B_DRAIN), 1);
@@ -163,63 +173,70 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
+    const uint32_t tmem_o = tmem + 128;
 
-    if (warp == 5) {
-        // ------------------------------------------------------------ producer
-        if (lane == 0) {
-            mbar_expect_tx(bar(B_QFULL), C::TILE_BYTES);
+    if (warp >= 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == 5 && lane == 0) {
+            // -------------------------------------------------------- producer
+            mbar_expect_tx(bar(B_QFULL), C::Q_BYTES);
             tma_load_tile4(base + C::OFF_Q, &tm_q, q0, bh, bar(B_QFULL));
             int issued = 0;
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j & 1;
-                if (j >= C::NST &&
-                    !mbar_wait(bar(B_EMPTY + s), ((j / C::NST) - 1) & 1, abort_flag, status, ST_PREFILL_TIMEOUT))
-                    break;
-                mbar_expect_tx(bar(B_KFULL + s), C::TILE_BYTES);
-                tma_load_tile4(base + C::OFF_K + s * C::TILE_BYTES, &tm_k, j * C::BN, kv_head, bar(B_KFULL + s));
-                mbar_expect_tx(bar(B_VFULL + s), C::TILE_BYTES);
-                tma_load_tile4(base + C::OFF_V + s * C::TILE_BYTES, &tm_v, j * C::BN, kv_head, bar(B_VFULL + s));
-                issued = j + 1;
+                const uint32_t ph_prev = ((j / C::NST) - 1) & 1;
+                if (j >= C::NST && !mbar_wait(bar(B_KEMPTY + s), ph_prev, abort_flag, status, ST_PREFILL_TIMEOUT)) break;
+                mbar_expect_tx(bar(B_KFULL + s), C::KV_BYTES);
+                tma_load_tile4(base + C::OFF_K + s * C::KV_BYTES, &tm_k, j * C::BN, kv_head, bar(B_KFULL + s));
+                issued = 2 * j + 1;
+                if (j >= C::NST && !mbar_wait(bar(B_VEMPTY + s), ph_prev, abort_flag, status, ST_PREFILL_TIMEOUT)) break;
+                mbar_expect_tx(bar(B_VFULL + s), C::KV_BYTES);
+                tma_load_tile4(base + C::OFF_V + s * C::KV_BYTES, &tm_v, j * C::BN, kv_head, bar(B_VFULL + s));
+                issued = 2 * j + 2;
             }
             // every copy issued has landed before the CTA gives its shared memory back
             mbar_wait_drain(bar(B_QFULL), 0);
-            for (int j = max(0, issued - C::NST); j < issued; ++j) {
+            const int k_issued = (issued + 1) / 2, v_issued = issued / 2;
+            for (int j = max(0, k_issued - C::NST); j < k_issued; ++j)
                 mbar_wait_drain(bar(B_KFULL + (j & 1)), (j / C::NST) & 1);
+            for (int j = max(0, v_issued - C::NST); j < v_issued; ++j)
                 mbar_wait_drain(bar(B_VFULL + (j & 1)), (j / C::NST) & 1);
-            }
-        }
-    } else if (warp == 4) {
-        // ------------------------------------------------------------ MMA issue
-        if (lane == 0) {
+        } else if (warp == 4 && lane == 0) {
+            // -------------------------------------------------------- MMA issue
             constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-            constexpr uint32_t IDESC_S = umma_idesc(FMT, 0, 0, 128, 128);     // Q (K-major) x K^T (K-major)
-            constexpr uint32_t IDESC_O = umma_idesc(FMT, 0, 1, 128, D);       // P (K-major) x V (MN-major)
+            constexpr uint32_t IDESC_S = umma_idesc(FMT, 0, 0, C::BM, C::BN);   // Q (K-major) x K^T (K-major)
+            constexpr uint32_t IDESC_O = umma_idesc(FMT, 0, 1, C::BM, D);       // P (K-major) x V (MN-major)
+            const uint32_t qa = base + C::OFF_Q, pa = base + C::OFF_P;
+            auto issue_scores = [&](int j) -> bool {
+                const int s = j & 1;
+                if (!mbar_wait(bar(B_KFULL + s), (j / C::NST) & 1, abort_flag, status, ST_PREFILL_TIMEOUT)) return false;
+                tc_fence_after();
+                const uint32_t ka = base + C::OFF_K + s * C::KV_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks)
+                    umma_f16(tmem + s * C::BN,
+                             umma_desc_sw128(qa + (ks >> 2) * C::Q_PANEL + (ks & 3) * 32, 16, 1024),
+                             umma_desc_sw128(ka + (ks >> 2) * C::KV_PANEL + (ks & 3) * 32, 16, 1024), IDESC_S, ks > 0);
+                umma_commit(bar(B_KEMPTY + s));
+                umma_commit(bar(B_SFULL + s));
+                return true;
+            };
             bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, status, ST_PREFILL_TIMEOUT);
+            ok = ok && issue_scores(0);
             for (int j = 0; ok && j < n_tiles; ++j) {
                 const int s = j & 1;
-                const uint32_t ph = (j / C::NST) & 1;
-                if (!(ok = mbar_wait(bar(B_KFULL + s), ph, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
-                tc_fence_after();
-                const uint32_t qa = base + C::OFF_Q, ka = base + C::OFF_K + s * C::TILE_BYTES;
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * C::PANEL + (ks & 3) * 32;
-                    umma_f16(tmem_s, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024),
-                             IDESC_S, ks > 0);
-                }
-                umma_commit(bar(B_SFULL));
+                // the next tile's scores go to the other S buffer while the softmax warps work on this one
+                // (that buffer's last reader, tile j-1, signalled P ready before its P.V was issued)
+                if (j + 1 < n_tiles && !(ok = issue_scores(j + 1))) break;
                 if (!(ok = mbar_wait(bar(B_PREADY), j & 1, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
-                if (!(ok = mbar_wait(bar(B_VFULL + s), ph, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
+                if (!(ok = mbar_wait(bar(B_VFULL + s), (j / C::NST) & 1, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
                 tc_fence_after();
-                const uint32_t pa = base + C::OFF_P, va = base + C::OFF_V + s * C::TILE_BYTES;
+                const uint32_t va = base + C::OFF_V + s * C::KV_BYTES;
 #pragma unroll
-                for (int ks = 0; ks < C::BN / 16; ++ks) {
-                    const uint32_t aoff = (ks >> 2) * C::PANEL + (ks & 3) * 32;
-                    umma_f16(tmem_o, umma_desc_sw128(pa + aoff, 16, 1024),
-                             umma_desc_sw128(va + ks * 2048, C::PANEL, 1024), IDESC_O, ks > 0);
-                }
-                umma_commit(bar(B_EMPTY + s));
+                for (int ks = 0; ks < C::BN / 16; ++ks)
+                    umma_f16(tmem_o, umma_desc_sw128(pa + ks * 32, 16, 1024),
+                             umma_desc_sw128(va + ks * 2048, C::KV_PANEL, 1024), IDESC_O, ks > 0);
+                umma_commit(bar(B_VEMPTY + s));
                 umma_commit(bar(B_OFULL));
             }
             // every MMA issued has completed before tensor memory is released
@@ -227,11 +244,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_wait_drain(bar(B_DRAIN), 0);
         }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         // ------------------------------------------------------------ softmax, accumulate, store
         const int row = threadIdx.x;                        // 0..127 = tensor-memory lane
         const int r_glob = q0 + row;
         const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
         const float sl2 = p.scale * 1.4426950408889634f;
+        const int lim = p.causal ? min(p.S - 1, r_glob) : p.S - 1;      // last live column of this row
         float acc[D];
 #pragma unroll
         for (int i = 0; i < D; ++i) acc[i] = 0.f;
@@ -239,15 +258,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int k0 = j * C::BN;
-            if (!(ok = mbar_wait(bar(B_SFULL), j & 1, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
+            const uint32_t ts = tmem + lane_base + (j & 1) * C::BN;
+            if (!(ok = mbar_wait(bar(B_SFULL + (j & 1)), (j / 2) & 1, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
             tc_fence_after();
             const bool need_mask = (k0 + C::BN > p.S) || (p.causal && k0 + C::BN - 1 > q0);
-            const int lim = p.causal ? min(p.S - 1, r_glob) : p.S - 1;   // last live column of this row
             float x[32];
             float mx = -INFINITY;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(tmem_s + lane_base + c * 32, x);
+            for (int c = 0; c < C::BN / 32; ++c) {
+                tmem_ld32(ts + c * 32, x);
                 if (need_mask) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
@@ -263,8 +282,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             m_run = m_new;
             float psum = 0.f;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(tmem_s + lane_base + c * 32, x);
+            for (int c = 0; c < C::BN / 32; ++c) {
+                tmem_ld32(ts + c * 32, x);
                 if (need_mask) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
@@ -276,10 +295,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     psum += x[i];
                 }
                 // 32 probabilities = four 16-byte chunks of this row in the swizzled K-major layout
-                const uint32_t prow = base + C::OFF_P + (c >> 1) * C::PANEL + row * 128;
+                const uint32_t prow = base + C::OFF_P + row * 128;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const uint32_t chunk = (uint32_t)((c & 1) * 4 + q4);
+                    const uint32_t chunk = (uint32_t)(c * 4 + q4);
                     const uint32_t addr = prow + ((chunk ^ (uint32_t)(row & 7)) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
                                  ::"r"(addr), "r"(pack2<T>(x[q4 * 8 + 0], x[q4 * 8 + 1])),
