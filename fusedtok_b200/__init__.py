@@ -26,7 +26,7 @@ except ImportError:  # pragma: no cover - torch is optional, as in the reference
 
 __version__ = "0.1.0"
 __all__ = ["attention_decode", "attention_decode_paged", "attention_prefill", "kv_append", "kv_append_paged",
-           "cuda_available"]
+           "rope", "cuda_available"]
 
 _PAGED_GROUPS = (1, 2, 4, 8, 16)
 
@@ -178,6 +178,67 @@ def _no_cpu_path():
 # ---------------------------------------------------------------------------
 # operators
 # ---------------------------------------------------------------------------
+
+def rope(q, k=None, *, theta=10000.0, pos_offset=0, neox=False, cuda=False):
+    """Rotary position embedding on (q, k): [seq, dim] with even dim.
+
+    ``neox=False`` rotates interleaved pairs (2j, 2j+1), ``neox=True`` the rotate_half layout (j, j + dim/2).
+    ``pos_offset`` is the absolute position of row 0. CUDA tensors may be float32 or bfloat16. Returns
+    ``(q_rotated, k_rotated)``; the second element is None if k is.
+    Reference: python/fusedtok/__init__.py:645-702.
+    """
+    if _is_torch(q) and q.is_cuda:
+        if q.dtype not in (torch.float32, torch.bfloat16):
+            raise TypeError("q must be float32 or bfloat16")
+        if not q.is_contiguous():
+            raise ValueError("q must be contiguous")
+        if q.ndim != 2:
+            raise ValueError("q must be 2-D [seq, dim]")
+        seq, dim = q.shape
+        if dim % 2:
+            raise ValueError("dim must be even (RoPE pairs elements)")
+        if pos_offset < 0:
+            raise ValueError("pos_offset must be >= 0")
+        q_out = torch.empty_like(q)
+        k_out = None
+        if k is not None:
+            if not (_is_torch(k) and k.is_cuda):
+                raise TypeError("k must be a CUDA tensor")
+            if k.dtype is not q.dtype:
+                raise TypeError("k must have the same dtype as q")
+            if k.shape != q.shape:
+                raise ValueError("k must have the same shape as q")
+            if not k.is_contiguous():
+                raise ValueError("k must be contiguous")
+            k_out = torch.empty_like(k)
+        with _on_device(q.device):
+            stream = _cuda_stream()
+            for src, dst in ((q, q_out), (k, k_out)):
+                if src is None:
+                    continue
+                if q.dtype is torch.bfloat16:
+                    launch = _fusedtok.rope_neox_launch_bf16 if neox else _fusedtok.rope_launch_bf16
+                    launch(src.data_ptr(), dst.data_ptr(), seq, dim, theta, pos_offset, stream)
+                else:
+                    _fusedtok.rope_launch(bool(neox), src.data_ptr(), dst.data_ptr(), seq, dim, theta, pos_offset,
+                                          stream)
+        return q_out, k_out
+    if not cuda:
+        _no_cpu_path()
+    arr_q = _as_numpy(q, "q")
+    arr_k = None if k is None else _as_numpy(k, "k")
+    if arr_q.ndim != 2:
+        raise ValueError("q must be 2-D [seq, dim]")
+    if arr_q.shape[1] % 2:
+        raise ValueError("dim must be even (RoPE pairs elements)")
+    if pos_offset < 0:
+        raise ValueError("pos_offset must be >= 0")
+    q_res, k_res = _fusedtok.rope(bool(neox), arr_q, arr_k, theta, pos_offset)
+    if _is_torch(q):
+        q_res = torch.from_numpy(q_res)
+        k_res = None if k_res is None else torch.from_numpy(k_res)
+    return q_res, k_res
+
 
 def attention_decode(q, k_cache, v_cache, lens=None, *, cuda=False):
     """Single-token (decode step) attention with GQA over a contiguous cache:

@@ -43,6 +43,10 @@ for _n in ("", "_bf16", "_fp16"):
     getattr(_lib, "fusedtok_kv_append_paged_launch" + _n).argtypes = [_vp] * 6 + [_i] * 5 + [_sz]
     getattr(_lib, "fusedtok_attention_prefill_launch" + _n).argtypes = [_vp] * 4 + [_i] * 6 + [_sz]
 _lib.fusedtok_attention_prefill.argtypes = [_vp] * 4 + [_i] * 6
+_lib.fusedtok_rope_launch.argtypes = [_i, _vp, _vp, _i, _i, ctypes.c_float, _i, _sz]
+_lib.fusedtok_rope_launch_bf16.argtypes = [_vp, _vp, _i, _i, ctypes.c_float, _i, _sz]
+_lib.fusedtok_rope_neox_launch_bf16.argtypes = [_vp, _vp, _i, _i, ctypes.c_float, _i, _sz]
+_lib.fusedtok_rope.argtypes = [_i, _vp, _vp, _vp, _vp, _i, _i, ctypes.c_float, _i]
 _lib.fusedtok_kv_append.argtypes = [_vp] * 5 + [_i] * 4
 _lib.fusedtok_kv_append_paged.argtypes = [_vp] * 6 + [_i] * 6
 _lib.fusedtok_attention_decode.argtypes = [_vp] * 5 + [_i] * 5
@@ -73,6 +77,7 @@ EXPORTS = (
     "fusedtok_attention_decode", "fusedtok_attention_decode_paged",
     "fusedtok_attention_prefill_launch", "fusedtok_attention_prefill_launch_bf16",
     "fusedtok_attention_prefill_launch_fp16", "fusedtok_attention_prefill",
+    "fusedtok_rope_launch", "fusedtok_rope_launch_bf16", "fusedtok_rope_neox_launch_bf16", "fusedtok_rope",
     "fusedtok_kv_append_launch", "fusedtok_kv_append_launch_bf16", "fusedtok_kv_append_launch_fp16",
     "fusedtok_kv_append_paged_launch", "fusedtok_kv_append_paged_launch_bf16",
     "fusedtok_kv_append_paged_launch_fp16", "fusedtok_kv_append", "fusedtok_kv_append_paged",
@@ -143,6 +148,20 @@ def _make_prefill(suffix):
 attention_prefill_launch = _make_prefill("")
 attention_prefill_launch_bf16 = _make_prefill("_bf16")
 attention_prefill_launch_fp16 = _make_prefill("_fp16")
+
+
+def rope_launch(neox, src, dst, seq, dim, theta, pos_offset, stream=0):
+    """float32, layout chosen by the bool (reference: src/bindings.cpp:722-735)."""
+    _check(_lib.fusedtok_rope_launch(1 if neox else 0, int(src), int(dst), seq, dim, float(theta), pos_offset,
+                                     int(stream)))
+
+
+def rope_launch_bf16(src, dst, seq, dim, theta, pos_offset, stream=0):
+    _check(_lib.fusedtok_rope_launch_bf16(int(src), int(dst), seq, dim, float(theta), pos_offset, int(stream)))
+
+
+def rope_neox_launch_bf16(src, dst, seq, dim, theta, pos_offset, stream=0):
+    _check(_lib.fusedtok_rope_neox_launch_bf16(int(src), int(dst), seq, dim, float(theta), pos_offset, int(stream)))
 
 
 def _make_append(suffix):
@@ -228,6 +247,23 @@ def attention_prefill(q, k, v, batch, hq, hkv, seq, dim, causal):
     _check(_lib.fusedtok_attention_prefill(_ptr(q), _ptr(k), _ptr(v), _ptr(out), batch, hq, hkv, seq, dim,
                                            1 if causal else 0))
     return out
+
+
+def rope(neox, q, k, theta, pos_offset):
+    """Staged RoPE: float32 host [seq, dim] arrays in, rotated copies out
+    (reference: src/bindings.cpp:683-716)."""
+    q = _f32(q)
+    if q.ndim != 2:
+        raise ValueError("q must be 2-D [seq, dim]")
+    if k is not None:
+        k = _f32(k)
+        if k.shape != q.shape:
+            raise ValueError("k must have the same shape as q")
+    q_out = np.empty_like(q)
+    k_out = None if k is None else np.empty_like(k)
+    _check(_lib.fusedtok_rope(1 if neox else 0, _ptr(q), _ptr(k), _ptr(q_out), _ptr(k_out), q.shape[0],
+                              q.shape[1], float(theta), int(pos_offset)))
+    return q_out, k_out
 
 
 def kv_append(k_new, v_new, lens, k_cache, v_cache, batch, hkv, dim, t_rows):

@@ -24,6 +24,7 @@
 #include "kv_append.cuh"
 #include "prefill_simt.cuh"
 #include "prefill_tc.cuh"
+#include "rope.cuh"
 #include "merge.cuh"
 
 namespace {
@@ -559,6 +560,39 @@ int prefill_common(int dt, const void* q, const void* k, const void* v, void* ou
     return check_launch("attention prefill kernel launch");
 }
 
+// reference: rope_launch / rope_neox_launch (+ _bf16), src/rope.cu:148-190 and its checks at :20-32
+int rope_common(int dt, int neox, const void* x, void* y, int seq, int dim, float theta, int pos_offset,
+                uintptr_t stream) {
+    if (seq < 0 || dim <= 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "seq must be >= 0 and dim must be > 0");
+    if (dim % 2 != 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "dim must be even (RoPE pairs elements)");
+    if (pos_offset < 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "pos_offset must be >= 0");
+    if (!(theta > 0.0f)) return fail(FUSEDTOK_INVALID_ARGUMENT, "theta must be positive");
+    if (seq == 0) return FUSEDTOK_OK;
+    if (!x || !y) return fail(FUSEDTOK_INVALID_ARGUMENT, "null rope operand");
+    DeviceState* dev = nullptr;
+    int rc = device_state(&dev);
+    if (rc) return rc;
+    RopeParams p{};
+    p.x = x; p.y = y; p.seq = seq; p.dim = dim; p.pos_offset = pos_offset; p.neox = neox ? 1 : 0;
+    p.log2_theta = std::log2((double)theta);
+    const size_t es = dtype_size(dt);
+    const uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y);
+    // two pairs per thread need every access (2 elements, rows and halves included) aligned to 2 elements
+    const bool vec = dim % 4 == 0 && (all & (2 * es - 1)) == 0;
+    const long long work = (long long)seq * (vec ? dim / 4 : dim / 2);
+    const long long want = (work + 255) / 256;
+    const unsigned grid = (unsigned)std::min<long long>(want, (long long)dev->sm_count * 16);
+    cudaStream_t cs = (cudaStream_t)stream;
+    if (dt == F32) {
+        if (vec) rope_kernel<float, true><<<grid, 256, 0, cs>>>(p);
+        else rope_kernel<float, false><<<grid, 256, 0, cs>>>(p);
+    } else {
+        if (vec) rope_kernel<__nv_bfloat16, true><<<grid, 256, 0, cs>>>(p);
+        else rope_kernel<__nv_bfloat16, false><<<grid, 256, 0, cs>>>(p);
+    }
+    return check_launch("rope kernel launch");
+}
+
 // RAII device buffer for the staged paths (reference: DevBuf, src/bindings.cpp:47-66)
 struct DevBuf {
     void* p = nullptr;
@@ -734,6 +768,46 @@ int fusedtok_attention_prefill(const float* q, const float* k, const float* v, f
     if (rc) return rc;
     if ((e = cudaMemcpy(out, dy.p, q_b, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("D2H copy failed", e);
     if ((e = cudaDeviceSynchronize()) != cudaSuccess) return cuda_fail("attention prefill kernel failed", e);
+    return FUSEDTOK_OK;
+}
+
+int fusedtok_rope_launch(int neox, const float* x, float* y, int seq, int dim, float theta, int pos_offset,
+                         uintptr_t stream) {
+    return rope_common(F32, neox, x, y, seq, dim, theta, pos_offset, stream);
+}
+int fusedtok_rope_launch_bf16(const void* x, void* y, int seq, int dim, float theta, int pos_offset,
+                              uintptr_t stream) {
+    return rope_common(BF16, 0, x, y, seq, dim, theta, pos_offset, stream);
+}
+int fusedtok_rope_neox_launch_bf16(const void* x, void* y, int seq, int dim, float theta, int pos_offset,
+                                   uintptr_t stream) {
+    return rope_common(BF16, 1, x, y, seq, dim, theta, pos_offset, stream);
+}
+
+int fusedtok_rope(int neox, const float* q, const float* k, float* q_out, float* k_out, int seq, int dim,
+                  float theta, int pos_offset) {
+    if (seq < 0 || dim <= 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "seq must be >= 0 and dim must be > 0");
+    if (dim % 2 != 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "dim must be even (RoPE pairs elements)");
+    if (pos_offset < 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "pos_offset must be >= 0");
+    const size_t bytes = (size_t)seq * dim * 4;
+    if (bytes == 0) return FUSEDTOK_OK;
+    const int n = k ? 2 : 1;
+    DevBuf dx(bytes * n), dy(bytes * n);
+    for (const DevBuf* b : {&dx, &dy})
+        if (b->err != cudaSuccess) return cuda_fail("cudaMalloc failed", b->err);
+    cudaError_t e;
+    if ((e = cudaMemcpy(dx.p, q, bytes, cudaMemcpyHostToDevice)) != cudaSuccess) return cuda_fail("H2D copy failed", e);
+    if (k && (e = cudaMemcpy((char*)dx.p + bytes, k, bytes, cudaMemcpyHostToDevice)) != cudaSuccess)
+        return cuda_fail("H2D copy failed", e);
+    for (int i = 0; i < n; ++i) {
+        const int rc = fusedtok_rope_launch(neox, (const float*)((char*)dx.p + i * bytes),
+                                            (float*)((char*)dy.p + i * bytes), seq, dim, theta, pos_offset, 0);
+        if (rc) return rc;
+    }
+    if ((e = cudaMemcpy(q_out, dy.p, bytes, cudaMemcpyDeviceToHost)) != cudaSuccess) return cuda_fail("D2H copy failed", e);
+    if (k && (e = cudaMemcpy(k_out, (char*)dy.p + bytes, bytes, cudaMemcpyDeviceToHost)) != cudaSuccess)
+        return cuda_fail("D2H copy failed", e);
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return cuda_fail("rope kernel failed", e);
     return FUSEDTOK_OK;
 }
 

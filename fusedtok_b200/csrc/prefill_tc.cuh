@@ -15,12 +15,14 @@
 //                        swizzled - exactly the K-major (Q, K) and MN-major (V) operand layouts of tcgen05.mma.
 //   warp 4  (MMA issue)  one elected thread: S = Q.K^T (M=128, N=64, K=D) into one of two S buffers in tensor
 //                        memory (the next tile's scores are computed while the softmax warps work on this
-//                        one), and after the softmax warps have produced P: O_tile = P.V (M=128, N=D, K=64);
+//                        one), and after the softmax warps have produced P: O += P.V (M=128, N=D, K=64);
 //                        completion is signalled by tcgen05.commit on mbarriers.
 //   warps 0-3 (softmax)  thread t owns query row t = tensor-memory lane t: reads its S row with tcgen05.ld
 //                        (no shuffles), online softmax in fp32, writes P as bf16/fp16 into shared memory in the
-//                        swizzled K-major operand layout, then folds O_tile into its fp32 output row
-//                        (acc = acc*alpha + O_tile) and finally stores the row divided by the softmax sum.
+//                        swizzled K-major operand layout. The output row accumulates in tensor memory
+//                        (P.V with accumulate) against a lazily raised reference maximum; raising it
+//                        rescales the row in tensor memory (tcgen05.ld / .st). At the end the row is read
+//                        back, divided by the softmax sum and stored.
 //                        These warps raise their register allowance (setmaxnreg), warps 4-7 lower theirs.
 //
 // Tensor memory: 256 columns (S: 2 x 64, O_tile: D). Every wait is bounded (2 s): on expiry the kernel records
@@ -102,6 +104,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&x)[32]) {
         : "memory");
 #pragma unroll
     for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(r[i]);
+}
+// 64 consecutive fp32 columns of this thread's tensor-memory lane (two loads in flight, one wait).
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&x)[64]) {
+    uint32_t r[64];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%64];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%65];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr), "r"(taddr + 32)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) x[i] = __uint_as_float(r[i]);
+}
+// Write 32 consecutive fp32 columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&x)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n\t"
+        "tcgen05.wait::st.sync.aligned;"
+        ::"r"(taddr), "r"(__float_as_uint(x[0])), "r"(__float_as_uint(x[1])), "r"(__float_as_uint(x[2])), "r"(__float_as_uint(x[3])), "r"(__float_as_uint(x[4])), "r"(__float_as_uint(x[5])), "r"(__float_as_uint(x[6])), "r"(__float_as_uint(x[7])), "r"(__float_as_uint(x[8])), "r"(__float_as_uint(x[9])), "r"(__float_as_uint(x[10])), "r"(__float_as_uint(x[11])), "r"(__float_as_uint(x[12])), "r"(__float_as_uint(x[13])), "r"(__float_as_uint(x[14])), "r"(__float_as_uint(x[15])), "r"(__float_as_uint(x[16])), "r"(__float_as_uint(x[17])), "r"(__float_as_uint(x[18])), "r"(__float_as_uint(x[19])), "r"(__float_as_uint(x[20])), "r"(__float_as_uint(x[21])), "r"(__float_as_uint(x[22])), "r"(__float_as_uint(x[23])), "r"(__float_as_uint(x[24])), "r"(__float_as_uint(x[25])), "r"(__float_as_uint(x[26])), "r"(__float_as_uint(x[27])), "r"(__float_as_uint(x[28])), "r"(__float_as_uint(x[29])), "r"(__float_as_uint(x[30])), "r"(__float_as_uint(x[31]))
+        : "memory");
 }
 // Wait that ignores the abort flag: used on the way out, so that no copy or MMA of this CTA is still in
 // flight when its shared and tensor memory are given back. Bounded all the same.
@@ -235,7 +258,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
                 for (int ks = 0; ks < C::BN / 16; ++ks)
                     umma_f16(tmem_o, umma_desc_sw128(pa + ks * 32, 16, 1024),
-                             umma_desc_sw128(va + ks * 2048, C::KV_PANEL, 1024), IDESC_O, ks > 0);
+                             umma_desc_sw128(va + ks * 2048, C::KV_PANEL, 1024), IDESC_O, (j | ks) > 0);
                 umma_commit(bar(B_VEMPTY + s));
                 umma_commit(bar(B_OFULL));
             }
@@ -245,95 +268,103 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-        // ------------------------------------------------------------ softmax, accumulate, store
+        // ------------------------------------------------------------ softmax, rescale, store
         const int row = threadIdx.x;                        // 0..127 = tensor-memory lane
         const int r_glob = q0 + row;
         const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
         const float sl2 = p.scale * 1.4426950408889634f;
         const int lim = p.causal ? min(p.S - 1, r_glob) : p.S - 1;      // last live column of this row
-        float acc[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) acc[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
+        // The output row accumulates in tensor memory across tiles (P.V with accumulate), relative to a
+        // reference maximum m_ref that is only raised when a tile's maximum exceeds it by more than 2^8:
+        // probabilities then stay below 256 (exact in bf16/fp16 terms), the sum l uses the same reference,
+        // and out = O / l does not depend on the reference. Raising it rescales O in tensor memory.
+        float m_ref = 0.f, l_run = 0.f;
+        // warp-uniform result: the tensor-memory loads and stores below are warp-wide instructions
+        auto wait_all = [&](uint32_t b, uint32_t parity) {
+            return __all_sync(0xffffffffu, mbar_wait(b, parity, abort_flag, status, ST_PREFILL_TIMEOUT)) != 0;
+        };
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int k0 = j * C::BN;
-            const uint32_t ts = tmem + lane_base + (j & 1) * C::BN;
-            if (!(ok = mbar_wait(bar(B_SFULL + (j & 1)), (j / 2) & 1, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
+            if (!(ok = wait_all(bar(B_SFULL + (j & 1)), (j / 2) & 1))) break;
             tc_fence_after();
-            const bool need_mask = (k0 + C::BN > p.S) || (p.causal && k0 + C::BN - 1 > q0);
-            float x[32];
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < C::BN / 32; ++c) {
-                tmem_ld32(ts + c * 32, x);
-                if (need_mask) {
+            float x[64];
+            tmem_ld64(tmem + lane_base + (j & 1) * C::BN, x);
+            if ((k0 + C::BN > p.S) || (p.causal && k0 + C::BN - 1 > q0)) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (k0 + c * 32 + i > lim) x[i] = -INFINITY;
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, x[i]);
+                for (int i = 0; i < 64; ++i)
+                    if (k0 + i > lim) x[i] = -INFINITY;
             }
-            const float m_new = fmaxf(m_run, mx);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = ex2((m_run - m_use) * sl2);
-            const float neg_ms = -m_use * sl2;
-            m_run = m_new;
+            float mx = x[0];
+#pragma unroll
+            for (int i = 1; i < 64; ++i) mx = fmaxf(mx, x[i]);
+            bool o_free = j == 0;                           // P.V of the previous tile has completed
+            if (j == 0) {
+                m_ref = mx == -INFINITY ? 0.f : mx;
+            } else if (__any_sync(0xffffffffu, (mx - m_ref) * sl2 > 8.0f)) {
+                const float m_new = fmaxf(m_ref, mx);
+                const float alpha = ex2((m_ref - m_new) * sl2);
+                m_ref = m_new;
+                l_run *= alpha;
+                if (!(ok = wait_all(bar(B_OFULL), (j - 1) & 1))) break;
+                tc_fence_after();
+                o_free = true;
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                    float o[32];
+                    tmem_ld32(tmem_o + lane_base + c * 32, o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                    tmem_st32(tmem_o + lane_base + c * 32, o);
+                }
+            }
+            const float neg_ms = -m_ref * sl2;
+            uint32_t pk[32];
             float psum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < C::BN / 32; ++c) {
-                tmem_ld32(ts + c * 32, x);
-                if (need_mask) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (k0 + c * 32 + i > lim) x[i] = -INFINITY;
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    x[i] = ex2(fmaf(x[i], sl2, neg_ms));
-                    psum += x[i];
-                }
-                // 32 probabilities = four 16-byte chunks of this row in the swizzled K-major layout
-                const uint32_t prow = base + C::OFF_P + row * 128;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const uint32_t chunk = (uint32_t)(c * 4 + q4);
-                    const uint32_t addr = prow + ((chunk ^ (uint32_t)(row & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(addr), "r"(pack2<T>(x[q4 * 8 + 0], x[q4 * 8 + 1])),
-                                   "r"(pack2<T>(x[q4 * 8 + 2], x[q4 * 8 + 3])),
-                                   "r"(pack2<T>(x[q4 * 8 + 4], x[q4 * 8 + 5])),
-                                   "r"(pack2<T>(x[q4 * 8 + 6], x[q4 * 8 + 7]))
-                                 : "memory");
-                }
+            for (int i = 0; i < 64; i += 2) {
+                const float a = ex2(fmaf(x[i], sl2, neg_ms)), bq = ex2(fmaf(x[i + 1], sl2, neg_ms));
+                psum += a + bq;
+                pk[i >> 1] = pack2<T>(a, bq);
             }
-            l_run = l_run * alpha + psum;
+            l_run += psum;
+            // the P tile is free once the previous tile's P.V has read it
+            if (!o_free) {
+                if (!(ok = wait_all(bar(B_OFULL), (j - 1) & 1))) break;
+            }
+            // 64 probabilities = eight 16-byte chunks of this row in the swizzled K-major layout
+            const uint32_t prow = base + C::OFF_P + row * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                const uint32_t addr = prow + (((uint32_t)ch ^ (uint32_t)(row & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                             ::"r"(addr), "r"(pk[ch * 4]), "r"(pk[ch * 4 + 1]), "r"(pk[ch * 4 + 2]), "r"(pk[ch * 4 + 3])
+                             : "memory");
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the tensor core
             tc_fence_before();
             mbar_arrive(bar(B_PREADY));
-
-            if (!(ok = mbar_wait(bar(B_OFULL), j & 1, abort_flag, status, ST_PREFILL_TIMEOUT))) break;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                tmem_ld32(tmem_o + lane_base + c * 32, x);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, x[i]);
-            }
-            tc_fence_before();
         }
-        if (ok && r_glob < p.S) {
+        if (ok) ok = wait_all(bar(B_OFULL), (n_tiles - 1) & 1);
+        if (ok) {
+            tc_fence_after();
             const float inv = 1.0f / l_run;
             T* orow = static_cast<T*>(p.out) + ((size_t)bh * p.S + r_glob) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                float o[32];
+                tmem_ld32(tmem_o + lane_base + c * 32, o);          // warp-wide: every lane takes part
+                if (r_glob < p.S) {
 #pragma unroll
-            for (int i = 0; i < D; i += 8) {
-                uint4 u;
-                u.x = pack2<T>(acc[i] * inv, acc[i + 1] * inv);
-                u.y = pack2<T>(acc[i + 2] * inv, acc[i + 3] * inv);
-                u.z = pack2<T>(acc[i + 4] * inv, acc[i + 5] * inv);
-                u.w = pack2<T>(acc[i + 6] * inv, acc[i + 7] * inv);
-                *reinterpret_cast<uint4*>(orow + i) = u;
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 u;
+                        u.x = pack2<T>(o[i] * inv, o[i + 1] * inv);
+                        u.y = pack2<T>(o[i + 2] * inv, o[i + 3] * inv);
+                        u.z = pack2<T>(o[i + 4] * inv, o[i + 5] * inv);
+                        u.w = pack2<T>(o[i + 6] * inv, o[i + 7] * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + i) = u;
+                    }
+                }
             }
         }
     }

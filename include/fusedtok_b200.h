@@ -119,6 +119,25 @@ int fusedtok_attention_prefill_launch_fp16(const void* q, const void* k, const v
 int fusedtok_attention_prefill(const float* q, const float* k, const float* v, float* out,
                                int batch, int q_heads, int kv_heads, int seq, int dim, int causal);
 
+/* ---- rotary position embedding (the step that produces q and k_new) ---------
+ * One [seq, dim] matrix per call, dim even: row r has absolute position
+ * r + pos_offset, pair j is rotated by (r + pos_offset) * theta^(-2j/dim);
+ * neox == 0 pairs elements (2j, 2j+1), neox != 0 pairs (j, j + dim/2). x and y
+ * may be the same buffer. Device pointers, asynchronous on `stream`, capturable.
+ * Replace fusedtok::rope_launch / rope_neox_launch (selected by the pybind's
+ * bool, src/bindings.cpp:722-735) and rope_launch_bf16 / rope_neox_launch_bf16,
+ * include/fusedtok/cuda_launch.hpp (src/rope.cu:148-190). The staged form takes
+ * HOST float32 q and optional k (k, k_out may be NULL) and rotates both
+ * (src/bindings.cpp:683-716). */
+int fusedtok_rope_launch(int neox, const float* x, float* y, int seq, int dim, float theta,
+                         int pos_offset, uintptr_t stream);
+int fusedtok_rope_launch_bf16(const void* x, void* y, int seq, int dim, float theta,
+                              int pos_offset, uintptr_t stream);
+int fusedtok_rope_neox_launch_bf16(const void* x, void* y, int seq, int dim, float theta,
+                                   int pos_offset, uintptr_t stream);
+int fusedtok_rope(int neox, const float* q, const float* k, float* q_out, float* k_out, int seq,
+                  int dim, float theta, int pos_offset);
+
 /* ---- kv-cache append: the write side of the decode loop --------------------
  * Scatter ONE fresh token's K and V rows per sequence (k_new, v_new
  * [B, Hkv, D]) into the cache at position lens[b] (lens is required):

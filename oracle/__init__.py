@@ -41,6 +41,7 @@ def _load():
         _lib.oracle_attention_partial.argtypes = [_fp, _fp, _fp, _fp, _fp, _fp, _i, _i, _i]
         _lib.oracle_attention_merge.argtypes = [_fp, _fp, _i, _i, _fp]
         _lib.oracle_attention_prefill.argtypes = [_fp, _fp, _fp, _fp] + [_i] * 6
+        _lib.oracle_rope.argtypes = [_fp, _fp, _i, _i, ctypes.c_float, _i, _i]
         _lib.oracle_kv_append.argtypes = [_fp, _fp, _ip, _fp, _fp] + [_i] * 4
         _lib.oracle_kv_append_paged.argtypes = [_fp, _fp, _ip, _ip, _fp, _fp] + [_i] * 6
     return _lib
@@ -68,6 +69,8 @@ def _load_ref():
         if hasattr(_ref, "ref_attention_prefill_cpu"):
             _ref.ref_attention_prefill_cpu.argtypes = [_fp, _fp, _fp, _fp] + [_i] * 6
             _ref.ref_attention_prefill_launch.argtypes = [_i, vp, vp, vp, vp] + [_i] * 6 + [ctypes.c_size_t]
+        if hasattr(_ref, "ref_rope_cpu"):
+            _ref.ref_rope_cpu.argtypes = [_fp, _fp, _i, _i, ctypes.c_float, _i, _i]
         _ref.ref_attention_decode_launch.argtypes = (
             [_i, vp, vp, vp, vp, vp] + [_i] * 5 + [ctypes.c_size_t])
         _ref.ref_attention_decode_paged_launch.argtypes = (
@@ -166,6 +169,27 @@ def ref_gpu_prefill_launch(dtype_code, q_ptr, k_ptr, v_ptr, out_ptr, b, hq, hkv,
                                         1 if causal else 0, stream)
     if rc:
         raise RuntimeError(r.ref_last_error().decode())
+
+
+def _rope(fn, x, theta, pos_offset, neox):
+    x = _f32(x)
+    if x.ndim != 2:
+        raise ValueError("x must be [seq, dim]")
+    y = np.empty_like(x)
+    rc = fn(_pf(x), _pf(y), x.shape[0], x.shape[1], float(theta), int(pos_offset), 1 if neox else 0)
+    if rc:
+        raise ValueError("oracle rejected the arguments (code %d)" % rc)
+    return y
+
+
+def rope(x, theta=10000.0, pos_offset=0, neox=False):
+    """Rotary embedding of one [seq, dim] matrix through the C restatement."""
+    return _rope(_load().oracle_rope, x, theta, pos_offset, neox)
+
+
+def ref_rope(x, theta=10000.0, pos_offset=0, neox=False):
+    """The reference's own rope_cpu / rope_neox_cpu (src/rope.cu:95-146)."""
+    return _rope(_load_ref().ref_rope_cpu, x, theta, pos_offset, neox)
 
 
 def partial(q_row, k_rows, v_rows, t0, t1):

@@ -357,3 +357,30 @@ int oracle_attention_prefill(const float *q, const float *k, const float *v,
     free(scores);
     return 0;
 }
+
+/*
+ * Rotary position embedding on one [seq, dim] matrix, restating rope_cpu /
+ * rope_neox_cpu (reference: src/rope.cu:95-146). Row r has absolute position
+ * m = r + pos_offset; pair j is rotated by angle m * theta^(-2j/dim), computed
+ * in double like the reference. neox == 0: pairs (2j, 2j+1); neox != 0: pairs
+ * (j, j + dim/2).
+ */
+int oracle_rope(const float *x, float *y, int seq, int dim, float theta,
+                int pos_offset, int neox)
+{
+    if (seq < 0 || dim <= 0 || dim % 2 != 0 || pos_offset < 0)
+        return 1;
+    for (int r = 0; r < seq; ++r) {
+        const int m = r + pos_offset;
+        for (int j = 0; j < dim / 2; ++j) {
+            const double angle = m * pow((double)theta, -2.0 * j / dim);
+            const double c = cos(angle), s = sin(angle);
+            const size_t a = neox ? (size_t)r * dim + j : (size_t)r * dim + 2 * j;
+            const size_t b = neox ? a + dim / 2 : a + 1;
+            const float xa = x[a], xb = x[b];
+            y[a] = (float)(xa * c - xb * s);
+            y[b] = (float)(xa * s + xb * c);
+        }
+    }
+    return 0;
+}

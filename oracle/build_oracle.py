@@ -6,7 +6,7 @@ benchmark's CPU-baseline leg - never by the shipped package:
 * ``oracle/liboracle.so``  - gcc build of ``attention_oracle.c`` (the plain-C
   restatement of the reference's CPU decode attention).
 * ``oracle/_ref/libfusedtok_ref.so`` - the reference's OWN implementation:
-  nvcc compiles the reference's ``src/attention.cu`` where it lies in the
+  nvcc compiles the reference's ``src/attention.cu`` and ``src/rope.cu`` where they lie in the
   reference checkout (nothing is copied) together with ``ref_shim.cpp``, a
   C-ABI shim. It carries the reference's CPU functions (the parity pin) and
   its GPU launchers (timed beside ours). Only built when a reference checkout
@@ -55,13 +55,14 @@ def build_ref(force=False):
     if not reference_present():
         return REF_SO if os.path.exists(REF_SO) else None
     ref_src = os.path.join(REF_DIR, "src", "attention.cu")
-    if force or _stale(REF_SO, [shim, ref_src]):
+    rope_src = os.path.join(REF_DIR, "src", "rope.cu")
+    if force or _stale(REF_SO, [shim, ref_src, rope_src]):
         os.makedirs(os.path.dirname(REF_SO), exist_ok=True)
         cmd = ["nvcc", "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
                "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
                "-I", os.path.join(REF_DIR, "include"),
                "-I", os.path.join(REF_DIR, "src"),
-               "-x", "cu", ref_src, "-x", "cu", shim, "-o", REF_SO]
+               "-x", "cu", ref_src, "-x", "cu", rope_src, "-x", "cu", shim, "-o", REF_SO]
         subprocess.check_call(cmd)
     return REF_SO
 

@@ -10,6 +10,7 @@
 // Exceptions become return codes: 0 ok, 1 std::invalid_argument, 2 other.
 
 #include "fusedtok/attention.hpp"
+#include "fusedtok/fusedtok.hpp"
 #include "fusedtok/cuda_launch.hpp"
 
 #include <cstddef>
@@ -120,6 +121,17 @@ int ref_attention_prefill_cpu(const float* q, const float* k, const float* v, fl
         std::vector<float> qv(q, q + nq), kv(k, k + nkv), vv(v, v + nkv);
         std::vector<float> y = fusedtok::attention_prefill_cpu(qv, kv, vv, batch, hq, hkv, seq, dim, causal != 0);
         if (!y.empty()) std::memcpy(out, y.data(), y.size() * sizeof(float));
+    });
+}
+
+// reference: fusedtok::rope_cpu / rope_neox_cpu, src/rope.cu:95-146 (one matrix per call)
+int ref_rope_cpu(const float* x, float* y, int seq, int dim, float theta, int pos_offset, int neox) {
+    return guarded([&] {
+        if (seq < 0 || dim < 0) throw std::invalid_argument("negative shape");
+        std::vector<float> xv(x, x + (size_t)seq * dim);
+        auto res = neox ? fusedtok::rope_neox_cpu(xv, nullptr, seq, dim, theta, pos_offset)
+                        : fusedtok::rope_cpu(xv, nullptr, seq, dim, theta, pos_offset);
+        if (!res.first.empty()) std::memcpy(y, res.first.data(), res.first.size() * sizeof(float));
     });
 }
 
