@@ -518,6 +518,196 @@ def run_ours(args, w, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+PREFILL_WORKLOADS = {
+    # the reference's own prefill benchmark shape (benchmarks/bench.py:518-541)
+    "pf_ref": dict(desc="prefill, reference benchmark shape: batch 1, 32/8 heads, D=128, S=1024, causal, bf16",
+                   B=1, Hq=32, Hkv=8, D=128, S=1024, dtype="bf16", causal=True),
+    # a long-prompt batch where the operator is compute-bound
+    "pf_long": dict(desc="prefill, batch 2, 32/8 heads, D=128, S=8192, causal, bf16",
+                    B=2, Hq=32, Hkv=8, D=128, S=8192, dtype="bf16", causal=True),
+    "pf_long_f32": dict(desc="prefill, batch 1, 32/8 heads, D=128, S=4096, causal, float32 (CUDA-core kernel)",
+                        B=1, Hq=32, Hkv=8, D=128, S=4096, dtype="f32", causal=True),
+}
+
+
+def prefill_cpu_sample(w, target_seconds, threads):
+    """The reference's CPU prefill (oracle/_ref, else the C restatement) on `threads` host threads, each on
+    one (head group, short sequence) problem of the workload's head shape; returns TFLOP/s."""
+    import numpy as np
+    import oracle
+    kind = "reference" if oracle.ref_available() else "port"
+    fn = oracle.ref_prefill if kind == "reference" else oracle.prefill
+    s_len = min(w["S"], 256)
+    rng = np.random.default_rng(0)
+    g = w["Hq"] // w["Hkv"]
+    q = rng.standard_normal((1, g, s_len, w["D"])).astype(np.float32)
+    k = rng.standard_normal((1, 1, s_len, w["D"])).astype(np.float32)
+    t0 = time.perf_counter()
+    fn(q, k, k, w["causal"])
+    one = time.perf_counter() - t0
+    reps = max(1, int(target_seconds / max(one, 1e-4)))
+
+    def work():
+        for _ in range(reps):
+            fn(q, k, k, w["causal"])
+
+    ths = [threading.Thread(target=work) for _ in range(threads)]
+    t0 = time.perf_counter()
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    dt = time.perf_counter() - t0
+    flops = 4.0 * s_len * s_len * w["D"] * g / (2 if w["causal"] else 1)
+    sample = ("%d calls (%d threads x %d) of one kv head's group (%d query heads), S=%d, D=%d, float32, %.1f s"
+              % (threads * reps, threads, reps, g, s_len, w["D"], dt))
+    return threads * reps * flops / dt / 1e12, kind, sample, dt
+
+
+def run_prefill(args, rank, world, local_rank):
+    """Prefill workloads: one step = one attention_prefill call over the whole batch. value = TFLOP/s with the
+    operands resident (FLOPs = 4*S*S*D*Hq*B, halved when causal); roofline against the measured dense bf16
+    GEMM rate (fp32: no tensor peak applies, reported against the same number for scale)."""
+    import torch
+    import torch.distributed as dist
+    import fusedtok_b200 as ft
+    from fusedtok_b200 import _fusedtok
+    w = dict(PREFILL_WORKLOADS[args.workload])
+    for kv in args.set:
+        key, val = kv.split("=", 1)
+        w[key] = type(w[key])(val) if not isinstance(w[key], bool) else val in ("1", "true", "True")
+    if args.impl == "reference":
+        if rank == 0:
+            threads = os.cpu_count() or 1
+            per_step = min(8.0, max(0.3, 60.0 / args.steps))
+            for _ in range(args.warmup):
+                prefill_cpu_sample(w, 0.2, threads)
+            vals, total_t = [], 0.0
+            for _ in range(args.steps):
+                v, kind, sample, dt = prefill_cpu_sample(w, per_step, threads)
+                vals.append(v)
+                total_t += dt
+            value = sum(vals) / len(vals)
+            print(json.dumps({
+                "impl": "reference", "metric": "prefill_attn_TFLOPs", "value": value, "unit": "TFLOP/s",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": total_t / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": args.workload + ": " + w["desc"] + " (CPU sample, see cpu_baseline.sample)"},
+                "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample},
+                "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}), flush=True)
+        return
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dt = torch.bfloat16 if w["dtype"] == "bf16" else (torch.float16 if w["dtype"] == "f16" else torch.float32)
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    shape_q = (w["B"], w["Hq"], w["S"], w["D"])
+    shape_kv = (w["B"], w["Hkv"], w["S"], w["D"])
+    q = torch.randn(shape_q, device=dev, generator=gen).to(dt)
+    k = torch.randn(shape_kv, device=dev, generator=gen).to(dt)
+    v = torch.randn(shape_kv, device=dev, generator=gen).to(dt)
+    flops = 4.0 * w["S"] * w["S"] * w["D"] * w["Hq"] * w["B"] / (2 if w["causal"] else 1)
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev)        # larger than L2 (126 MB)
+    small = q.numel() * q.element_size() * 2 + k.numel() * k.element_size() * 2 < (126 << 20)
+
+    def step():
+        return ft.attention_prefill(q, k, v, causal=w["causal"])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if args.profile:
+        for _ in range(args.warmup):
+            step()
+        for _ in range(args.steps):
+            step()
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_run": True, "workload": args.workload}), flush=True)
+        return
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    n0 = _fusedtok.attention_launch_count()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for a, b in ev:
+        if small:
+            flush.fill_(1)                     # operands fit L2: evict them between timed steps
+        a.record()
+        step()
+        b.record()
+    barrier()
+    clocks = sampler.stop()
+    launches = _fusedtok.attention_launch_count() - n0
+    ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    value = world * flops / (ms * 1e-3) / 1e12
+
+    # end to end: operands from pinned host memory, result read back, every step
+    hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
+    hout = torch.empty(shape_q, dtype=dt).pin_memory()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        hout.copy_(ft.attention_prefill(dq, dk, dv, causal=w["causal"]), non_blocking=True)
+        torch.cuda.synchronize()
+        return float(hout[0, 0, 0, 0])
+
+    for _ in range(3):
+        e2e_step()
+    n_e2e = max(3, min(args.steps, 20))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        e2e_step()
+    e2e_ms = (time.perf_counter() - t0) / n_e2e * 1e3
+    t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    if rank != 0:
+        return
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, peak_kind = float(json.load(f)["bf16_tflops"]), "of measured (cuBLAS bf16 burst)"
+    except Exception:
+        peak, peak_kind = 1590.0, "of fallback"
+    line = {
+        "metric": "prefill_attn_TFLOPs", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": args.workload + ": " + w["desc"], "batch_per_gpu": w["B"], "q_heads": w["Hq"],
+                   "kv_heads": w["Hkv"], "head_dim": w["D"], "seq": w["S"], "causal": w["causal"],
+                   "flops_per_step_per_gpu": flops,
+                   "l2": ("L2 flushed between timed steps (160 MB fill)" if small else "operands larger than L2"),
+                   "parallelism": "batch-sharded x%d, no communication" % world},
+        "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
+                     "frac": value / world / peak, "peak_kind": peak_kind, "traffic": None,
+                     "note": ("float32 runs on CUDA cores: the tensor peak is shown for scale only"
+                              if w["dtype"] == "f32" else "one kernel per step")},
+        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in (q, k, v)),
+                "d2h_bytes_per_step": q.numel() * q.element_size()},
+        "gpu_launches": int(launches), "device_status": _fusedtok.attention_device_status(), "clocks": clocks,
+    }
+    if not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        v_cpu, kind, sample, _ = prefill_cpu_sample(w, 10.0, threads)
+        line["cpu_baseline"] = {"value": v_cpu, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample}
+    print(json.dumps(line), flush=True)
+
+
 def run_reference_rows(args):
     """The reference's own attention-decode benchmark rows (benchmarks/bench.py:468-516) on this
     GPU: batch 1, 32/8 heads, head dim 128, T in {4096, 16384}, fp32 and bf16, plus the paged fp32
@@ -637,7 +827,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["refrows"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS) + ["refrows"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--graph", action="store_true", help="replay the step as a CUDA graph")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
@@ -654,6 +844,21 @@ def main():
     if args.workload == "refrows":
         if rank == 0:
             run_reference_rows(args)
+        return
+    if args.workload in PREFILL_WORKLOADS:
+        if world > 1:
+            import torch.distributed as dist
+            if args.impl == "reference":
+                if rank == 0:
+                    run_prefill(args, rank, world, local_rank)
+                return
+            dist.init_process_group("nccl", device_id=__import__("torch").device("cuda", local_rank))
+            try:
+                run_prefill(args, rank, world, local_rank)
+            finally:
+                dist.destroy_process_group()
+            return
+        run_prefill(args, rank, world, local_rank)
         return
     w = dict(WORKLOADS[args.workload])
     for kv in args.set:
