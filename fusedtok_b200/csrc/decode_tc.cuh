@@ -104,36 +104,10 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
 // Bounded wait. Returns false when the limit expired or another warp already
 // gave up; the caller then carries on without the data.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
-#ifdef FTK_SPIN_TEST_WAIT
-    if (mbar_test_wait(bar, parity)) return true;
-    const long long c0 = clock64();
-    for (uint32_t it = 1;; ++it) {
-        if (mbar_test_wait(bar, parity)) return true;
-        if ((it & 255u) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - c0 > 6000000000ll) {
-                *abort_flag = 1;
-                atomicCAS(status, ST_OK, code);
-                return false;
-            }
-        }
-    }
-#else
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (uint32_t it = 1;; ++it) {
@@ -147,7 +121,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             }
         }
     }
-#endif
 }
 __device__ __forceinline__ uint64_t policy_evict_first() {
     uint64_t pol;

@@ -6,7 +6,7 @@
 // src/attention.cu:951-1217).
 //
 // One CTA owns 128 query rows of one (batch, query head) and walks the key/value rows in tiles of 64; two
-// CTAs share an SM (112 KB of shared memory, 256 tensor-memory columns and half the register file each), so
+// CTAs share an SM (96 KB of shared memory, 256 tensor-memory columns and half the register file each), so
 // one CTA's softmax overlaps the other's MMAs:
 //
 //   warp 5  (producer)   TMA: the Q tile once, then K and V tiles into two 2-stage rings. Rank-4 tensor maps
@@ -15,17 +15,19 @@
 //                        swizzled - exactly the K-major (Q, K) and MN-major (V) operand layouts of tcgen05.mma.
 //   warp 4  (MMA issue)  one elected thread: S = Q.K^T (M=128, N=64, K=D) into one of two S buffers in tensor
 //                        memory (the next tile's scores are computed while the softmax warps work on this
-//                        one), and after the softmax warps have produced P: O += P.V (M=128, N=D, K=64);
+//                        one), and after the softmax warps have produced P: O += P.V (M=128, N=D, K=64, A = P from tensor memory);
 //                        completion is signalled by tcgen05.commit on mbarriers.
 //   warps 0-3 (softmax)  thread t owns query row t = tensor-memory lane t: reads its S row with tcgen05.ld
-//                        (no shuffles), online softmax in fp32, writes P as bf16/fp16 into shared memory in the
-//                        swizzled K-major operand layout. The output row accumulates in tensor memory
+//                        (no shuffles), online softmax in fp32, writes P as bf16/fp16 back into tensor memory
+//                        over the scores it came from (tcgen05.st; the P.V MMA takes its A operand from
+//                        tensor memory, so P never touches shared memory, whose bandwidth the operand reads of
+//                        the MMAs already use up). The output row accumulates in tensor memory
 //                        (P.V with accumulate) against a lazily raised reference maximum; raising it
 //                        rescales the row in tensor memory (tcgen05.ld / .st). At the end the row is read
 //                        back, divided by the softmax sum and stored.
 //                        These warps raise their register allowance (setmaxnreg), warps 4-7 lower theirs.
 //
-// Tensor memory: 256 columns (S: 2 x 64, O_tile: D). Every wait is bounded (2 s): on expiry the kernel records
+// Tensor memory: 256 columns (S/P: 2 x 64, O: D). Every wait is bounded (2 s): on expiry the kernel records
 // a status code, all roles leave their loops, tensor memory is released and the kernel returns.
 #pragma once
 
@@ -44,16 +46,14 @@ template <int D> struct PfCfg {
     static constexpr int KV_PANEL = BN * 128;                  // 64 rows x 128 B
     static constexpr int Q_BYTES = (D / 64) * Q_PANEL;
     static constexpr int KV_BYTES = (D / 64) * KV_PANEL;       // one K or V tile
-    static constexpr int P_BYTES = BM * BN * 2;                // 128 x 64 probabilities: one panel
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = OFF_Q + Q_BYTES;
     static constexpr int OFF_V = OFF_K + NST * KV_BYTES;
-    static constexpr int OFF_P = OFF_V + NST * KV_BYTES;
-    static constexpr int OFF_BAR = OFF_P + P_BYTES;            // 16 mbarrier slots
+    static constexpr int OFF_BAR = OFF_V + NST * KV_BYTES;     // 16 mbarrier slots
     static constexpr int OFF_TMEM = OFF_BAR + 16 * 8;
     static constexpr int OFF_ABORT = OFF_TMEM + 8;
     static constexpr int SMEM_BYTES = OFF_ABORT + 8;
-    static constexpr uint32_t TMEM_COLS = 256;                 // S0 [0,64), S1 [64,128), O [128,128+D)
+    static constexpr uint32_t TMEM_COLS = 256;                 // S0/P0 [0,64), S1/P1 [64,128), O [128,128+D)
     static_assert(2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs must fit the 228 KB of one SM");
 };
 
@@ -77,6 +77,16 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Same with the A operand (K-major, 16-bit elements packed two per column) read from tensor memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -125,6 +135,12 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&x)[32]) 
         "tcgen05.wait::st.sync.aligned;"
         ::"r"(taddr), "r"(__float_as_uint(x[0])), "r"(__float_as_uint(x[1])), "r"(__float_as_uint(x[2])), "r"(__float_as_uint(x[3])), "r"(__float_as_uint(x[4])), "r"(__float_as_uint(x[5])), "r"(__float_as_uint(x[6])), "r"(__float_as_uint(x[7])), "r"(__float_as_uint(x[8])), "r"(__float_as_uint(x[9])), "r"(__float_as_uint(x[10])), "r"(__float_as_uint(x[11])), "r"(__float_as_uint(x[12])), "r"(__float_as_uint(x[13])), "r"(__float_as_uint(x[14])), "r"(__float_as_uint(x[15])), "r"(__float_as_uint(x[16])), "r"(__float_as_uint(x[17])), "r"(__float_as_uint(x[18])), "r"(__float_as_uint(x[19])), "r"(__float_as_uint(x[20])), "r"(__float_as_uint(x[21])), "r"(__float_as_uint(x[22])), "r"(__float_as_uint(x[23])), "r"(__float_as_uint(x[24])), "r"(__float_as_uint(x[25])), "r"(__float_as_uint(x[26])), "r"(__float_as_uint(x[27])), "r"(__float_as_uint(x[28])), "r"(__float_as_uint(x[29])), "r"(__float_as_uint(x[30])), "r"(__float_as_uint(x[31]))
         : "memory");
+}
+__device__ __forceinline__ void tmem_st32p(uint32_t taddr, const uint32_t (&x)[32]) {
+    float f[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(x[i]);
+    tmem_st32(taddr, f);
 }
 // Wait that ignores the abort flag: used on the way out, so that no copy or MMA of this CTA is still in
 // flight when its shared and tensor memory are given back. Bounded all the same.
@@ -229,7 +245,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
             constexpr uint32_t IDESC_S = umma_idesc(FMT, 0, 0, C::BM, C::BN);   // Q (K-major) x K^T (K-major)
             constexpr uint32_t IDESC_O = umma_idesc(FMT, 0, 1, C::BM, D);       // P (K-major) x V (MN-major)
-            const uint32_t qa = base + C::OFF_Q, pa = base + C::OFF_P;
+            const uint32_t qa = base + C::OFF_Q;
             auto issue_scores = [&](int j) -> bool {
                 const int s = j & 1;
                 if (!mbar_wait(bar(B_KFULL + s), (j / C::NST) & 1, abort_flag, status, ST_PREFILL_TIMEOUT)) return false;
@@ -257,8 +273,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const uint32_t va = base + C::OFF_V + s * C::KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < C::BN / 16; ++ks)
-                    umma_f16(tmem_o, umma_desc_sw128(pa + ks * 32, 16, 1024),
-                             umma_desc_sw128(va + ks * 2048, C::KV_PANEL, 1024), IDESC_O, (j | ks) > 0);
+                    umma_f16_ts(tmem_o, tmem + s * C::BN + ks * 8,
+                                umma_desc_sw128(va + ks * 2048, C::KV_PANEL, 1024), IDESC_O, (j | ks) > 0);
                 umma_commit(bar(B_VEMPTY + s));
                 umma_commit(bar(B_OFULL));
             }
@@ -295,9 +311,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 for (int i = 0; i < 64; ++i)
                     if (k0 + i > lim) x[i] = -INFINITY;
             }
-            float mx = x[0];
+            float mx8[8];                                   // eight independent chains, then a tree
 #pragma unroll
-            for (int i = 1; i < 64; ++i) mx = fmaxf(mx, x[i]);
+            for (int i = 0; i < 8; ++i) mx8[i] = x[i];
+#pragma unroll
+            for (int i = 8; i < 64; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], x[i]);
+            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                                   fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             bool o_free = j == 0;                           // P.V of the previous tile has completed
             if (j == 0) {
                 m_ref = mx == -INFINITY ? 0.f : mx;
@@ -320,28 +340,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             const float neg_ms = -m_ref * sl2;
             uint32_t pk[32];
-            float psum = 0.f;
+            float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < 64; i += 2) {
                 const float a = ex2(fmaf(x[i], sl2, neg_ms)), bq = ex2(fmaf(x[i + 1], sl2, neg_ms));
-                psum += a + bq;
+                ps4[(i >> 1) & 3] += a + bq;
                 pk[i >> 1] = pack2<T>(a, bq);
             }
-            l_run += psum;
-            // the P tile is free once the previous tile's P.V has read it
+            l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+            // Keeps this thread in step with the P.V completions (a parity wait must never fall two
+            // completions behind); tile j-1's P.V was issued a whole softmax ago, so this rarely waits.
             if (!o_free) {
                 if (!(ok = wait_all(bar(B_OFULL), (j - 1) & 1))) break;
             }
-            // 64 probabilities = eight 16-byte chunks of this row in the swizzled K-major layout
-            const uint32_t prow = base + C::OFF_P + row * 128;
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                const uint32_t addr = prow + (((uint32_t)ch ^ (uint32_t)(row & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                             ::"r"(addr), "r"(pk[ch * 4]), "r"(pk[ch * 4 + 1]), "r"(pk[ch * 4 + 2]), "r"(pk[ch * 4 + 3])
-                             : "memory");
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the tensor core
+            // P replaces the scores it came from: 64 probabilities = 32 packed columns of this lane, the
+            // K-major A operand of the P.V MMA read straight from tensor memory.
+            tmem_st32p(tmem + lane_base + (j & 1) * C::BN, pk);
             tc_fence_before();
             mbar_arrive(bar(B_PREADY));
         }
