@@ -845,6 +845,15 @@ def main():
         if rank == 0:
             run_reference_rows(args)
         return
+    if args.gpus > 1 and "RANK" not in os.environ and args.impl != "reference":
+        # not under a launcher yet: start one rank per GPU
+        import socket
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(args.gpus),
+               "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
     if args.workload in PREFILL_WORKLOADS:
         if world > 1:
             import torch.distributed as dist
@@ -868,15 +877,6 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, w, rank)
         return
-    if args.gpus > 1 and "RANK" not in os.environ:
-        # not under a launcher yet: start one rank per GPU
-        import socket
-        with socket.socket() as s:
-            s.bind(("127.0.0.1", 0))
-            port = s.getsockname()[1]
-        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(args.gpus),
-               "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.abspath(__file__)] + sys.argv[1:]
-        raise SystemExit(subprocess.call(cmd))
     run_ours(args, w, rank, world, local_rank)
 
 
