@@ -7,11 +7,16 @@
 // attn_split_paged_kernel (src/attention.cu:195-319, 336-466, 567-693).
 //
 // 8 warps per CTA. A warp owns whole cache rows (lanes cover the head dim in
-// 4-element chunks, 128-bit loads for fp32, 64-bit for 16-bit storage) and
-// processes R rows per step so that R independent K/V row loads and R x GC
-// shuffle reductions are in flight together; the softmax state is rescaled
-// once per step instead of once per row. GC query heads of the GQA group
-// share every loaded row.
+// 4-element chunks, 128-bit accesses for fp32, 64-bit for 16-bit storage) and
+// processes R rows per step so that R x GC shuffle reductions are in flight
+// together; the softmax state is rescaled once per step instead of once per
+// row. GC query heads of the GQA group share every loaded row.
+//
+// The rows of the NEXT step are always in flight while a step is computed:
+// every lane copies its own chunks with cp.async into a private slot of a
+// two-stage shared-memory area (no registers held across the wait, nothing
+// shared between lanes, so no barrier), following its own copy of the tile
+// walker one step ahead, across tile, unit and sequence boundaries.
 #pragma once
 
 #include "common.cuh"
@@ -20,6 +25,62 @@ namespace ftk {
 
 constexpr int SIMT_WARPS = 8;
 constexpr int SIMT_THREADS = SIMT_WARPS * 32;
+// staging: [warp][2 stages][R rows][K, V][LC chunks][32 lanes] slots of 16 bytes; R * LC == 4 for every variant
+constexpr int SIMT_STAGE_BYTES = SIMT_WARPS * 2 * 4 * 2 * 32 * 16;
+
+// 16-byte (float32) or 8-byte (16-bit storage) asynchronous copy of 4 elements into this lane's slot;
+// bytes == 0 fills the slot with zeros without reading.
+template <typename T>
+__device__ __forceinline__ void cp_async4(uint32_t dst, const T* src, bool live) {
+    if constexpr (sizeof(T) == 4) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(live ? 16 : 0)
+                     : "memory");
+    } else {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(live ? 8 : 0)
+                     : "memory");
+    }
+}
+template <typename T> __device__ __forceinline__ float4 lds4(uint32_t addr) {
+    if constexpr (sizeof(T) == 4) {
+        float4 v;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+        return v;
+    } else {
+        uint2 u;
+        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(u.x), "=r"(u.y) : "r"(addr));
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+            return make_float4(lo.x, lo.y, hi.x, hi.y);
+        } else {
+            const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+            const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+            return make_float4(lo.x, lo.y, hi.x, hi.y);
+        }
+    }
+}
+
+// The sequence of row steps of one warp: tile by tile along the CTA's range, rows t0 = first row of
+// the tile + warp * R, + 8 R, ... Tiles in which the warp has no row are skipped.
+struct RowStep {
+    Walker w;
+    int t0, t_end;
+    bool live;
+};
+__device__ __forceinline__ void rowstep_settle(const DecodeParams& p, RowStep& s, int first_off) {
+    while (s.w.g < s.w.end) {
+        const int t_base = s.w.ti * TILE;
+        s.t_end = min(s.w.len, t_base + TILE);
+        if (s.t0 < 0) s.t0 = t_base + first_off;
+        if (s.t0 < s.t_end) {
+            s.live = true;
+            return;
+        }
+        walker_advance(p, s.w);
+        s.t0 = -1;
+    }
+    s.live = false;
+}
 
 template <int N> struct Log2 { static constexpr int v = (N <= 1) ? 0 : 1 + Log2<N / 2>::v; };
 template <> struct Log2<0> { static constexpr int v = 0; };
@@ -75,6 +136,48 @@ decode_simt_kernel(const DecodeParams p) {
     const T* kbase = reinterpret_cast<const T*>(p.k);
     const T* vbase = reinterpret_cast<const T*>(p.v);
 
+    // this lane's staging slots: ((stage * R + r) * 2 + kv) * LC + j
+    extern __shared__ __align__(16) unsigned char simt_stage[];
+    const uint32_t slot0 = (uint32_t)__cvta_generic_to_shared(simt_stage) + (uint32_t)(warp * 2 * 4 * 2 * 32 + lane) * 16u;
+    auto slot = [&](int stage, int r, int kvsel, int j) {
+        return slot0 + (uint32_t)((((stage * R + r) * 2 + kvsel) * LC + j) * 32) * 16u;
+    };
+    // issue the copies of one step (or nothing when the steps are exhausted) and close the group
+    auto prefetch = [&](const RowStep& s, int stage) {
+        if (s.live) {
+            const int kvh = s.w.ub / p.NCH;
+            const int t_base = s.w.ti * TILE;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int t = s.t0 + r;
+                const bool live = t < s.t_end;
+                size_t row;
+                if (p.table) {
+                    const int tt = live ? t : t_base;
+                    const int blk = __ldg(p.table + (size_t)s.w.b * p.tbl_width + tt / p.page);
+                    row = ((size_t)blk * p.Hkv + kvh) * p.page + (tt % p.page);
+                } else {
+                    row = ((size_t)s.w.b * p.Hkv + kvh) * p.T + (live ? t : t_base);
+                }
+#pragma unroll
+                for (int j = 0; j < LC; ++j) {
+                    const int c = lane + 32 * j;
+                    const bool on = live && c < chunks;
+                    const size_t off = on ? row * D + c * 4 : 0;
+                    cp_async4<T>(slot(stage, r, 0, j), kbase + off, on);
+                    cp_async4<T>(slot(stage, r, 1, j), vbase + off, on);
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    RowStep ahead;
+    ahead.w = w;
+    ahead.t0 = -1;
+    rowstep_settle(p, ahead, warp * R);
+    prefetch(ahead, 0);
+    int stage = 0;
+
     // The R x GC scores of a step are reduced all at once (lane_transpose_reduce), after which lane
     // L owns score number L >> SH = g * R + r. The softmax state is kept the same way: a lane
     // carries (m, l) of its own head g only (l: the share of its own row slot r), computes ONE
@@ -109,31 +212,27 @@ decode_simt_kernel(const DecodeParams p) {
         const int t_base = w.ti * TILE;
         const int t_end = min(w.len, t_base + TILE);
         for (int t0 = t_base + warp * R; t0 < t_end; t0 += SIMT_WARPS * R) {
+            // next step's rows go in flight, then this step's (copied one step ago) are taken
+            if (ahead.live) {
+                ahead.t0 += SIMT_WARPS * R;
+                if (ahead.t0 >= ahead.t_end) {
+                    walker_advance(p, ahead.w);
+                    ahead.t0 = -1;
+                }
+                rowstep_settle(p, ahead, warp * R);
+            }
+            prefetch(ahead, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
             float4 kc[R][LC], vc[R][LC];
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                const int t = t0 + r;
-                const bool live = t < t_end;
-                size_t row;
-                if (p.table) {
-                    const int tt = live ? t : t_base;
-                    const int blk = __ldg(p.table + (size_t)w.b * p.tbl_width + tt / p.page);
-                    row = ((size_t)blk * p.Hkv + kv) * p.page + (tt % p.page);
-                } else {
-                    row = ((size_t)w.b * p.Hkv + kv) * p.T + (live ? t : t_base);
-                }
 #pragma unroll
                 for (int j = 0; j < LC; ++j) {
-                    const int c = lane + 32 * j;
-                    if (live && c < chunks) {
-                        kc[r][j] = Store<T>::ld4(kbase + row * D + c * 4);
-                        vc[r][j] = Store<T>::ld4(vbase + row * D + c * 4);
-                    } else {
-                        kc[r][j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        vc[r][j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
+                    kc[r][j] = lds4<T>(slot(stage, r, 0, j));
+                    vc[r][j] = lds4<T>(slot(stage, r, 1, j));
                 }
             }
+            stage ^= 1;
             float sc[NV];
 #pragma unroll
             for (int g = 0; g < GC; ++g)

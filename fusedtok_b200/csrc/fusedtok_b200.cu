@@ -110,6 +110,18 @@ int set_all_smem_attrs() {
     FTK_SET_ALL(__half)
 #undef FTK_SET_ALL
 #undef FTK_SET
+#define FTK_SET_SIMT(T)                                                                             \
+    if ((rc = set_smem(decode_simt_kernel<T, 1, 1>, SIMT_STAGE_BYTES))) return rc;                  \
+    if ((rc = set_smem(decode_simt_kernel<T, 4, 1>, SIMT_STAGE_BYTES))) return rc;                  \
+    if ((rc = set_smem(decode_simt_kernel<T, 8, 1>, SIMT_STAGE_BYTES))) return rc;                  \
+    if ((rc = set_smem(decode_simt_kernel<T, 1, 2>, SIMT_STAGE_BYTES))) return rc;                  \
+    if ((rc = set_smem(decode_simt_kernel<T, 4, 2>, SIMT_STAGE_BYTES))) return rc;                  \
+    if ((rc = set_smem(decode_simt_kernel<T, 1, 4>, SIMT_STAGE_BYTES))) return rc;                  \
+    if ((rc = set_smem(decode_simt_kernel<T, 2, 4>, SIMT_STAGE_BYTES))) return rc;
+    FTK_SET_SIMT(float)
+    FTK_SET_SIMT(__nv_bfloat16)
+    FTK_SET_SIMT(__half)
+#undef FTK_SET_SIMT
     return rc;
 }
 
@@ -273,7 +285,7 @@ void launch_tc_t(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParam
 }
 
 template <typename T> void launch_simt_t(const DecodeParams& p, int lc, cudaStream_t cs) {
-#define FTK_GO(GC, LC) decode_simt_kernel<T, GC, LC><<<p.ncta, SIMT_THREADS, 0, cs>>>(p)
+#define FTK_GO(GC, LC) decode_simt_kernel<T, GC, LC><<<p.ncta, SIMT_THREADS, SIMT_STAGE_BYTES, cs>>>(p)
     if (lc == 1) { if (p.GC == 1) FTK_GO(1, 1); else if (p.GC == 4) FTK_GO(4, 1); else FTK_GO(8, 1); }
     else if (lc == 2) { if (p.GC == 1) FTK_GO(1, 2); else FTK_GO(4, 2); }
     else { if (p.GC == 1) FTK_GO(1, 4); else FTK_GO(2, 4); }
@@ -366,7 +378,7 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
     if (p.ncta < 1) p.ncta = 1;
 
     Arena a;
-    rc = get_arena(*dev, cs, (size_t)units, p.ncta, p.GC, dim, use_tc, &a);
+    rc = get_arena(*dev, cs, (size_t)units, p.ncta, p.GC, dim, true, &a);
     if (rc) return rc;
     p.ws_ml = a.ws_ml; p.ws_acc = a.ws_acc; p.counters = a.counters; p.status = a.status;
 
