@@ -65,7 +65,14 @@ def _att_launch_fn(t, base):
     return getattr(_fusedtok, base)
 
 
+_raw_stream = getattr(getattr(torch, "_C", None), "_cuda_getCurrentRawStream", None) if _HAS_TORCH else None
+
+
 def _cuda_stream():
+    """The current stream of the current device as a raw handle (the launch runs inside _on_device, so the
+    current device is the tensors' device). The direct accessor avoids building a Stream object per call."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

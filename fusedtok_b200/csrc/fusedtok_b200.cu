@@ -242,6 +242,21 @@ int attention_check(int batch, int hq, int hkv, long long t_seq, int dim) {
 // The cache as a rank-3 tensor: (64 elements, rows with a stride of one cache row, D/64 column blocks of
 // 128 bytes). A box [64, box_rows, D/64] is one copy and lands as [column block][row][128 B].
 int encode_map(CUtensorMap* map, int dt, const void* base, unsigned long long rows, int dim, int box_rows) {
+    // A descriptor is a pure function of these five values, and a decode loop asks for the same two every
+    // step: keep the last few per thread and skip the driver call.
+    struct Entry {
+        const void* base = nullptr;
+        unsigned long long rows = 0;
+        int dt = -1, dim = 0, box_rows = 0;
+        CUtensorMap map;
+    };
+    constexpr int kSlots = 8;
+    thread_local Entry cache[kSlots];
+    Entry& e = cache[(reinterpret_cast<uintptr_t>(base) >> 8) % kSlots];
+    if (e.base == base && e.rows == rows && e.dt == dt && e.dim == dim && e.box_rows == box_rows) {
+        *map = e.map;
+        return FUSEDTOK_OK;
+    }
     const cuuint64_t gdim[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(dim / 64)};
     const cuuint64_t gstride[2] = {(cuuint64_t)dim * 2, 128u};
     const cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)(dim / 64)};
@@ -252,6 +267,8 @@ int encode_map(CUtensorMap* map, int dt, const void* base, unsigned long long ro
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(FUSEDTOK_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed (code " + std::to_string((int)r) + ")");
+    e.base = base; e.rows = rows; e.dt = dt; e.dim = dim; e.box_rows = box_rows;
+    e.map = *map;
     return FUSEDTOK_OK;
 }
 
