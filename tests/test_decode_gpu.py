@@ -398,3 +398,40 @@ def test_partial_triples_merge_to_full_result(dt, code, tol):
     assert np.abs(out.float().cpu().numpy() - ref).max() <= tol
     assert torch.count_nonzero(out[2]) == 0
     assert_status_ok()
+
+
+@pytest.mark.gpu
+def test_missing_peer_expires_with_a_status_and_the_context_stays_usable():
+    """Failure detection without a fault: a KV-split step whose peer never delivers. The second exchange buffer
+    here belongs to no rank, so nothing ever raises this rank's flag for it; the merge kernel's wait (2 s limit)
+    must run out, report status 5 and return, and the next ordinary call must work."""
+    import time
+    b, hq, hkv, d, t = 2, 8, 2, 64, 128
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(b, hq, d, generator=g).bfloat16().cuda()
+    k = torch.randn(b, hkv, t, d, generator=g).bfloat16().cuda()
+    v = torch.randn(b, hkv, t, d, generator=g).bfloat16().cuda()
+    out = torch.empty_like(q)
+    ft.attention_decode(q, k, v)                                   # arena and status word exist
+    assert _fusedtok.attention_device_status() == 0
+    mine, _ = _fusedtok.exchange_alloc(2, b, hq, d)
+    ghost, _ = _fusedtok.exchange_alloc(2, b, hq, d)
+    try:
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        _fusedtok.attention_decode_exchange_launch(1, q.data_ptr(), k.data_ptr(), v.data_ptr(), 0, out.data_ptr(),
+                                                   [mine, ghost], 0, b, hq, hkv, t, d,
+                                                   torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t0
+        assert 1.5 < waited < 15.0, waited
+        assert _fusedtok.attention_device_status() == 5
+        assert _fusedtok.attention_device_status() == 0             # reading it clears it
+        y = ft.attention_decode(q, k, v)
+        want = oracle.decode(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy())
+        np.testing.assert_allclose(y.float().cpu().numpy(), want, atol=2e-2, rtol=2e-2)
+        assert _fusedtok.attention_device_status() == 0
+    finally:
+        torch.cuda.synchronize()
+        _fusedtok.exchange_free(mine)
+        _fusedtok.exchange_free(ghost)
