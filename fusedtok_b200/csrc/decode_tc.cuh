@@ -59,7 +59,7 @@ template <int D> struct TcCfg {
 #ifdef FTK_NS
     static constexpr int NS = FTK_NS;
 #else
-    static constexpr int NS = (D == 128) ? 4 : 8;
+    static constexpr int NS = (D == 64) ? 8 : ((D == 128) ? 4 : 2);     // 128 KB of K/V tiles (96 KB at D = 192)
 #endif
     static_assert(NS % 2 == 0, "ring depth must be even (see above)");
     static constexpr int ACC_STRIDE = D + 4;           // floats; rows stay 16-byte aligned
@@ -187,7 +187,7 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 // ---- the kernel ------------------------------------------------------------
-// T: __nv_bfloat16 or __half. D: 64 or 128. GP: 8 or 16 = query-head rows of
+// T: __nv_bfloat16 or __half. D: 64, 128, 192 or 256 (the last two with GP = 8 only). GP: 8 or 16 = query-head rows of
 // the MMA tile that carry data (heads per unit <= GP). PAGED selects the
 // block-table front end; PAGE_LE_TILE says whether a page is at most one tile.
 template <typename T, int D, int GP, bool PAGED>

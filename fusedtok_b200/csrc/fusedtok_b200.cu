@@ -105,7 +105,8 @@ int set_all_smem_attrs() {
     if ((rc = set_smem(decode_tc_kernel<T, D, GP, PG>, TcCfg<D>::SMEM_BYTES))) return rc;
 #define FTK_SET_ALL(T)                                                                          \
     FTK_SET(T, 64, 8, false) FTK_SET(T, 64, 16, false) FTK_SET(T, 64, 8, true) FTK_SET(T, 64, 16, true) \
-    FTK_SET(T, 128, 8, false) FTK_SET(T, 128, 16, false) FTK_SET(T, 128, 8, true) FTK_SET(T, 128, 16, true)
+    FTK_SET(T, 128, 8, false) FTK_SET(T, 128, 16, false) FTK_SET(T, 128, 8, true) FTK_SET(T, 128, 16, true) \
+    FTK_SET(T, 192, 8, false) FTK_SET(T, 192, 8, true) FTK_SET(T, 256, 8, false) FTK_SET(T, 256, 8, true)
     FTK_SET_ALL(__nv_bfloat16)
     FTK_SET_ALL(__half)
 #undef FTK_SET_ALL
@@ -297,7 +298,9 @@ void launch_tc_t(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParam
         else launch_tc<T, D, GP, false>(mk, mv, p, cs);            \
     } while (0)
     if (p.D == 64) { if (gp == 8) FTK_GO(64, 8); else FTK_GO(64, 16); }
-    else           { if (gp == 8) FTK_GO(128, 8); else FTK_GO(128, 16); }
+    else if (p.D == 128) { if (gp == 8) FTK_GO(128, 8); else FTK_GO(128, 16); }
+    else if (p.D == 192) FTK_GO(192, 8);
+    else FTK_GO(256, 8);
 #undef FTK_GO
 }
 
@@ -352,7 +355,7 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
     const bool paged = table != nullptr;
     const unsigned long long map_rows =
         paged ? 0ull : (unsigned long long)batch * hkv * (unsigned long long)rows;
-    bool use_tc = dt != F32 && (dim == 64 || dim == 128) &&
+    bool use_tc = dt != F32 && (dim == 64 || dim == 128 || dim == 192 || dim == 256) &&
                   ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
                   ((reinterpret_cast<uintptr_t>(q)) & 3u) == 0;
     if (use_tc && !paged && map_rows >= (1ull << 31)) use_tc = false;
@@ -377,7 +380,7 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
     p.scale = 1.0f / sqrtf((float)dim);
     int lc = 1, gp = 8;
     if (use_tc) {
-        p.GC = std::min(G, 16);
+        p.GC = std::min(G, dim > 128 ? 8 : 16);       // the wide heads keep 8 query heads per MMA tile
         gp = p.GC <= 8 ? 8 : 16;
     } else {
         lc = dim <= 128 ? 1 : (dim <= 256 ? 2 : 4);
@@ -1148,7 +1151,7 @@ int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const voi
     // same kernel selection as the allocating launcher
     const int G = q_heads / kv_heads;
     const unsigned long long map_rows = (unsigned long long)batch * kv_heads * (unsigned long long)cache_rows;
-    const bool use_tc = dtype != F32 && (dim == 64 || dim == 128) && map_rows < (1ull << 31) &&
+    const bool use_tc = dtype != F32 && (dim == 64 || dim == 128 || dim == 192 || dim == 256) && map_rows < (1ull << 31) &&
                         ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
                         ((reinterpret_cast<uintptr_t>(q)) & 3u) == 0;
     DecodeParams p;
@@ -1158,7 +1161,7 @@ int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const voi
     p.scale = 1.0f / sqrtf((float)dim);
     int lc = 1, gp = 8;
     if (use_tc) {
-        p.GC = std::min(G, 16);
+        p.GC = std::min(G, dim > 128 ? 8 : 16);       // the wide heads keep 8 query heads per MMA tile
         gp = p.GC <= 8 ? 8 : 16;
     } else {
         lc = dim <= 128 ? 1 : (dim <= 256 ? 2 : 4);

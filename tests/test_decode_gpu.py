@@ -190,6 +190,40 @@ def test_half_matches_oracle(dt, tol, shape):
 
 
 @pytest.mark.parametrize("dt,tol", HALF)
+@pytest.mark.parametrize("d", [192, 256])
+@pytest.mark.parametrize("hq,hkv", [(8, 8), (8, 2), (16, 2), (32, 2), (10, 2)])
+def test_half_wide_heads(dt, tol, d, hq, hkv):
+    """Head dims 192 and 256 on the tensor-core kernel (8 query heads per MMA tile, groups above 8 in chunks),
+    contiguous with ragged lengths across tile boundaries, and paged."""
+    rng = np.random.default_rng(d + hq * 3 + hkv)
+    b, t = 3, 700
+    q, k, v, lens = cases.make_case(rng, b, hq, hkv, t, d, True)
+    lens[:] = [t, 65, 333]
+    qt, kt, vt, (qr, kr, vr) = half_case(dt, q, k, v)
+    ref = oracle.decode(qr, kr, vr, lens)
+    y = ft.attention_decode(qt, kt, vt, torch.from_numpy(lens).cuda()).float().cpu().numpy()
+    assert np.abs(y - ref).max() <= tol
+    assert mean_rel(y, ref) <= 1e-2
+    # the same cache cut into pages of 16 rows, blocks shuffled
+    page = 16
+    nblk = (t + page - 1) // page
+    pad = nblk * page - t
+    kp = torch.nn.functional.pad(kt, (0, 0, 0, pad)).view(b, hkv, nblk, page, d).permute(0, 2, 1, 3, 4).reshape(
+        b * nblk, hkv, page, d)
+    vp = torch.nn.functional.pad(vt, (0, 0, 0, pad)).view(b, hkv, nblk, page, d).permute(0, 2, 1, 3, 4).reshape(
+        b * nblk, hkv, page, d)
+    perm = torch.randperm(b * nblk, generator=torch.Generator().manual_seed(d)).cuda()
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(b * nblk, device="cuda")
+    table = inv.view(b, nblk).to(torch.int32).contiguous()          # sequence b, page s lives in block inv[b*nblk+s]
+    kpool, vpool = kp[perm].contiguous(), vp[perm].contiguous()
+    if hq // hkv in (1, 2, 4, 8, 16):
+        yp = ft.attention_decode_paged(qt, kpool, vpool, table, torch.from_numpy(lens).cuda()).float().cpu().numpy()
+        assert np.abs(yp - ref).max() <= tol
+    assert_status_ok()
+
+
+@pytest.mark.parametrize("dt,tol", HALF)
 def test_half_other_dims_take_generic_kernel(dt, tol):
     rng = np.random.default_rng(7)
     for d in (32, 96, 256):
