@@ -140,6 +140,8 @@ int set_prefill_smem_attrs() {
     if ((rc = set_smem(prefill_tc_kernel<__nv_bfloat16, 128>, PfCfg<128>::SMEM_BYTES))) return rc;
     if ((rc = set_smem(prefill_tc_kernel<__half, 64>, PfCfg<64>::SMEM_BYTES))) return rc;
     if ((rc = set_smem(prefill_tc_kernel<__half, 128>, PfCfg<128>::SMEM_BYTES))) return rc;
+    if ((rc = set_smem(prefill_tc_kernel<__nv_bfloat16, 256>, PfCfg<256>::SMEM_BYTES))) return rc;
+    if ((rc = set_smem(prefill_tc_kernel<__half, 256>, PfCfg<256>::SMEM_BYTES))) return rc;
     return rc;
 }
 
@@ -512,8 +514,10 @@ void launch_prefill_tc_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUt
     const unsigned grid = (unsigned)((long long)p.B * p.Hq * p.q_tiles);
     if (p.D == 64)
         prefill_tc_kernel<T, 64><<<grid, PF_THREADS, PfCfg<64>::SMEM_BYTES, cs>>>(mq, mk, mv, p, status);
-    else
+    else if (p.D == 128)
         prefill_tc_kernel<T, 128><<<grid, PF_THREADS, PfCfg<128>::SMEM_BYTES, cs>>>(mq, mk, mv, p, status);
+    else
+        prefill_tc_kernel<T, 256><<<grid, PF_THREADS, PfCfg<256>::SMEM_BYTES, cs>>>(mq, mk, mv, p, status);
 }
 
 // Prefill launcher. reference: attention_prefill_launch_t, src/attention.cu:1649-1712.
@@ -561,7 +565,8 @@ int prefill_common(int dt, const void* q, const void* k, const void* v, void* ou
     p.causal = causal ? 1 : 0;
     p.scale = 1.0f / sqrtf((float)dim);
     // tensor-core path: half storage, head dim 64 / 128, 16-byte aligned operands
-    const bool use_tc = dt != F32 && (dim == 64 || dim == 128) && (all & 15u) == 0 && !g_prefill_force_simt;
+    const bool use_tc = dt != F32 && (dim == 64 || dim == 128 || dim == 256) && (all & 15u) == 0 &&
+                        !g_prefill_force_simt;
     if (use_tc) {
         if ((rc = get_encode_fn())) return rc;
         {

@@ -1,5 +1,5 @@
 // Prefill (fresh-sequence self-attention) on the 5th-generation tensor cores: bf16 / fp16 storage,
-// head dim 64 or 128.
+// head dim 64, 128 or 256.
 //
 // Operator: see prefill_simt.cuh (reference: attention_prefill_launch_bf16 / _fp16,
 // include/fusedtok/cuda_launch.hpp:370-379; the reference's own tensor-core path is the mma.sync kernel at
@@ -40,7 +40,7 @@ constexpr int PF_THREADS = 256;
 constexpr int ST_PREFILL_TIMEOUT = 6;
 
 template <int D> struct PfCfg {
-    static_assert(D == 64 || D == 128, "tensor-core prefill: head dim 64 or 128");
+    static_assert(D == 64 || D == 128 || D == 256, "tensor-core prefill: head dim 64, 128 or 256");
     static constexpr int BM = 128, BN = 64, NST = 2;
     static constexpr int Q_PANEL = BM * 128;                   // bytes: 128 rows x 128 B
     static constexpr int KV_PANEL = BN * 128;                  // 64 rows x 128 B
@@ -53,8 +53,11 @@ template <int D> struct PfCfg {
     static constexpr int OFF_TMEM = OFF_BAR + 16 * 8;
     static constexpr int OFF_ABORT = OFF_TMEM + 8;
     static constexpr int SMEM_BYTES = OFF_ABORT + 8;
-    static constexpr uint32_t TMEM_COLS = 256;                 // S0/P0 [0,64), S1/P1 [64,128), O [128,128+D)
-    static_assert(2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs must fit the 228 KB of one SM");
+    // S0/P0 [0,64), S1/P1 [64,128), O [128,128+D). Head dim 256 needs 384 columns (allocations are powers of
+    // two) and 192 KB of shared memory: one CTA per SM there, two otherwise.
+    static constexpr uint32_t TMEM_COLS = D <= 128 ? 256 : 512;
+    static_assert(D > 128 || 2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs must fit the 228 KB of one SM");
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------

@@ -154,6 +154,25 @@ def test_gpu_half_dim_matrix(dtname, rtol, atol, s, d):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtname,rtol,atol", HALF)
+@pytest.mark.parametrize("s", [64, 129, 300])
+def test_gpu_half_head_dim_256(dtname, rtol, atol, s):
+    """Head dim 256 on the tensor-core kernel (512 tensor-memory columns, one CTA per SM)."""
+    torch = _torch()
+    import fusedtok_b200 as ft
+    dt = getattr(torch, dtname)
+    b, hq, hkv, d = 2, 4, 2, 256
+    g = torch.Generator().manual_seed(s)
+    q = torch.randn(b, hq, s, d, generator=g).to(dt)
+    k = torch.randn(b, hkv, s, d, generator=g).to(dt)
+    v = torch.randn(b, hkv, s, d, generator=g).to(dt)
+    for causal in (True, False):
+        out = ft.attention_prefill(q.cuda(), k.cuda(), v.cuda(), causal=causal)
+        want = oracle.prefill(q.float().numpy(), k.float().numpy(), v.float().numpy(), causal)
+        np.testing.assert_allclose(out.float().cpu().numpy(), want, rtol=rtol, atol=atol)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtname,rtol,atol", HALF)
 @pytest.mark.parametrize("d", [36, 48, 80, 96, 112, 256])
 def test_gpu_half_other_dims(dtname, rtol, atol, d):
     """reference: test_prefill_non_instantiated_wmma_dims / _wmma_and_fallback_agree, test_attention.py:697-730."""
