@@ -45,8 +45,11 @@ constexpr int TC_THREADS = (NCW + 1) * 32;    // + 1 producer warp
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
 
 template <int D> struct TcCfg {
-    static constexpr int NH = D / 64;                  // 128-byte column blocks per row
-    static constexpr int KV_BYTES = TILE * D * 2;      // K (or V) bytes per stage
+    static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head dim: a multiple of 16 up to 256");
+    static constexpr int NH = (D + 63) / 64;           // 128-byte column blocks per row (the last one may be partial)
+    static constexpr int DP = NH * 64;                 // row width in shared memory, elements
+    static constexpr bool SPLIT = (D % 64) != 0;       // one copy per column block (rank-2 map) instead of one per box
+    static constexpr int KV_BYTES = TILE * DP * 2;     // K (or V) bytes per stage
     static constexpr int STAGE_BYTES = 2 * KV_BYTES;
     // Ring depth. MUST be even: tiles alternate between the two consumer
     // groups, and with an even depth a stage is always consumed by the same
@@ -59,7 +62,7 @@ template <int D> struct TcCfg {
 #ifdef FTK_NS
     static constexpr int NS = FTK_NS;
 #else
-    static constexpr int NS = (D == 64) ? 8 : ((D == 128) ? 4 : 2);     // 128 KB of K/V tiles (96 KB at D = 192)
+    static constexpr int NS = (DP == 64) ? 8 : ((DP == 128) ? 4 : 2);   // 128 KB of K/V tiles (96 KB at 192)
 #endif
     static_assert(NS % 2 == 0, "ring depth must be even (see above)");
     static constexpr int ACC_STRIDE = D + 4;           // floats; rows stay 16-byte aligned
@@ -127,6 +130,20 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
     return pol;
 }
+// Head dims that are not a multiple of 64: the cache is a rank-2 tensor (D elements, rows) and a box is copied
+// one 64-element column block at a time; the part of the last block past D is zero-filled by the copy engine
+// (never read: the MMAs stop at D), and nothing is read past the end of a row. Same shared-memory layout.
+template <int NH>
+__device__ __forceinline__ void tma_load_rows_split(uint32_t dst, const CUtensorMap* map, int row, uint32_t panel_bytes,
+                                                    uint32_t bar, uint64_t pol) {
+#pragma unroll
+    for (int cb = 0; cb < NH; ++cb)
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+            " [%0], [%1, {%2, %3}], [%4], %5;"
+            ::"r"(dst + cb * panel_bytes), "l"(map), "r"(cb * 64), "r"(row), "r"(bar), "l"(pol)
+            : "memory");
+}
 // Box [64 elements, box_rows rows, D/64 column blocks] starting at row `row`.
 __device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* map, int row, uint32_t bar,
                                               uint64_t pol) {
@@ -187,7 +204,7 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 // ---- the kernel ------------------------------------------------------------
-// T: __nv_bfloat16 or __half. D: 64, 128, 192 or 256 (the last two with GP = 8 only). GP: 8 or 16 = query-head rows of
+// T: __nv_bfloat16 or __half. D: a multiple of 16 up to 256 (above 128, and where not a multiple of 64, with GP = 8 only). GP: 8 or 16 = query-head rows of
 // the MMA tile that carry data (heads per unit <= GP). PAGED selects the
 // block-table front end; PAGE_LE_TILE says whether a page is at most one tile.
 template <typename T, int D, int GP, bool PAGED>
@@ -268,7 +285,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     }
                     const int blk = __shfl_sync(0xffffffffu, tbl_val, (pg0 - tbl_base + lane) & 31);
                     row = (blk * p.Hkv + kv) * p.page;
-                    bytes = (uint32_t)(npg * p.page * D * 4);
+                    bytes = (uint32_t)(npg * p.page * Cfg::DP * 4);
                 } else {
                     const int blk = __ldg(p.table + (size_t)w.b * p.tbl_width + t0 / p.page);
                     row = (blk * p.Hkv + kv) * p.page + (t0 % p.page);
@@ -286,17 +303,22 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             const uint32_t dst_v = dst_k + Cfg::KV_BYTES;
             const uint32_t fb = bar_full + s * 8;
             if (lane == 0) mbar_expect_tx(fb, bytes);
+            const uint32_t panel_bytes = (uint32_t)p.box_rows * 128u;
+            auto copy_box = [&](uint32_t dst, const CUtensorMap* map) {
+                if constexpr (Cfg::SPLIT) tma_load_rows_split<Cfg::NH>(dst, map, row, panel_bytes, fb, pol);
+                else tma_load_rows(dst, map, row, fb, pol);
+            };
             if (!PAGED || p.page > TILE) {
                 if (lane == 0) {
-                    tma_load_rows(dst_k, &tm_k, row, fb, pol);
-                    tma_load_rows(dst_v, &tm_v, row, fb, pol);
+                    copy_box(dst_k, &tm_k);
+                    copy_box(dst_v, &tm_v);
                 }
             } else {
                 __syncwarp();                                            // expect_tx before any complete_tx
                 if (lane < npg) {
-                    const uint32_t off = (uint32_t)(lane * p.page) * (uint32_t)(D * 2);   // page-major stage
-                    tma_load_rows(dst_k + off, &tm_k, row, fb, pol);
-                    tma_load_rows(dst_v + off, &tm_v, row, fb, pol);
+                    const uint32_t off = (uint32_t)(lane * p.page) * (uint32_t)(Cfg::DP * 2);   // page-major stage
+                    copy_box(dst_k + off, &tm_k);
+                    copy_box(dst_v + off, &tm_v);
                 }
             }
             ++issued;
@@ -358,7 +380,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const int box_rows = p.box_rows, box_shift = p.box_shift;
     const uint32_t half_stride = (uint32_t)box_rows * 128u;
     auto row_off = [&](int r) -> uint32_t {
-        return (uint32_t)(r >> box_shift) * (uint32_t)(box_rows * D * 2) + (uint32_t)(r & (box_rows - 1)) * 128u;
+        return (uint32_t)(r >> box_shift) * (uint32_t)(box_rows * Cfg::DP * 2) + (uint32_t)(r & (box_rows - 1)) * 128u;
     };
     // per-lane ldmatrix geometry (constant over the kernel)
     const int lrow = lane & 7, lmat = lane >> 3;

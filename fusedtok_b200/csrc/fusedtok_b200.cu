@@ -106,7 +106,10 @@ int set_all_smem_attrs() {
 #define FTK_SET_ALL(T)                                                                          \
     FTK_SET(T, 64, 8, false) FTK_SET(T, 64, 16, false) FTK_SET(T, 64, 8, true) FTK_SET(T, 64, 16, true) \
     FTK_SET(T, 128, 8, false) FTK_SET(T, 128, 16, false) FTK_SET(T, 128, 8, true) FTK_SET(T, 128, 16, true) \
-    FTK_SET(T, 192, 8, false) FTK_SET(T, 192, 8, true) FTK_SET(T, 256, 8, false) FTK_SET(T, 256, 8, true)
+    FTK_SET(T, 192, 8, false) FTK_SET(T, 192, 8, true) FTK_SET(T, 256, 8, false) FTK_SET(T, 256, 8, true) \
+    FTK_SET(T, 32, 8, false) FTK_SET(T, 32, 8, true) FTK_SET(T, 80, 8, false) FTK_SET(T, 80, 8, true)       \
+    FTK_SET(T, 96, 8, false) FTK_SET(T, 96, 8, true) FTK_SET(T, 112, 8, false) FTK_SET(T, 112, 8, true)     \
+    FTK_SET(T, 160, 8, false) FTK_SET(T, 160, 8, true)
     FTK_SET_ALL(__nv_bfloat16)
     FTK_SET_ALL(__half)
 #undef FTK_SET_ALL
@@ -260,14 +263,24 @@ int encode_map(CUtensorMap* map, int dt, const void* base, unsigned long long ro
         *map = e.map;
         return FUSEDTOK_OK;
     }
-    const cuuint64_t gdim[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(dim / 64)};
-    const cuuint64_t gstride[2] = {(cuuint64_t)dim * 2, 128u};
-    const cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)(dim / 64)};
+    const CUtensorMapDataType dtype = dt == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const cuuint32_t estr[3] = {1u, 1u, 1u};
-    const CUresult r = g_encode(map, dt == BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                                3, const_cast<void*>(base), gdim, gstride, box, estr,
-                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r;
+    if (dim % 64 == 0) {
+        const cuuint64_t gdim[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(dim / 64)};
+        const cuuint64_t gstride[2] = {(cuuint64_t)dim * 2, 128u};
+        const cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)(dim / 64)};
+        r = g_encode(map, dtype, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        // rank 2: (D elements, rows); a box is one 64-element column block of box_rows rows, the part of the
+        // last block past D comes back as zeros
+        const cuuint64_t gdim[2] = {(cuuint64_t)dim, (cuuint64_t)rows};
+        const cuuint64_t gstride[1] = {(cuuint64_t)dim * 2};
+        const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+        r = g_encode(map, dtype, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS)
         return fail(FUSEDTOK_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed (code " + std::to_string((int)r) + ")");
     e.base = base; e.rows = rows; e.dt = dt; e.dim = dim; e.box_rows = box_rows;
@@ -302,7 +315,12 @@ void launch_tc_t(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParam
     if (p.D == 64) { if (gp == 8) FTK_GO(64, 8); else FTK_GO(64, 16); }
     else if (p.D == 128) { if (gp == 8) FTK_GO(128, 8); else FTK_GO(128, 16); }
     else if (p.D == 192) FTK_GO(192, 8);
-    else FTK_GO(256, 8);
+    else if (p.D == 256) FTK_GO(256, 8);
+    else if (p.D == 32) FTK_GO(32, 8);
+    else if (p.D == 80) FTK_GO(80, 8);
+    else if (p.D == 96) FTK_GO(96, 8);
+    else if (p.D == 112) FTK_GO(112, 8);
+    else FTK_GO(160, 8);
 #undef FTK_GO
 }
 
@@ -315,6 +333,10 @@ template <typename T> void launch_simt_t(const DecodeParams& p, int lc, cudaStre
 }
 
 inline bool is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
+// head dims the tensor-core decode kernel is instantiated for
+inline bool tc_head_dim(int d) {
+    return d == 32 || d == 64 || d == 80 || d == 96 || d == 112 || d == 128 || d == 160 || d == 192 || d == 256;
+}
 
 // The one launcher behind every zero-copy entry point.
 // table == nullptr: contiguous cache with `rows` cache rows per (b, kv).
@@ -357,7 +379,7 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
     const bool paged = table != nullptr;
     const unsigned long long map_rows =
         paged ? 0ull : (unsigned long long)batch * hkv * (unsigned long long)rows;
-    bool use_tc = dt != F32 && (dim == 64 || dim == 128 || dim == 192 || dim == 256) &&
+    bool use_tc = dt != F32 && tc_head_dim(dim) &&
                   ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
                   ((reinterpret_cast<uintptr_t>(q)) & 3u) == 0;
     if (use_tc && !paged && map_rows >= (1ull << 31)) use_tc = false;
@@ -382,7 +404,7 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
     p.scale = 1.0f / sqrtf((float)dim);
     int lc = 1, gp = 8;
     if (use_tc) {
-        p.GC = std::min(G, dim > 128 ? 8 : 16);       // the wide heads keep 8 query heads per MMA tile
+        p.GC = std::min(G, (dim == 64 || dim == 128) ? 16 : 8);   // only these two have the 16-head MMA tile
         gp = p.GC <= 8 ? 8 : 16;
     } else {
         lc = dim <= 128 ? 1 : (dim <= 256 ? 2 : 4);
@@ -1156,7 +1178,7 @@ int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const voi
     // same kernel selection as the allocating launcher
     const int G = q_heads / kv_heads;
     const unsigned long long map_rows = (unsigned long long)batch * kv_heads * (unsigned long long)cache_rows;
-    const bool use_tc = dtype != F32 && (dim == 64 || dim == 128 || dim == 192 || dim == 256) && map_rows < (1ull << 31) &&
+    const bool use_tc = dtype != F32 && tc_head_dim(dim) && map_rows < (1ull << 31) &&
                         ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
                         ((reinterpret_cast<uintptr_t>(q)) & 3u) == 0;
     DecodeParams p;
@@ -1166,7 +1188,7 @@ int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const voi
     p.scale = 1.0f / sqrtf((float)dim);
     int lc = 1, gp = 8;
     if (use_tc) {
-        p.GC = std::min(G, dim > 128 ? 8 : 16);       // the wide heads keep 8 query heads per MMA tile
+        p.GC = std::min(G, (dim == 64 || dim == 128) ? 16 : 8);   // only these two have the 16-head MMA tile
         gp = p.GC <= 8 ? 8 : 16;
     } else {
         lc = dim <= 128 ? 1 : (dim <= 256 ? 2 : 4);

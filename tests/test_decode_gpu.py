@@ -190,11 +190,12 @@ def test_half_matches_oracle(dt, tol, shape):
 
 
 @pytest.mark.parametrize("dt,tol", HALF)
-@pytest.mark.parametrize("d", [192, 256])
+@pytest.mark.parametrize("d", [32, 80, 96, 112, 160, 192, 256])
 @pytest.mark.parametrize("hq,hkv", [(8, 8), (8, 2), (16, 2), (32, 2), (10, 2)])
-def test_half_wide_heads(dt, tol, d, hq, hkv):
-    """Head dims 192 and 256 on the tensor-core kernel (8 query heads per MMA tile, groups above 8 in chunks),
-    contiguous with ragged lengths across tile boundaries, and paged."""
+def test_half_other_tensor_core_head_dims(dt, tol, d, hq, hkv):
+    """Head dims other than 64 / 128 on the tensor-core kernel (8 query heads per MMA tile, groups above 8 in
+    chunks; dims that are not a multiple of 64 through per-column-block copies), contiguous with ragged lengths
+    across tile boundaries, and paged."""
     rng = np.random.default_rng(d + hq * 3 + hkv)
     b, t = 3, 700
     q, k, v, lens = cases.make_case(rng, b, hq, hkv, t, d, True)
