@@ -488,6 +488,29 @@ def run_ours(args, w, rank, world, local_rank):
         gbs, sps, kind, sample, _ = cpu_baseline(w, 12.0, threads)
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": kind,
                                 "sample": sample, "seq_steps_per_s": sps}
+    if world == 1 and not w["paged"] and not args.no_cpu_baseline:
+        # the staged C-ABI entry point: every operand in HOST memory (float32, as in the reference's staged
+        # binding), whole cache copied to the device inside the call, result copied back; bytes counted at fp32
+        try:
+            from fusedtok_b200 import _fusedtok as _ft
+            k0, v0 = sets[0]
+            hq_, hk_, hv_ = q.float().cpu().numpy(), k0.float().cpu().numpy(), v0.float().cpu().numpy()
+            hl_ = None if lens_t is None else lens_t.cpu().numpy()
+            _ft.attention_decode(hq_, hk_, hv_, hl_, batch, w["Hq"], w["Hkv"], wl["T"], w["D"])
+            t0 = time.perf_counter()
+            n_st = 2
+            for _ in range(n_st):
+                ys = _ft.attention_decode(hq_, hk_, hv_, hl_, batch, w["Hq"], w["Hkv"], wl["T"], w["D"])
+            st_s = (time.perf_counter() - t0) / n_st
+            fp32_bytes = bytes_step * 4 // (4 if w["dtype"] == "f32" else 2)
+            line["e2e_staged"] = {"value": fp32_bytes / st_s / 1e9, "unit": "GB/s", "ms_per_step": st_s * 1e3,
+                                  "h2d_bytes_per_step": int(hq_.nbytes + hk_.nbytes + hv_.nbytes),
+                                  "d2h_bytes_per_step": int(ys.nbytes), "steps": n_st,
+                                  "note": "fusedtok_attention_decode: all operands in pageable host memory, float32; "
+                                          "dominated by the host-to-device copy of the whole cache"}
+            del hq_, hk_, hv_
+        except Exception as exc:   # informational only
+            line["e2e_staged"] = {"error": str(exc)[:200]}
     if world == 1:
         # the reference's own GPU kernels on the same inputs (informational)
         try:
