@@ -26,7 +26,7 @@ except ImportError:  # pragma: no cover - torch is optional, as in the reference
 
 __version__ = "0.1.0"
 __all__ = ["attention_decode", "attention_decode_paged", "attention_prefill", "kv_append", "kv_append_paged",
-           "rope", "cuda_available"]
+           "rope", "rope_kv_append", "rope_kv_append_paged", "cuda_available"]
 
 _PAGED_GROUPS = (1, 2, 4, 8, 16)
 
@@ -535,3 +535,86 @@ def kv_append_paged(k_pool, v_pool, block_table, k_new, v_new, lens, *, cuda=Fal
     _fusedtok.kv_append_paged(arr_kn, arr_vn, arr_t, arr_l, arr_kp, arr_vp, b, hkv, d, page,
                               arr_t.shape[1], nb)
     return None
+
+
+def _dtype_code(t):
+    return {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[t.dtype]
+
+
+def _rope_append_checks(q, k_new, v_new, cache_k, cache_v, hkv, d, theta, pos_offset, out):
+    for name, t in (("q", q), ("k_new", k_new), ("v_new", v_new), ("k cache", cache_k), ("v cache", cache_v)):
+        _check_torch_att(t, name)
+        if t.dtype is not q.dtype:
+            raise TypeError(f"{name} must have the dtype of q")
+        if t.device != q.device:
+            raise TypeError(f"{name} must be on the device of q")
+    if q.ndim != 3 or k_new.ndim != 3 or v_new.ndim != 3:
+        raise ValueError("q must be [B, Hq, D]; k_new / v_new [B, Hkv, D]")
+    b, hq, dq = q.shape
+    if dq != d or tuple(k_new.shape) != (b, hkv, d) or v_new.shape != k_new.shape or cache_v.shape != cache_k.shape:
+        raise ValueError("q / k_new / v_new must match the cache layout")
+    if hq % hkv:
+        raise ValueError("q heads must be a multiple of kv heads")
+    if d % 4:
+        raise ValueError("head dim must be a multiple of 4")
+    if pos_offset < 0:
+        raise ValueError("pos_offset must be >= 0")
+    if not theta > 0:
+        raise ValueError("theta must be positive")
+    if out is None:
+        return torch.empty_like(q)
+    _check_torch_att(out, "out")
+    if out.dtype is not q.dtype or out.shape != q.shape or out.device != q.device:
+        raise ValueError("out must match q")
+    return out
+
+
+def rope_kv_append(q, k_cache, v_cache, k_new, v_new, lens, *, theta=10000.0, pos_offset=0, neox=False, out=None):
+    """The elementwise part of one decode step in a single launch: rotate ``q`` ([B, Hq, D]) and
+    ``k_new`` ([B, Hkv, D]) to position ``lens[b] + pos_offset`` and write the rotated key and ``v_new``
+    into row ``lens[b]`` of the contiguous caches ([B, Hkv, T, D]), in place. Returns the rotated q (``out``
+    if given; ``out=q`` rotates in place). CUDA tensors only, float32 / bfloat16 / float16.
+
+    Equal, bit for bit, to ``rope`` on every head as a one-row matrix at ``pos_offset + lens[b]`` followed by
+    ``kv_append`` (reference: python/fusedtok/__init__.py:645-702 and :1029-1112, three to four launches)."""
+    if not (_is_torch(k_cache) and k_cache.is_cuda):
+        raise TypeError("rope_kv_append takes CUDA tensors (there is no host path)")
+    if k_cache.ndim != 4:
+        raise ValueError("caches must be [B, Hkv, T, D]")
+    b, hkv, t_rows, d = k_cache.shape
+    q_out = _rope_append_checks(q, k_new, v_new, k_cache, v_cache, hkv, d, theta, pos_offset, out)
+    if q.shape[0] != b:
+        raise ValueError("q batch must match the cache batch")
+    if b == 0:
+        return q_out
+    lt = _lens_arg(lens, b, t_rows, q.device, upper_inclusive=False)
+    with _on_device(q.device):
+        _fusedtok.rope_kv_append_launch(_dtype_code(q), bool(neox), q.data_ptr(), q_out.data_ptr(),
+                                        k_new.data_ptr(), v_new.data_ptr(), lt.data_ptr(), k_cache.data_ptr(),
+                                        v_cache.data_ptr(), b, q.shape[1], hkv, d, t_rows, theta, pos_offset,
+                                        _cuda_stream())
+    return q_out
+
+
+def rope_kv_append_paged(q, k_pool, v_pool, block_table, k_new, v_new, lens, *, theta=10000.0, pos_offset=0,
+                         neox=False, out=None):
+    """``rope_kv_append`` for a paged cache: the rotated key and ``v_new`` land in pool block
+    ``block_table[b, lens[b] // P]`` at offset ``lens[b] % P`` (pools [Nb, Hkv, P, D]).
+    Composes ``rope`` and ``kv_append_paged`` (reference: python/fusedtok/__init__.py:645-702, :943-1026)."""
+    if not (_is_torch(k_pool) and k_pool.is_cuda):
+        raise TypeError("rope_kv_append_paged takes CUDA tensors (there is no host path)")
+    if k_pool.ndim != 4:
+        raise ValueError("pools must be [Nb, Hkv, P, D]")
+    nb, hkv, page, d = k_pool.shape
+    q_out = _rope_append_checks(q, k_new, v_new, k_pool, v_pool, hkv, d, theta, pos_offset, out)
+    b = q.shape[0]
+    if b == 0:
+        return q_out
+    bt = _table_arg(block_table, b, nb, q.device)
+    lt = _lens_arg(lens, b, bt.shape[1] * page, q.device, upper_inclusive=False)
+    with _on_device(q.device):
+        _fusedtok.rope_kv_append_paged_launch(_dtype_code(q), bool(neox), q.data_ptr(), q_out.data_ptr(),
+                                              k_new.data_ptr(), v_new.data_ptr(), bt.data_ptr(), lt.data_ptr(),
+                                              k_pool.data_ptr(), v_pool.data_ptr(), b, q.shape[1], hkv, d, page,
+                                              bt.shape[1], theta, pos_offset, _cuda_stream())
+    return q_out

@@ -48,6 +48,8 @@ _lib.fusedtok_rope_launch_bf16.argtypes = [_vp, _vp, _i, _i, ctypes.c_float, _i,
 _lib.fusedtok_rope_neox_launch_bf16.argtypes = [_vp, _vp, _i, _i, ctypes.c_float, _i, _sz]
 _lib.fusedtok_rope.argtypes = [_i, _vp, _vp, _vp, _vp, _i, _i, ctypes.c_float, _i]
 _lib.fusedtok_kv_append.argtypes = [_vp] * 5 + [_i] * 4
+_lib.fusedtok_rope_kv_append_launch.argtypes = [_i, _i] + [_vp] * 7 + [_i] * 5 + [ctypes.c_float, _i, _sz]
+_lib.fusedtok_rope_kv_append_paged_launch.argtypes = [_i, _i] + [_vp] * 8 + [_i] * 6 + [ctypes.c_float, _i, _sz]
 _lib.fusedtok_kv_append_paged.argtypes = [_vp] * 6 + [_i] * 6
 _lib.fusedtok_attention_decode.argtypes = [_vp] * 5 + [_i] * 5
 _lib.fusedtok_attention_decode_paged.argtypes = [_vp] * 6 + [_i] * 7
@@ -81,6 +83,7 @@ EXPORTS = (
     "fusedtok_kv_append_launch", "fusedtok_kv_append_launch_bf16", "fusedtok_kv_append_launch_fp16",
     "fusedtok_kv_append_paged_launch", "fusedtok_kv_append_paged_launch_bf16",
     "fusedtok_kv_append_paged_launch_fp16", "fusedtok_kv_append", "fusedtok_kv_append_paged",
+    "fusedtok_rope_kv_append_launch", "fusedtok_rope_kv_append_paged_launch",
     "fusedtok_attention_decode_partial_launch", "fusedtok_attention_partial_floats",
     "fusedtok_attention_merge_partials_launch",
     "fusedtok_exchange_alloc", "fusedtok_exchange_free", "fusedtok_exchange_export",
@@ -192,6 +195,24 @@ kv_append_launch_fp16 = _make_append("_fp16")
 kv_append_paged_launch = _make_append_paged("")
 kv_append_paged_launch_bf16 = _make_append_paged("_bf16")
 kv_append_paged_launch_fp16 = _make_append_paged("_fp16")
+
+
+def rope_kv_append_launch(dtype, neox, q, q_out, k_new, v_new, lens, k_cache, v_cache, batch, hq, hkv, dim,
+                          t_rows, theta, pos_offset, stream=0):
+    """RoPE of q and k_new at position lens[b] + pos_offset, rotated key and v_new written into the
+    contiguous cache, one launch. dtype: 0 float32, 1 bfloat16, 2 float16."""
+    _check(_lib.fusedtok_rope_kv_append_launch(dtype, 1 if neox else 0, int(q), int(q_out), int(k_new),
+                                               int(v_new), int(lens), int(k_cache), int(v_cache), batch, hq,
+                                               hkv, dim, t_rows, float(theta), pos_offset, int(stream)))
+
+
+def rope_kv_append_paged_launch(dtype, neox, q, q_out, k_new, v_new, table, lens, k_pool, v_pool, batch, hq,
+                                hkv, dim, page, tbl_width, theta, pos_offset, stream=0):
+    """The paged-cache form of rope_kv_append_launch."""
+    _check(_lib.fusedtok_rope_kv_append_paged_launch(dtype, 1 if neox else 0, int(q), int(q_out), int(k_new),
+                                                     int(v_new), int(table), int(lens), int(k_pool),
+                                                     int(v_pool), batch, hq, hkv, dim, page, tbl_width,
+                                                     float(theta), pos_offset, int(stream)))
 
 
 def _f32(a):

@@ -25,6 +25,7 @@
 #include "prefill_simt.cuh"
 #include "prefill_tc.cuh"
 #include "rope.cuh"
+#include "rope_append.cuh"
 #include "merge.cuh"
 
 namespace {
@@ -652,6 +653,43 @@ int rope_common(int dt, int neox, const void* x, void* y, int seq, int dim, floa
     return check_launch("rope kernel launch");
 }
 
+// The decode step's three elementwise launches in one (no reference counterpart as a single call; it composes
+// rope_launch* on one-row matrices, src/rope.cu:148-190, with kv_append[_paged]_launch*, src/attention.cu:1924-2005).
+int rope_append_common(int dt, int neox, const void* q, void* q_out, const void* k_new, const void* v_new,
+                       const int* table, const int* lens, void* k_dst, void* v_dst, int batch, int hq, int hkv,
+                       int dim, int rows, int tbl_width, float theta, int pos_offset, uintptr_t stream) {
+    if (dt < 0 || dt > 2) return fail(FUSEDTOK_INVALID_ARGUMENT, "dtype must be 0 (f32), 1 (bf16) or 2 (fp16)");
+    if (batch <= 0) return FUSEDTOK_OK;
+    if (dim < 4 || dim % 4 != 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "dim must be a multiple of 4");
+    if (hq < 1 || hkv < 1 || hq % hkv != 0)
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "q_heads must be a positive multiple of kv_heads");
+    if (table && rows < 1) return fail(FUSEDTOK_INVALID_ARGUMENT, "page size must be >= 1");
+    if (rows < 0 || tbl_width < 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "cache rows and table width must be >= 0");
+    if (pos_offset < 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "pos_offset must be >= 0");
+    if (!(theta > 0.0f)) return fail(FUSEDTOK_INVALID_ARGUMENT, "theta must be positive");
+    if (!lens) return fail(FUSEDTOK_INVALID_ARGUMENT, "lens is required (it is the write position)");
+    if (!q || !q_out || !k_new || !v_new || !k_dst || !v_dst)
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "null rope/append operand");
+    const size_t es = dtype_size(dt);
+    const uintptr_t all = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(q_out) |
+                          reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new) |
+                          reinterpret_cast<uintptr_t>(k_dst) | reinterpret_cast<uintptr_t>(v_dst);
+    if (all & (2 * es - 1)) return fail(FUSEDTOK_INVALID_ARGUMENT, "operands must be aligned to two elements");
+    RopeAppendParams p{};
+    p.q = q; p.q_out = q_out; p.k_new = k_new; p.v_new = v_new; p.k_dst = k_dst; p.v_dst = v_dst;
+    p.lens = lens; p.table = table;
+    p.B = batch; p.Hq = hq; p.Hkv = hkv; p.D = dim; p.rows = rows; p.tbl_width = tbl_width;
+    p.pos_offset = pos_offset; p.neox = neox ? 1 : 0;
+    p.log2_theta = std::log2((double)theta);
+    const long long work = (long long)(hq + 2 * hkv) * (dim / 4);
+    dim3 grid((unsigned)batch, (unsigned)((work + 255) / 256));
+    cudaStream_t cs = (cudaStream_t)stream;
+    if (dt == F32) rope_append_kernel<float><<<grid, 256, 0, cs>>>(p);
+    else if (dt == BF16) rope_append_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(p);
+    else rope_append_kernel<__half><<<grid, 256, 0, cs>>>(p);
+    return check_launch("rope + kv append kernel launch");
+}
+
 // RAII device buffer for the staged paths (reference: DevBuf, src/bindings.cpp:47-66)
 struct DevBuf {
     void* p = nullptr;
@@ -868,6 +906,22 @@ int fusedtok_rope(int neox, const float* q, const float* k, float* q_out, float*
         return cuda_fail("D2H copy failed", e);
     if ((e = cudaDeviceSynchronize()) != cudaSuccess) return cuda_fail("rope kernel failed", e);
     return FUSEDTOK_OK;
+}
+
+int fusedtok_rope_kv_append_launch(int dtype, int neox, const void* q, void* q_out, const void* k_new,
+                                   const void* v_new, const int* lens, void* k_cache, void* v_cache, int batch,
+                                   int q_heads, int kv_heads, int dim, int cache_rows, float theta, int pos_offset,
+                                   uintptr_t stream) {
+    return rope_append_common(dtype, neox, q, q_out, k_new, v_new, nullptr, lens, k_cache, v_cache, batch, q_heads,
+                              kv_heads, dim, cache_rows, 0, theta, pos_offset, stream);
+}
+int fusedtok_rope_kv_append_paged_launch(int dtype, int neox, const void* q, void* q_out, const void* k_new,
+                                         const void* v_new, const int* table, const int* lens, void* k_pool,
+                                         void* v_pool, int batch, int q_heads, int kv_heads, int dim, int page,
+                                         int tbl_width, float theta, int pos_offset, uintptr_t stream) {
+    if (!table) return fail(FUSEDTOK_INVALID_ARGUMENT, "block table is required");
+    return rope_append_common(dtype, neox, q, q_out, k_new, v_new, table, lens, k_pool, v_pool, batch, q_heads,
+                              kv_heads, dim, page, tbl_width, theta, pos_offset, stream);
 }
 
 int fusedtok_kv_append_launch(const float* k_new, const float* v_new, const int* lens, float* k_cache,

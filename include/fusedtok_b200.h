@@ -178,6 +178,30 @@ int fusedtok_kv_append_paged(const float* k_new, const float* v_new, const int* 
                              const int* lens, float* k_pool, float* v_pool, int batch,
                              int kv_heads, int dim, int page, int tbl_width, int num_blocks);
 
+/* ---- rotary embedding + kv-cache append in ONE launch (decode step) ---------
+ * The elementwise work that precedes a decode-attention call, fused: q
+ * [B, Hq, D] is rotated to position lens[b] + pos_offset into q_out (which may
+ * be q), k_new [B, Hkv, D] is rotated to the same position and written
+ * straight into the cache at position lens[b], v_new is copied beside it.
+ * dtype: 0 float32, 1 bfloat16, 2 float16 (all operands); dim a multiple of 4.
+ * No single counterpart in the reference: it composes fusedtok::rope_launch* /
+ * rope_neox_launch* on one-row matrices (src/rope.cu:148-190) with
+ * kv_append_launch* / kv_append_paged_launch* (src/attention.cu:1924-2035),
+ * and its results are bit-identical to fusedtok_rope_launch* followed by
+ * fusedtok_kv_append*_launch*. Asynchronous on `stream`, capturable, no
+ * workspace; a position outside the cache skips the K/V write. */
+int fusedtok_rope_kv_append_launch(int dtype, int neox, const void* q, void* q_out,
+                                   const void* k_new, const void* v_new, const int* lens,
+                                   void* k_cache, void* v_cache, int batch, int q_heads,
+                                   int kv_heads, int dim, int cache_rows, float theta,
+                                   int pos_offset, uintptr_t stream);
+int fusedtok_rope_kv_append_paged_launch(int dtype, int neox, const void* q, void* q_out,
+                                         const void* k_new, const void* v_new, const int* table,
+                                         const int* lens, void* k_pool, void* v_pool, int batch,
+                                         int q_heads, int kv_heads, int dim, int page,
+                                         int tbl_width, float theta, int pos_offset,
+                                         uintptr_t stream);
+
 /* ---- KV-length split across GPUs (no counterpart in the reference, which is
  * single-GPU; the exchanged triple and the merge rule are the reference's
  * intra-GPU ones, src/attention.cu:434-463 and :503-548) --------------------
