@@ -14,8 +14,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfusedtok_b200.so")
 SOURCES = ["fusedtok_b200.cu"]
-HEADERS = ["common.cuh", "decode_tc.cuh", "decode_simt.cuh", "merge.cuh", "kv_append.cuh",
-           os.path.join("..", "..", "include", "fusedtok_b200.h")]
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith(".cuh")) + [
+    os.path.join("..", "..", "include", "fusedtok_b200.h")]
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
