@@ -69,9 +69,7 @@ template <int D> struct TcCfg {
     static constexpr int SCRATCH_BYTES = NCW * 8 * ACC_STRIDE * 4;
     static constexpr int OFF_SCRATCH = NS * STAGE_BYTES;
     static constexpr int OFF_ML = OFF_SCRATCH + SCRATCH_BYTES;       // [NCW][8] float2
-    static constexpr int OFF_SCALE = OFF_ML + NCW * 8 * 8;           // [NCW][8] float
-    static constexpr int OFF_GLOB = OFF_SCALE + NCW * 8 * 4;         // [8] float2 (m, l) merged
-    static constexpr int OFF_BAR = OFF_GLOB + 8 * 8;                 // full[NS], empty[NS]
+    static constexpr int OFF_BAR = OFF_ML + NCW * 8 * 8;             // full[NS], empty[NS]
     static constexpr int OFF_SCHED = OFF_BAR + 2 * NS * 8;
     static constexpr int OFF_ABORT = OFF_SCHED + (int)sizeof(SchedShared);
     static constexpr int SMEM_BYTES = OFF_ABORT + 16;
@@ -362,8 +360,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 
     float* s_acc = reinterpret_cast<float*>(smem + Cfg::OFF_SCRATCH);
     float2* s_ml = reinterpret_cast<float2*>(smem + Cfg::OFF_ML);
-    float* s_scale = reinterpret_cast<float*>(smem + Cfg::OFF_SCALE);
-    float2* s_glob = reinterpret_cast<float2*>(smem + Cfg::OFF_GLOB);
     volatile int* s_last = abort_flag + 1;
 
     constexpr int KSTEPS = D / 16;      // k-steps of S^T = K Q^T
@@ -579,36 +575,31 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     if (quad == 0) s_ml[warp * 8 + qi * 2 + e] = make_float2(m_run[hh][e], l_run[hh][e]);
                 }
                 bar_consumers();
-                if (tc < NCW * 8) {
-                    const int row = tc & 7;
-                    float mg = -INFINITY;
-#pragma unroll
-                    for (int ww = 0; ww < NCW; ++ww) mg = fmaxf(mg, s_ml[ww * 8 + row].x);
-                    const float mg_safe = (mg == -INFINITY) ? 0.0f : mg;
-                    s_scale[tc] = ex2((s_ml[tc].x - mg_safe) * sl2);   // tc = (warp index) * 8 + row
-                    if (tc < 8) {
-                        float lg = 0.0f;
-#pragma unroll
-                        for (int ww = 0; ww < NCW; ++ww)
-                            lg += s_ml[ww * 8 + row].y * ex2((s_ml[ww * 8 + row].x - mg_safe) * sl2);
-                        s_glob[row] = make_float2(mg * p.scale, lg);   // m from raw score units to natural-log units
-                    }
-                }
-                bar_consumers();
                 for (int e = tc; e < 8 * (D / 2); e += NCW * 32) {
                     const int row = e / (D / 2), d = (e % (D / 2)) * 2;
                     const int g = hh * 8 + row;
                     if (g >= dst.gvalid) continue;
-                    float a0 = 0.0f, a1 = 0.0f;
+                    // every thread derives the merged maximum and the warps' scale factors of its row itself
+                    // (8 values from shared memory, 8 ex2): cheaper than a third barrier per fold
+                    float mw[NCW];
+                    float mg = -INFINITY;
 #pragma unroll
                     for (int ww = 0; ww < NCW; ++ww) {
-                        const float sc = s_scale[ww * 8 + row];
+                        mw[ww] = s_ml[ww * 8 + row].x;
+                        mg = fmaxf(mg, mw[ww]);
+                    }
+                    const float mg_safe = (mg == -INFINITY) ? 0.0f : mg;
+                    float a0 = 0.0f, a1 = 0.0f, lg = 0.0f;
+#pragma unroll
+                    for (int ww = 0; ww < NCW; ++ww) {
+                        const float sc = ex2((mw[ww] - mg_safe) * sl2);
                         const float2 v = *reinterpret_cast<const float2*>(
                             s_acc + ((size_t)ww * 8 + row) * Cfg::ACC_STRIDE + d);
                         a0 += v.x * sc;
                         a1 += v.y * sc;
+                        lg += s_ml[ww * 8 + row].y * sc;
                     }
-                    const float2 ml = s_glob[row];
+                    const float2 ml = make_float2(mg * p.scale, lg);   // m from raw score units to natural-log units
                     if (dst.whole) {
                         emit_final2<T>(p, dst.b, dst.h0 + g, d, ml.x, ml.y, a0, a1, d == 0);
                     } else {
