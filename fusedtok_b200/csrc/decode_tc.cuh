@@ -239,10 +239,18 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     // written, which must wait for that kernel to have completed. Letting our
     // own dependents start early is always safe: they wait the same way.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
     Walker w;
-    if (!sched_init<T>(p, sh, w)) return;      // block-uniform
+    bool have_work;                             // block-uniform
+    if (!p.lens) {
+        // every sequence has p.T rows: the schedule is arithmetic on kernel parameters and
+        // belongs to the part that may overlap the previous kernel
+        have_work = sched_init<T>(p, sh, w);
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        have_work = sched_init<T>(p, sh, w);    // reads lens
+    }
+    if (!have_work) return;
     const long long total = sh->total;
     const int upb_nch = p.NCH;
 
