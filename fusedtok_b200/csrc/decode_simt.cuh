@@ -127,8 +127,20 @@ decode_simt_kernel(const DecodeParams p) {
     __shared__ float2 s_glob[GC];
     __shared__ int s_last;
 
+    // Launched with programmatic stream serialization: up to here (and, when every sequence has p.T
+    // rows, through the arithmetic of the tile schedule) the kernel may overlap the tail of the
+    // previous kernel in the stream; global memory is touched only after griddepcontrol.wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     Walker w;
-    if (!sched_init<T>(p, &sh, w)) return;
+    bool have_work;                             // block-uniform
+    if (!p.lens) {
+        have_work = sched_init<T>(p, &sh, w);
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        have_work = sched_init<T>(p, &sh, w);   // reads lens
+    }
+    if (!have_work) return;
     const long long total = sh.total;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int D = p.D;

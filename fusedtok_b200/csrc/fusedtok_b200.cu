@@ -326,7 +326,18 @@ void launch_tc_t(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParam
 }
 
 template <typename T> void launch_simt_t(const DecodeParams& p, int lc, cudaStream_t cs) {
-#define FTK_GO(GC, LC) decode_simt_kernel<T, GC, LC><<<p.ncta, SIMT_THREADS, SIMT_STAGE_BYTES, cs>>>(p)
+    // programmatic stream serialization, as for the tensor-core kernel
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p.ncta);
+    cfg.blockDim = dim3(SIMT_THREADS);
+    cfg.dynamicSmemBytes = SIMT_STAGE_BYTES;
+    cfg.stream = cs;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+#define FTK_GO(GC, LC) cudaLaunchKernelEx(&cfg, decode_simt_kernel<T, GC, LC>, p)
     if (lc == 1) { if (p.GC == 1) FTK_GO(1, 1); else if (p.GC == 4) FTK_GO(4, 1); else FTK_GO(8, 1); }
     else if (lc == 2) { if (p.GC == 1) FTK_GO(1, 2); else FTK_GO(4, 2); }
     else { if (p.GC == 1) FTK_GO(1, 4); else FTK_GO(2, 4); }
