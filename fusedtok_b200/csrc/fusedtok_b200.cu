@@ -488,6 +488,23 @@ int decode_paged(int dt, const void* q, const void* kp, const void* vp, const in
                          dim, stream);
 }
 
+// Launch configuration with programmatic stream serialization allowed (the kernel starts with
+// griddepcontrol.wait, so it touches memory only after the kernel before it has completed).
+struct PdlLaunch {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    PdlLaunch(dim3 grid, dim3 block, size_t smem, cudaStream_t cs) : cfg{} {
+        cfg.gridDim = grid;
+        cfg.blockDim = block;
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = cs;
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+};
+
 // reference: kv_append_launch_t / kv_append_paged_launch_t, src/attention.cu:1924-1941, 1989-2005
 int kv_append_common(int dt, const void* k_new, const void* v_new, const int* table, const int* lens,
                      void* k_dst, void* v_dst, int batch, int hkv, int dim, int rows, int tbl_width,
@@ -514,8 +531,9 @@ int kv_append_common(int dt, const void* k_new, const void* v_new, const int* ta
     const int chunks = hkv * (p.row_bytes / vec);
     dim3 grid((unsigned)batch, (unsigned)((chunks + 255) / 256));
     cudaStream_t cs = (cudaStream_t)stream;
-    if (wide) kv_append_kernel<uint4><<<grid, 256, 0, cs>>>(p);
-    else kv_append_kernel<uint2><<<grid, 256, 0, cs>>>(p);
+    PdlLaunch l(grid, dim3(256), 0, cs);
+    if (wide) cudaLaunchKernelEx(&l.cfg, kv_append_kernel<uint4>, p);
+    else cudaLaunchKernelEx(&l.cfg, kv_append_kernel<uint2>, p);
     return check_launch("kv append kernel launch");
 }
 
@@ -695,9 +713,10 @@ int rope_append_common(int dt, int neox, const void* q, void* q_out, const void*
     const long long work = (long long)(hq + 2 * hkv) * (dim / 4);
     dim3 grid((unsigned)batch, (unsigned)((work + 255) / 256));
     cudaStream_t cs = (cudaStream_t)stream;
-    if (dt == F32) rope_append_kernel<float><<<grid, 256, 0, cs>>>(p);
-    else if (dt == BF16) rope_append_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(p);
-    else rope_append_kernel<__half><<<grid, 256, 0, cs>>>(p);
+    PdlLaunch l(grid, dim3(256), 0, cs);
+    if (dt == F32) cudaLaunchKernelEx(&l.cfg, rope_append_kernel<float>, p);
+    else if (dt == BF16) cudaLaunchKernelEx(&l.cfg, rope_append_kernel<__nv_bfloat16>, p);
+    else cudaLaunchKernelEx(&l.cfg, rope_append_kernel<__half>, p);
     return check_launch("rope + kv append kernel launch");
 }
 

@@ -31,6 +31,10 @@ struct AppendParams {
 
 template <typename V>
 __global__ void __launch_bounds__(256) kv_append_kernel(const AppendParams p) {
+    // launched with programmatic stream serialization: the launch overlaps the previous kernel's
+    // tail and the decode kernel that follows may set itself up while this one runs
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int b = blockIdx.x;
     const int chunks_per_row = p.row_bytes / (int)sizeof(V);
     const int idx = blockIdx.y * blockDim.x + threadIdx.x;

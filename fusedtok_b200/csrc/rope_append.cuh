@@ -49,6 +49,10 @@ struct RopeAppendParams {
 
 template <typename T>
 __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams p) {
+    // launched with programmatic stream serialization: the launch overlaps the previous kernel's
+    // tail and the decode kernel that follows may set itself up while this one runs
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int b = blockIdx.x;
     const int half = p.D >> 1;
     const int per_row = half >> 1;                       // threads per row: two pairs each (D % 4 == 0)
