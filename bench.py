@@ -511,6 +511,40 @@ def run_ours(args, w, rank, world, local_rank):
             del hq_, hk_, hv_
         except Exception as exc:   # informational only
             line["e2e_staged"] = {"error": str(exc)[:200]}
+    if world == 1 and not w["paged"]:
+        # the whole decode step on the device: rope of q / k_new at position T-1 + cache write (one launch) followed
+        # by the attention kernel, direct launches chained by programmatic stream serialization (informational)
+        try:
+            g2 = torch.Generator(device=device).manual_seed(7)
+            k_new = torch.randn(batch, w["Hkv"], w["D"], device=device, generator=g2).to(q.dtype)
+            v_new = torch.randn(batch, w["Hkv"], w["D"], device=device, generator=g2).to(q.dtype)
+            q_rot = torch.empty_like(q)
+            pos = torch.full((batch,), wl["T"] - 1, dtype=torch.int32, device=device)
+
+            def full_step(i):
+                k, v = sets[i % n_sets]
+                _fusedtok.rope_kv_append_launch(dt_code, True, q.data_ptr(), q_rot.data_ptr(), k_new.data_ptr(),
+                                                v_new.data_ptr(), pos.data_ptr(), k.data_ptr(), v.data_ptr(), batch,
+                                                w["Hq"], w["Hkv"], w["D"], wl["T"], 10000.0, 0, stream.cuda_stream)
+                getattr(_fusedtok, "attention_decode_launch" + sfx)(
+                    q_rot.data_ptr(), k.data_ptr(), v.data_ptr(), lens_ptr, out.data_ptr(),
+                    batch, w["Hq"], w["Hkv"], wl["T"], w["D"], stream.cuda_stream)
+
+            for i in range(5):
+                full_step(i)
+            torch.cuda.synchronize()
+            e0.record()
+            for i in range(args.steps):
+                full_step(i)
+            e1.record()
+            torch.cuda.synchronize()
+            fs_ms = e0.elapsed_time(e1) / args.steps
+            line["decode_step"] = {"ms_per_step": fs_ms, "attention_only_ms_per_step": ms_step,
+                                   "launches_per_step": 2,
+                                   "note": "rope_kv_append (rope of q and k_new + cache write, one launch) + "
+                                           "attention_decode, back to back on one stream"}
+        except Exception as exc:   # informational only
+            line["decode_step"] = {"error": str(exc)[:200]}
     if world == 1:
         # the reference's own GPU kernels on the same inputs (informational)
         try:

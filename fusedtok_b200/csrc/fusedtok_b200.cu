@@ -664,6 +664,7 @@ int rope_common(int dt, int neox, const void* x, void* y, int seq, int dim, floa
     RopeParams p{};
     p.x = x; p.y = y; p.seq = seq; p.dim = dim; p.pos_offset = pos_offset; p.neox = neox ? 1 : 0;
     p.log2_theta = std::log2((double)theta);
+    p.ratio = std::exp2(-2.0 / dim * p.log2_theta);
     const size_t es = dtype_size(dt);
     const uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y);
     // two pairs per thread need every access (2 elements, rows and halves included) aligned to 2 elements
@@ -710,6 +711,7 @@ int rope_append_common(int dt, int neox, const void* q, void* q_out, const void*
     p.B = batch; p.Hq = hq; p.Hkv = hkv; p.D = dim; p.rows = rows; p.tbl_width = tbl_width;
     p.pos_offset = pos_offset; p.neox = neox ? 1 : 0;
     p.log2_theta = std::log2((double)theta);
+    p.ratio = std::exp2(-2.0 / dim * p.log2_theta);
     const long long work = (long long)(hq + 2 * hkv) * (dim / 4);
     dim3 grid((unsigned)batch, (unsigned)((work + 255) / 256));
     cudaStream_t cs = (cudaStream_t)stream;

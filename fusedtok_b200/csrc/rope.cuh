@@ -1,7 +1,7 @@
 // Rotary position embedding on one [seq, dim] matrix (reference: rope_kernel / rope_neox_kernel,
 // src/rope.cu:39-92): row r has absolute position m = r + pos_offset, pair j is rotated by the angle
 // m * theta^(-2j/dim); interleaved pairs (2j, 2j+1) or NeoX pairs (j, j + dim/2). The rotation itself is
-// float32; the angle and its sine/cosine are computed in double (see rope_cs), which keeps the result within
+// float32; the angle is formed and reduced to [-pi, pi] in double (see rope_cs_from_freq), which keeps the result within
 // 1e-4 of the reference's CPU statement (src/rope.cu:95-146) at any position. HBM-bound: 2 * seq * dim *
 // sizeof bytes per call.
 //
@@ -22,6 +22,7 @@ struct RopeParams {
     int pos_offset;
     int neox;
     double log2_theta;
+    double ratio;          // theta^(-2/dim): frequency of pair j + 1 over that of pair j
 };
 
 template <typename T> __device__ __forceinline__ float rope_ld(const T* p) { return (float)*p; }
@@ -47,15 +48,27 @@ template <> __device__ __forceinline__ void rope_st2<__nv_bfloat16>(__nv_bfloat1
     *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
 
-// The angle is formed and reduced in double: at position m the float32 product m * freq is only good to
-// m * 2^-24 radians (1e-3 at m = 4096, 1e-2 at m = 100000), which the reference's double-precision CPU
-// statement does not suffer; the kernel is HBM-bound with room for the extra arithmetic.
+// The angle is formed in double: at position m the float32 product m * freq is only good to m * 2^-24 radians
+// (1e-3 at m = 4096, 1e-2 at m = 100000), which the reference's double-precision CPU statement does not suffer.
+// Only the product and its reduction to [-pi, pi] need double (two fused multiply-adds against a two-term 2*pi);
+// the sine and cosine of the reduced angle are float32 (2 ulp), which keeps the result within 1e-6 of the double
+// statement at any position and the kernel's latency short (no double-precision sincos).
+__device__ __forceinline__ void rope_cs_from_freq(double freq, int m, float& c, float& s) {
+    const double a = (double)m * freq;
+    const double k = rint(a * 0.15915494309189535);          // a / (2 pi)
+    double r = fma(-k, 6.283185307179586, a);                 // a - k * 2 pi, high part
+    r = fma(-k, 2.4492935982947064e-16, r);                   // ... low part
+    sincosf((float)r, &s, &c);
+}
 __device__ __forceinline__ void rope_cs(int j, int dim, int m, double log2_theta, float& c, float& s) {
-    const double freq = exp2(-(2.0 * j / dim) * log2_theta);
-    double sd, cd;
-    sincos((double)m * freq, &sd, &cd);
-    s = (float)sd;
-    c = (float)cd;
+    rope_cs_from_freq(exp2(-(2.0 * j / dim) * log2_theta), m, c, s);
+}
+// Pairs j and j + 1: the second frequency is the first times theta^(-2/dim) (`ratio`, from the host).
+__device__ __forceinline__ void rope_cs2(int j, int dim, int m, double log2_theta, double ratio, float& c0, float& s0,
+                                         float& c1, float& s1) {
+    const double f0 = exp2(-(2.0 * j / dim) * log2_theta);
+    rope_cs_from_freq(f0, m, c0, s0);
+    rope_cs_from_freq(f0 * ratio, m, c1, s1);
 }
 
 // VEC: two pairs per thread (dim % 4 == 0 and 8-byte aligned rows), else one pair per thread.
@@ -75,8 +88,7 @@ __global__ void __launch_bounds__(256) rope_kernel(const RopeParams p) {
         if (VEC) {
             const int j = 2 * u;
             float c0, s0, c1, s1;
-            rope_cs(j, p.dim, m, p.log2_theta, c0, s0);
-            rope_cs(j + 1, p.dim, m, p.log2_theta, c1, s1);
+            rope_cs2(j, p.dim, m, p.log2_theta, p.ratio, c0, s0, c1, s1);
             if (p.neox) {
                 const float2 a = rope_ld2<T>(x + base + j), b = rope_ld2<T>(x + base + half + j);
                 rope_st2<T>(y + base + j, a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);

@@ -45,6 +45,7 @@ struct RopeAppendParams {
     int pos_offset;
     int neox;
     double log2_theta;
+    double ratio;         // theta^(-2/D)
 };
 
 template <typename T>
@@ -98,8 +99,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
     }
     const int m = pos + p.pos_offset;
     float c0, s0, c1, s1;
-    rope_cs(j, p.D, m, p.log2_theta, c0, s0);
-    rope_cs(j + 1, p.D, m, p.log2_theta, c1, s1);
+    rope_cs2(j, p.D, m, p.log2_theta, p.ratio, c0, s0, c1, s1);
     const float2 a = rope_ld2<T>(src + e0), bb = rope_ld2<T>(src + e1);
     if (p.neox) {
         rope_st2<T>(dst + e0, a.x * c0 - bb.x * s0, a.y * c1 - bb.y * s1);
