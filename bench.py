@@ -22,6 +22,8 @@ e2e            : the same metric through the public Python operator with the
 roofline       : HBM bound; achieved = algorithmic bytes / step time (partial
                  kernel incl. its in-kernel merge, plus the launch gap between
                  steps); peak = measured copy bandwidth.
+decode_step    : (N=1, contiguous) the whole step on the device: rope of q and k_new +
+                 cache write (one launch) followed by the attention kernel.
 cpu_baseline   : the reference's own CPU implementation (built from the
                  reference sources) or, where that build is absent, the C
                  restatement, on the host cores, on a bounded sample.
