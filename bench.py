@@ -12,7 +12,14 @@ K and V ~ 0.5 * N(0,1)). Prints ONE JSON line.
 metric / value : algorithmic KV-read bandwidth, GB/s, whole job, inputs
                  resident in HBM: bytes = sum_b len_b*Hkv*D*2*sizeof + 2*B*Hq*D*sizeof
                  per step, divided by the CUDA-event time of the timed steps
-                 (max over ranks).
+                 (max over ranks). The region of `--steps` back-to-back steps is
+                 timed `--rounds` times (default 5); `value` is the median round
+                 and `rounds_ms_per_step` lists them all.
+kv_split,
+c2_strong      : (N > 1, default workload) two more measurements in the same
+                 line: configuration 4 with the KV length split over the N GPUs
+                 (the one path with an exchange between GPUs) and configuration
+                 2 with its batch of 32 divided over the N GPUs.
 e2e            : the same metric through the public Python operator with the
                  step's inputs (q, lens) copied from pinned host memory and the
                  result copied back and read, every step. The KV cache is decode
@@ -49,8 +56,8 @@ L2_BYTES = 126 * 1024 * 1024
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the split-KV
-# partial kernel on the default workload, from the ncu capture summarised in
-# profiles/decode_tc_bf16_d128_config2.md (537.23 MB read + 4.13 MB written).
+# kernel on the default workload, from an ncu capture of this kernel (not
+# re-measured by this script: a profiler cannot run inside a timed benchmark).
 NCU_TRAFFIC_BYTES = {"c2": 541363712}
 
 WORKLOADS = {
@@ -275,6 +282,195 @@ def run_reference_arm(args, w, rank):
 # our arm
 # ---------------------------------------------------------------------------
 
+def multi_gpu_extras(args, torch, dist, device, rank, world, c2_weak_ms_step, barrier):
+    """Two more measurements for the N > 1 line (every rank calls this; the returned dict matters on rank 0):
+
+    kv_split  - configuration 4 (batch 4, 64/8 heads, 131072 rows, bf16) with the KV length split over the
+                `world` GPUs: per step every rank streams its 1/N of the rows, the ranks exchange the raw
+                (m, l, acc) triples over NVLink and every rank folds them. Beside it, measured in the same
+                process: one rank's 1/N share WITHOUT the exchange (what the split can at best reach) and
+                the whole configuration on ONE GPU (what it is a speed-up over).
+    c2_strong - configuration 2 with its batch of 32 divided over the GPUs (no communication); the
+                single-GPU time it is compared with is this run's own headline (same per-GPU work)."""
+    from fusedtok_b200 import _fusedtok
+    steps, rounds = args.steps, max(3, min(args.rounds, 5))
+    out = {}
+
+    def measure(case):
+        for i in range(5):
+            case.step(i)
+        torch.cuda.synchronize()
+        r = timed_rounds(torch, case.step, steps, rounds, barrier)
+        r = max_over_ranks(torch, dist, device, r)
+        return statistics.median(r) / steps, [x / steps for x in r]
+
+    # ---- configuration 4, KV length split
+    w4 = dict(WORKLOADS["c4"])
+    if w4["T"] % world == 0:
+        split = Case(w4, w4["B"], device, seed=100 + rank, mode="split", world=world, group=dist.group.WORLD,
+                     exchange=args.exchange, dist=dist)
+        ms_split, split_rounds = measure(split)
+        status = _fusedtok.attention_device_status()
+        st = torch.tensor([float(status)], device=device, dtype=torch.float64)
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        # the same per-rank rows through the ordinary operator: no exchange, no merge across GPUs
+        local = Case(split.wl, w4["B"], device, seed=100 + rank)
+        local.sets, local.n_sets = split.sets, split.n_sets          # same tensors
+        ms_local, _ = measure(local)
+        bytes_total = algorithmic_bytes(w4, None, w4["B"])
+        split.close()
+        del split, local
+        torch.cuda.empty_cache()
+        # the whole configuration on one GPU, timed on rank 0 while the others wait at the barrier
+        ms_full = 0.0
+        if rank == 0:
+            full = Case(w4, w4["B"], device, seed=100)
+            for i in range(5):
+                full.step(i)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            vals = []
+            for _ in range(3):
+                e0.record()
+                for i in range(steps):
+                    full.step(i)
+                e1.record()
+                torch.cuda.synchronize()
+                vals.append(e0.elapsed_time(e1) / steps)
+            ms_full = statistics.median(vals)
+            full.close()
+            del full
+            torch.cuda.empty_cache()
+        barrier()
+        out["kv_split"] = {
+            "workload": "c4: " + w4["desc"], "n_gpus": world, "exchange": args.exchange,
+            "launches_per_step_per_gpu": 1 if args.exchange == "p2p" else 3,
+            "ms_per_step": ms_split, "rounds_ms_per_step": split_rounds,
+            "GBps": bytes_total / (ms_split * 1e-3) / 1e9, "seq_steps_per_s": w4["B"] / (ms_split * 1e-3),
+            "single_gpu_ms_per_step": ms_full,
+            "speedup_vs_single_gpu": (ms_full / ms_split) if ms_full else None,
+            "local_share_ms_per_step": ms_local,
+            "speedup_bound_from_local_share": (ms_full / ms_local) if ms_full else None,
+            "exchange_and_sync_ms_per_step": ms_split - ms_local,
+            "device_status": int(st.item()),
+            "note": "KV length 131072 split over the GPUs; (m, l, acc) of every finished unit stored into every "
+                    "rank's buffer over NVLink and folded at the end of the same kernel; times are the max over "
+                    "ranks per round, median round; single_gpu = the whole configuration on rank 0's GPU",
+        }
+    # ---- configuration 2, batch divided over the GPUs
+    w2 = dict(WORKLOADS["c2"])
+    if w2["B"] % world == 0:
+        strong = Case(w2, w2["B"] // world, device, seed=200 + rank)
+        ms_strong, strong_rounds = measure(strong)
+        bytes_total = algorithmic_bytes(w2, None, w2["B"])
+        n_sets = strong.n_sets
+        strong.close()
+        del strong
+        torch.cuda.empty_cache()
+        out["c2_strong"] = {
+            "workload": "c2: " + w2["desc"], "n_gpus": world, "batch_per_gpu": w2["B"] // world,
+            "ms_per_step": ms_strong, "rounds_ms_per_step": strong_rounds,
+            "GBps": bytes_total / (ms_strong * 1e-3) / 1e9, "seq_steps_per_s": w2["B"] / (ms_strong * 1e-3),
+            "single_gpu_ms_per_step": c2_weak_ms_step,
+            "speedup_vs_single_gpu": c2_weak_ms_step / ms_strong,
+            "l2": "rotating over %d independent K/V sets so reads come from HBM" % n_sets,
+            "note": "batch 32 divided over the GPUs, no communication; single_gpu = this line's own ms_per_step "
+                    "(batch 32 on every GPU)",
+        }
+    return out
+
+
+class Case:
+    """One workload as one rank runs it: inputs resident on the device, one `step(i)` call per decode step.
+
+    mode "plain": the ordinary operator on this rank's batch; "split": configuration-4 style KV-length split
+    (this rank holds rows/world of every sequence, partials exchanged between the GPUs)."""
+
+    def __init__(self, w, batch, device, seed, mode="plain", world=1, group=None, exchange="p2p", dist=None):
+        import torch
+        from fusedtok_b200 import _fusedtok
+        self.w = w
+        self.batch = batch
+        self.mode = mode
+        self.wl = dict(w)
+        if mode == "split":
+            assert w["T"] % world == 0
+            self.wl["T"] = w["T"] // world            # this rank's slice of the cache rows
+        es = 4 if w["dtype"] == "f32" else 2
+        self.kv_bytes = 2 * batch * w["Hkv"] * self.wl["T"] * w["D"] * es
+        self.n_sets = 1 if self.kv_bytes >= 3 * L2_BYTES else int(math.ceil(3 * L2_BYTES / self.kv_bytes))
+        self.q, self.sets, self.lens_t, self.table, self.lens_np = build_inputs(self.wl, batch, device, seed,
+                                                                                self.n_sets)
+        self.bytes_step = algorithmic_bytes(self.wl, self.lens_np, batch)
+        self.out = torch.empty_like(self.q)
+        self.sfx = {"f32": "", "bf16": "_bf16", "fp16": "_fp16"}[w["dtype"]]
+        self.lens_ptr = self.lens_t.data_ptr() if self.lens_t is not None else 0
+        self.dec = None
+        self.exchange = exchange
+        if mode == "split":
+            from fusedtok_b200 import sharded
+            cls = sharded.PeerSplitKVDecoder if exchange == "p2p" else sharded.SplitKVDecoder
+            self.dec = cls(batch, w["Hq"], w["Hkv"], w["D"], self.q.dtype, device, group)
+        self._ft = _fusedtok
+        self._torch = torch
+
+    def step(self, i):
+        w, wl = self.w, self.wl
+        k, v = self.sets[i % self.n_sets]
+        stream = self._torch.cuda.current_stream()      # the capture stream while a graph is being recorded
+        if self.dec is not None:
+            self.dec.decode(self.q, k, v, None, self.out)
+        elif w["paged"]:
+            getattr(self._ft, "attention_decode_paged_launch" + self.sfx)(
+                self.q.data_ptr(), k.data_ptr(), v.data_ptr(), self.table.data_ptr(), self.lens_ptr,
+                self.out.data_ptr(), self.batch, w["Hq"], w["Hkv"], 16, self.table.shape[1], w["D"],
+                stream.cuda_stream)
+        else:
+            getattr(self._ft, "attention_decode_launch" + self.sfx)(
+                self.q.data_ptr(), k.data_ptr(), v.data_ptr(), self.lens_ptr, self.out.data_ptr(),
+                self.batch, w["Hq"], w["Hkv"], wl["T"], w["D"], stream.cuda_stream)
+
+    def launches_per_step(self):
+        if self.dec is None or self.exchange == "p2p":
+            return 1
+        return 3            # partial kernel, NCCL all-gather, merge kernel
+
+    def close(self):
+        if self.dec is not None and hasattr(self.dec, "close"):
+            self._torch.cuda.synchronize()
+            self.dec.close()
+        self.sets = None
+
+
+def timed_rounds(torch, run, steps, rounds, barrier):
+    """`rounds` regions of exactly `steps` back-to-back calls of run(i), each bracketed by a barrier and a
+    device synchronize on both sides and timed with CUDA events on the launching stream. Returns the
+    per-round times in ms."""
+    out = []
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    n = 0
+    for _ in range(rounds):
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            run(n)
+            n += 1
+        e1.record()
+        barrier()
+        out.append(e0.elapsed_time(e1))
+    return out
+
+
+def max_over_ranks(torch, dist, device, values):
+    """Element-wise maximum of a list of floats over the ranks (identity on one GPU)."""
+    if dist is None:
+        return list(values)
+    t = torch.tensor(list(values), device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(x) for x in t]
+
+
 def run_ours(args, w, rank, world, local_rank):
     import numpy as np
     import torch
@@ -287,7 +483,9 @@ def run_ours(args, w, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
-        os.environ["NCCL_DEBUG"] = "WARN"        # keep NCCL's version banner off stdout (one JSON line only)
+        # NCCL_DEBUG is left as the caller set it; whatever NCCL logs goes to a file so that stdout stays one JSON line
+        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+        os.environ.setdefault("NCCL_DEBUG_FILE", os.path.join(ROOT, "gpurun_out", "nccl_debug.%h.%p.log"))
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", device_id=device)
@@ -299,41 +497,14 @@ def run_ours(args, w, rank, world, local_rank):
     else:
         assert w["B"] % world == 0, "strong scaling shards the batch evenly"
         batch = w["B"] // world
-    wl = dict(w)
-    if split_kv:
-        assert w["T"] % world == 0
-        wl["T"] = w["T"] // world            # this rank's slice of the cache rows
-    es = 4 if w["dtype"] == "f32" else 2
-    kv_bytes = 2 * batch * w["Hkv"] * wl["T"] * w["D"] * es
-    n_sets = 1 if kv_bytes >= 3 * L2_BYTES else int(math.ceil(3 * L2_BYTES / kv_bytes))
-    q, sets, lens_t, table, lens_np = build_inputs(wl, batch, device, seed=rank, n_sets=n_sets)
-    bytes_step = algorithmic_bytes(wl, lens_np, batch)
+    case = Case(w, batch, device, seed=rank, mode="split" if split_kv else "plain", world=world,
+                group=dist.group.WORLD if dist else None, exchange=args.exchange, dist=dist)
+    wl, n_sets, bytes_step, kv_bytes = case.wl, case.n_sets, case.bytes_step, case.kv_bytes
+    q, sets, lens_t, table, out = case.q, case.sets, case.lens_t, case.table, case.out
+    sfx, lens_ptr, dec = case.sfx, case.lens_ptr, case.dec
     stream = torch.cuda.current_stream()
-    out = torch.empty_like(q)
     dt_code = {"f32": 0, "bf16": 1, "fp16": 2}[w["dtype"]]
-    sfx = {"f32": "", "bf16": "_bf16", "fp16": "_fp16"}[w["dtype"]]
-    lens_ptr = lens_t.data_ptr() if lens_t is not None else 0
-
-    if split_kv:
-        from fusedtok_b200 import sharded
-        if args.exchange == "p2p":
-            dec = sharded.PeerSplitKVDecoder(batch, w["Hq"], w["Hkv"], w["D"], q.dtype, device, dist.group.WORLD)
-        else:
-            dec = sharded.SplitKVDecoder(batch, w["Hq"], w["Hkv"], w["D"], q.dtype, device, dist.group.WORLD)
-
-    def step(i):
-        k, v = sets[i % n_sets]
-        stream = torch.cuda.current_stream()        # the capture stream while a graph is being recorded
-        if split_kv:
-            dec.decode(q, k, v, None, out)
-        elif w["paged"]:
-            getattr(_fusedtok, "attention_decode_paged_launch" + sfx)(
-                q.data_ptr(), k.data_ptr(), v.data_ptr(), table.data_ptr(), lens_ptr, out.data_ptr(),
-                batch, w["Hq"], w["Hkv"], 16, table.shape[1], w["D"], stream.cuda_stream)
-        else:
-            getattr(_fusedtok, "attention_decode_launch" + sfx)(
-                q.data_ptr(), k.data_ptr(), v.data_ptr(), lens_ptr, out.data_ptr(),
-                batch, w["Hq"], w["Hkv"], wl["T"], w["D"], stream.cuda_stream)
+    step = case.step
 
     use_graph = args.graph or args.workload == "c5"
     graphs = None
@@ -356,24 +527,22 @@ def run_ours(args, w, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-timed region: K steps, inputs resident
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    _fusedtok.attention_launch_count(reset=True)
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for i in range(args.steps):
+    def run(i):
         if graphs:
             graphs[i % n_sets].replay()
         else:
             step(i)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    launches = _fusedtok.attention_launch_count() if not graphs else args.steps * (2 if split_kv else 1)
+
+    # ---- device-timed regions: `rounds` x exactly K steps, inputs resident
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    _fusedtok.attention_launch_count(reset=True)
+    round_ms = timed_rounds(torch, run, args.steps, 1 if args.profile else args.rounds, barrier)
+    launches = (_fusedtok.attention_launch_count() if not graphs else len(round_ms) * args.steps) // len(round_ms)
+    if dec is not None and args.exchange == "nccl":
+        launches = args.steps * case.launches_per_step()
+    ms = statistics.median(round_ms)
     if args.profile:
         print(json.dumps({"profile_run": True, "ms_per_step": ms / args.steps, "workload": args.workload,
                           "GBps": bytes_step / (ms / args.steps * 1e-3) / 1e9}), flush=True)
@@ -385,7 +554,7 @@ def run_ours(args, w, rank, world, local_rank):
     j = 0
     while time.perf_counter() < t_end:
         for _ in range(50):
-            (graphs[j % n_sets].replay() if graphs else step(j))
+            run(j)
             j += 1
         torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
@@ -422,20 +591,23 @@ def run_ours(args, w, rank, world, local_rank):
 
     for i in range(3):
         e2e_step(i)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        e2e_step(i)
-    barrier()
-    e2e_s = time.perf_counter() - t0
+    e2e_rounds = []
+    for _ in range(3):
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            e2e_step(i)
+        barrier()
+        e2e_rounds.append(time.perf_counter() - t0)
     h2d = q_host.numel() * q_host.element_size() + (lens_host.numel() * 4 if lens_host is not None else 0)
     d2h = out_host.numel() * out_host.element_size()
 
-    # ---- max over ranks
+    # ---- max over ranks (round by round), then the median round
+    round_ms = max_over_ranks(torch, dist, device, round_ms)
+    e2e_rounds = max_over_ranks(torch, dist, device, e2e_rounds)
+    ms = statistics.median(round_ms)
+    e2e_s = statistics.median(e2e_rounds)
     if dist is not None:
-        t = torch.tensor([ms, e2e_s], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_s = float(t[0]), float(t[1])
         tot = torch.tensor([float(bytes_step), float(batch)], device=device, dtype=torch.float64)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
         job_bytes, job_seqs = float(tot[0]), float(tot[1])
@@ -443,6 +615,14 @@ def run_ours(args, w, rank, world, local_rank):
             job_seqs = float(batch)            # every rank works on the same sequences
     else:
         job_bytes, job_seqs = float(bytes_step), float(batch)
+
+    # ---- N > 1, default workload: the multi-GPU paths the headline does not cover
+    extra = {}
+    if dist is not None and args.workload == "c2" and not args.no_multi_extras:
+        case.close()
+        del sets, case
+        torch.cuda.empty_cache()
+        extra = multi_gpu_extras(args, torch, dist, device, rank, world, ms / args.steps, barrier)
 
     if rank != 0:
         if dist is not None:
@@ -457,6 +637,7 @@ def run_ours(args, w, rank, world, local_rank):
     line = {
         "metric": "decode_attn_kv_read_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "rounds": len(round_ms), "rounds_ms_per_step": [r / args.steps for r in round_ms],
         "higher_is_better": True, "scaling": "strong" if split_kv else args.scaling,
         "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
         "seq_steps_per_s": job_seqs / (ms_step * 1e-3),
@@ -471,19 +652,28 @@ def run_ours(args, w, rank, world, local_rank):
             "parallelism": ("kv-length split x%d, %s exchange of (m,l,acc) + merge" % (world, args.exchange)) if split_kv else
                            ("batch-sharded x%d, no communication" % world),
             "cuda_graph": bool(graphs),
+            "timing": "%d rounds of %d back-to-back steps, CUDA events, max over ranks per round, median round"
+                      % (len(round_ms), args.steps),
         },
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                      "frac": per_gpu / peak, "peak_kind": "of " + peak_kind,
                      "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                     "note": "achieved = algorithmic bytes / whole step time (one kernel per step, launch gaps included)"},
+                     "traffic_source": "ncu capture of one launch of this kernel on this workload, taken separately",
+                     "note": "achieved = algorithmic bytes / whole step time (one kernel per step, launch gaps included); "
+                             "the peak is a copy (read + write) bandwidth while this kernel almost only reads, so "
+                             "a fraction slightly above 1 is possible"},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s / args.steps * 1e3,
+                "rounds_ms_per_step": [r / args.steps * 1e3 for r in e2e_rounds],
                 "note": "public operator; q/lens H2D from pinned memory and result D2H + host read every step; "
                         "KV cache is device-resident decode state"},
         "gpu_launches": launches,
         "device_status": status,
         "clocks": clocks,
     }
+    line.update(extra)
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
 
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
@@ -892,6 +1082,9 @@ def main():
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="KV-length split (c4, N>1): the library's own peer exchange or an NCCL all-gather")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--rounds", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
+    ap.add_argument("--no-multi-extras", action="store_true",
+                    help="N > 1: skip the kv_split and c2_strong measurements that ride on the default line")
     ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE",
                     help="override a field of the workload (e.g. --set T=32768), for experiments")
     ap.add_argument("--profile", action="store_true",

@@ -31,16 +31,25 @@ def stale():
     return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
-    if not force and not stale():
+def build(force=False, verbose=False, defines=(), out=None):
+    """Compile the library. `defines` / `out` produce a variant build next to the product (for example
+    ``defines=["FTK_TIMELINE"]``: per-CTA timestamps in the tensor-core decode kernel, read back with
+    ``ftk_debug_timeline``); the product itself is always built without defines."""
+    target = out or LIB
+    if not force and not defines and not stale():
         return LIB
-    cmd = ["nvcc"] + NVCC_FLAGS
+    cmd = ["nvcc"] + NVCC_FLAGS + ["-D" + d for d in defines]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB]
+    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", target]
     subprocess.check_call(cmd)
-    return LIB
+    return target
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    # python fusedtok_b200/_build.py [--force] [-v] [-DNAME ...] [--out path]
+    defs = [a[2:] for a in sys.argv[1:] if a.startswith("-D")]
+    out_path = sys.argv[sys.argv.index("--out") + 1] if "--out" in sys.argv else None
+    if defs and not out_path:
+        raise SystemExit("a build with -D defines needs --out: the product library is built without defines")
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, defines=defs, out=out_path))

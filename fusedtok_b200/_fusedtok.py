@@ -68,6 +68,7 @@ _lib.fusedtok_attention_decode_exchange_launch.argtypes = (
 _lib.fusedtok_attention_device_status.argtypes = [ctypes.POINTER(_i)]
 _lib.fusedtok_attention_launch_count.argtypes = [_i]
 _lib.fusedtok_attention_launch_count.restype = ctypes.c_longlong
+_lib.fusedtok_debug_poke_status.argtypes = [_i, _i, _i]
 
 # every symbol include/fusedtok_b200.h declares
 EXPORTS = (
@@ -89,7 +90,7 @@ EXPORTS = (
     "fusedtok_exchange_alloc", "fusedtok_exchange_free", "fusedtok_exchange_export",
     "fusedtok_exchange_open", "fusedtok_exchange_close", "fusedtok_attention_decode_exchange_launch",
     "fusedtok_attention_decode_launch_noalloc",
-    "fusedtok_attention_device_status", "fusedtok_attention_launch_count",
+    "fusedtok_attention_device_status", "fusedtok_attention_launch_count", "fusedtok_debug_poke_status",
 )
 
 
@@ -364,8 +365,8 @@ def exchange_close(ptr):
 
 def attention_decode_exchange_launch(dtype, q, k, v, lens, out, buffers, rank, batch, hq, hkv, t_seq,
                                      dim, stream=0):
-    """KV-length split step with direct peer exchange: `buffers` lists every
-    rank's exchange buffer pointer (own at index `rank`)."""
+    """KV-length split step with direct peer exchange, one kernel per rank:
+    `buffers` lists every rank's exchange buffer pointer (own at index `rank`)."""
     n = len(buffers)
     arr = (_vp * n)(*buffers)
     _check(_lib.fusedtok_attention_decode_exchange_launch(

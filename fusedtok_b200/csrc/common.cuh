@@ -6,17 +6,25 @@
 // head chunk) triple - the query heads of one GQA group (at most GC of them)
 // that share the same K/V rows. A unit with len_b valid rows has
 // ceil(len_b / TILE) TILES of TILE cache rows. All tiles of all units, in
-// (b, kv, chunk, tile) order, form one linear sequence; CTA c of n owns the
-// contiguous range [c*total/n, (c+1)*total/n). A CTA therefore walks through
-// a few SEGMENTS (maximal runs of tiles of one unit). A segment that covers
-// its whole unit is finished in place; otherwise its (m, l, acc) goes to the
-// workspace slot c + unit (unique, because both indices only grow along the
-// walk), the CTA bumps the unit's arrival counter, and whichever CTA arrives
-// last folds the unit's slots - always in CTA order, so the result does not
-// depend on who was last. The split depends only on (lens, n): results are
-// bit-identical from call to call. (Counterpart of the reference's workspace +
-// attn_reduce_kernel, src/attention.cu:434-463 and :478-549, without the
-// second launch.)
+// (b, kv, chunk, tile) order, form one linear sequence, which a PLAN cuts into
+// RANGES whose boundaries are a pure function of (lens, number of CTAs):
+//   * equal split: range c = [c*total/n, (c+1)*total/n), one per CTA;
+//   * static + dynamic (large launches, tensor-core kernel): the sequence is cut
+//     into one block per CTA; CTA c first takes the static range at the head
+//     of block c; the last few tiles of every block are cut into small ranges
+//     of `chunk` tiles that the CTAs take from an atomic counter as they run
+//     dry, so that SMs which stream faster do more of them.
+// A range crosses unit boundaries; each maximal run of its tiles inside one
+// unit is a SEGMENT. A segment that covers its whole unit is finished in
+// place; otherwise its (m, l, acc) goes to the workspace slot range + unit
+// (unique, because both indices only grow along the tile sequence), the CTA
+// bumps the unit's arrival counter, and whichever CTA arrives last folds the
+// unit's slots - always in range order. WHICH CTA computes a tail range varies
+// from launch to launch; what is computed and the order in which it is merged
+// do not, so results are bit-identical from call to call. (Counterpart of the
+// reference's workspace + attn_reduce_kernel, src/attention.cu:434-463 and
+// :478-549, without the second launch, and of its capacity-based equal slice
+// counts, src/attention.cu:1819-1821.)
 #pragma once
 
 #include <cuda_bf16.h>
@@ -38,6 +46,8 @@ enum : int {
     ST_WAIT_EMPTY_TIMEOUT = 2,   // the producer gave up waiting for a free stage
     ST_SMEM_MISALIGNED = 3,
     ST_DRAIN_TIMEOUT = 4,
+    ST_PEER_TIMEOUT = 5,         // a peer's block of the KV-length split never arrived
+    ST_WAIT_RANGE_TIMEOUT = 7,   // a consumer gave up waiting for the producer's next range
 };
 
 struct DecodeParams {
@@ -49,14 +59,18 @@ struct DecodeParams {
     const int* table;     // [B, tbl_width] block ids, null for contiguous
     float* ws_ml;         // [slots][GC][2]  (m natural-log units, l)
     float* ws_acc;        // [slots][GC][D]  unnormalised
-    int* counters;        // [units] arrival counters, zero between launches (the last arriver resets)
+    int* counters;        // [units] arrival counters, zero between launches (the last arriver resets);
+                          // counters[units] hands out the tail ranges of a launch (reset by the last taker)
     int* status;          // device status word
     float* triple_ml;     // when non-null: emit raw triples instead of `out`: one block
                           // [B*Hq*2 (m, l), padded | B*Hq*D unnormalised acc] starting here ...
     size_t triple_acc_off;  // ... with the acc part at this float offset
-    // KV-length split with direct peer exchange: when n_peers > 0 the triple block is written
-    // into EVERY rank's exchange buffer (plain stores over NVLink) instead of triple_ml.
+    // KV-length split with direct peer exchange: when n_peers > 0 the rows of every finished unit
+    // are written into EVERY rank's exchange buffer (plain stores over NVLink) instead of
+    // triple_ml, a per-(unit, rank) flag is raised there, and at its end every CTA folds the n
+    // blocks of its share of the rows into `out` (peer_fold).
     float* peer_blocks[16];          // data region of each rank's exchange buffer (own included)
+    unsigned int* peer_hdr[16];      // header of each rank's exchange buffer
     const unsigned int* peer_epoch;  // this rank's count of completed exchange steps
     int n_peers, peer_rank;
     long long peer_nf;               // floats per triple block
@@ -67,6 +81,9 @@ struct DecodeParams {
     int page, tbl_width;
     int box_rows, box_shift;   // rows per TMA box (a power of two) and its log2 (tensor-core kernel)
     int ncta;
+    int dyn_chunk;        // tiles per tail range of the static + dynamic plan; 0 = equal split only
+    int dyn_tail_max;     // most tiles per CTA that go to the dynamic tail
+    int sched_table;      // lens given and the per-sequence tile prefix sums fit the kernel's table
     float scale;          // 1/sqrt(D)
 };
 
@@ -137,7 +154,7 @@ template <> struct Store<__half> {
 
 __device__ __forceinline__ float* triple_block(const DecodeParams& p, int j) {
     if (!p.n_peers) return p.triple_ml;
-    const unsigned int parity = (__ldg(p.peer_epoch) + 1u) & 1u;
+    const unsigned int parity = (__ldcg(p.peer_epoch) + 1u) & 1u;   // L2: the word changes between launches
     return p.peer_blocks[j] + ((size_t)parity * p.n_peers + p.peer_rank) * (size_t)p.peer_nf;
 }
 
@@ -156,6 +173,9 @@ __device__ __forceinline__ long long qdiv(long long a, long long b) {
     return (long long)((unsigned int)a / (unsigned int)b);
 }
 
+constexpr int SCHED_MAX_B = 2048;   // sequences whose tile prefix sums fit the shared-memory table
+constexpr int DYN_MIN_PER = 24;     // tiles per CTA below which a launch keeps the equal split
+
 struct SchedShared {
     long long total;     // tiles in the whole launch
     long long red[33];   // block-reduction scratch
@@ -163,6 +183,93 @@ struct SchedShared {
     int b_start;
     int found;
 };
+
+// How the tile sequence of a launch is cut into ranges. Under the static + dynamic plan the sequence is
+// cut into ncta equal blocks of `per` tiles; block c is the static range of CTA c (its first S tiles)
+// followed by nd dynamic ranges of `chunk` tiles; what is left over after the ncta blocks (fewer than ncta
+// tiles) forms a few more dynamic ranges. Ranges are numbered in tile order (which is the order partials
+// are merged in); the dynamic ones are handed out round-robin over the blocks (dyn_range).
+struct Plan {
+    long long total;     // tiles in the launch
+    long long per;       // tiles per block; 0 = equal split
+    int S;               // tiles of a block's static range
+    int chunk;           // tiles per dynamic range
+    int nd;              // dynamic ranges per block
+    int nstat;           // ranges inside the blocks: ncta * (1 + nd)
+    int ndyn;            // dynamic ranges in all: ncta * nd + those of the leftover
+    int R;               // ranges (equal split: one per CTA, some possibly empty)
+    int ncta;
+};
+
+// dyn_chunk == 0: equal split. Otherwise a block keeps all but min(per / 6, dyn_tail_max) of its
+// per = total / ncta tiles static (the rest rounded to whole dynamic ranges of dyn_chunk tiles),
+// provided per >= DYN_MIN_PER.
+__device__ __forceinline__ Plan make_plan(long long total, int ncta, int dyn_chunk, int dyn_tail_max) {
+    Plan pl;
+    pl.total = total;
+    pl.per = 0;
+    pl.S = 0;
+    pl.chunk = 1;
+    pl.nd = 0;
+    pl.nstat = ncta;
+    pl.ndyn = 0;
+    pl.R = ncta;
+    pl.ncta = ncta;
+    if (dyn_chunk > 0) {
+        const long long per = qdiv(total, ncta);
+        if (per >= DYN_MIN_PER && per < (1ll << 30)) {
+            int td = (int)(per / 6);
+            if (td > dyn_tail_max) td = dyn_tail_max;
+            const int nd = td / dyn_chunk;
+            if (nd > 0) {
+                pl.per = per;
+                pl.chunk = dyn_chunk;
+                pl.nd = nd;
+                pl.S = (int)per - nd * dyn_chunk;
+                pl.nstat = ncta * (1 + nd);
+                const int left = (int)(total - per * ncta);          // < ncta
+                const int nl = (left + dyn_chunk - 1) / dyn_chunk;
+                pl.ndyn = ncta * nd + nl;
+                pl.R = pl.nstat + nl;
+            }
+        }
+    }
+    return pl;
+}
+// first tile of range r (r == R gives the end of the sequence)
+__device__ __forceinline__ long long range_start(const Plan& pl, int r) {
+    if (!pl.per) return qdiv(pl.total * r, pl.ncta);
+    if (r < pl.nstat) {
+        const int c = (int)((unsigned)r / (unsigned)(1 + pl.nd)), k = r - c * (1 + pl.nd);
+        return (long long)c * pl.per + (k ? pl.S + (k - 1) * pl.chunk : 0);
+    }
+    const long long x = pl.per * pl.ncta + (long long)(r - pl.nstat) * pl.chunk;
+    return x < pl.total ? x : pl.total;
+}
+// range that holds tile x
+__device__ __forceinline__ int range_of(const Plan& pl, long long x) {
+    if (!pl.per) return (int)qdiv((x + 1) * pl.ncta - 1, pl.total);
+    const long long blocks_end = pl.per * pl.ncta;
+    if (x < blocks_end) {
+        const int c = (int)qdiv(x, pl.per);
+        const int off = (int)(x - (long long)c * pl.per);
+        return c * (1 + pl.nd) + (off < pl.S ? 0 : 1 + (off - pl.S) / pl.chunk);
+    }
+    return pl.nstat + (int)qdiv(x - blocks_end, pl.chunk);
+}
+__device__ __forceinline__ bool range_empty(const Plan& pl, int r) {
+    return !pl.per && qdiv(pl.total * r, pl.ncta) == qdiv(pl.total * (r + 1), pl.ncta);
+}
+// static range of CTA c, and the i-th dynamic range in hand-out order
+__device__ __forceinline__ int static_range(const Plan& pl, int c) { return pl.per ? c * (1 + pl.nd) : c; }
+__device__ __forceinline__ int dyn_range(const Plan& pl, int i) {
+    const int in_blocks = pl.ncta * pl.nd;
+    if (i < in_blocks) {
+        const int round = (int)((unsigned)i / (unsigned)pl.ncta), c = i - round * pl.ncta;
+        return c * (1 + pl.nd) + 1 + round;
+    }
+    return pl.nstat + (i - in_blocks);
+}
 
 // Position of one walker inside the linear tile sequence.
 struct Walker {
@@ -184,6 +291,36 @@ __device__ __forceinline__ long long block_sum(long long v, long long* red) {
     return s;
 }
 
+// ---- direct peer exchange (KV-length split) -----------------------------------
+// Exchange buffer of one rank (allocated by the library, mapped into every peer
+// through CUDA IPC): a header of 32-bit words - [0] steps completed (epoch),
+// [1] count of warps that have finished the current step, and from word
+// XCHG_FLAG_WORD on one flag per (unit, rank): "rank's rows of this unit have
+// landed for step <value>" - then, from byte xchg_data_off(rows) on, the triple
+// blocks gather[2][n][nf], double-buffered by step parity.
+constexpr int XCHG_FLAG_WORD = 16;
+constexpr unsigned long long XCHG_WAIT_NS = 2000000000ull;      // bounded wait: 2 s
+__host__ __device__ __forceinline__ size_t xchg_data_off(long long rows, int n) {
+    // at most one unit per (sequence, query head) row
+    return (((size_t)XCHG_FLAG_WORD + (size_t)rows * n) * 4 + 1023) & ~(size_t)1023;
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// One thread, after every thread of the CTA that wrote rows of `unit` has executed
+// __threadfence_system() and the CTA has synchronised: tell every rank that this rank's rows of
+// the unit are in its buffer for the current step.
+__device__ __forceinline__ void peer_signal_unit(const DecodeParams& p, long long unit) {
+    const unsigned int e = __ldcg(p.peer_epoch) + 1u;
+    for (int j = 0; j < p.n_peers; ++j)
+        st_release_sys(p.peer_hdr[j] + XCHG_FLAG_WORD + (size_t)unit * p.n_peers + p.peer_rank, e);
+}
+
 // Zero row for an empty sequence (len == 0): the reference's convention
 // (src/attention.cu:211-216). One thread writes the whole [Hq, D] row.
 template <typename T>
@@ -200,6 +337,11 @@ __device__ void zero_rows(const DecodeParams& p, int b) {
                     *reinterpret_cast<float4*>(blk + p.triple_acc_off + r * p.D + d) = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
+        if (p.n_peers) {
+            __threadfence_system();
+            const int upb = p.Hkv * p.NCH;
+            for (int u = 0; u < upb; ++u) peer_signal_unit(p, (long long)b * upb + u);
+        }
         return;
     }
     T* o = reinterpret_cast<T*>(p.out) + (size_t)b * p.Hq * p.D;
@@ -207,10 +349,10 @@ __device__ void zero_rows(const DecodeParams& p, int b) {
     for (int i = 0; i < n; i += 4) Store<T>::st4(o + i, make_float4(0.f, 0.f, 0.f, 0.f));
 }
 
-// Block-wide: total tile count, this CTA's range and its starting position.
-// Every thread of the block must call it. Returns false for an empty range.
-// Also writes the zero rows of empty sequences (sequence b is handled by the
-// CTA with b % ncta == blockIdx.x).
+// Block-wide: total tile count, this CTA's range under the equal split and its
+// starting position. Every thread of the block must call it. Returns false for
+// an empty range. Also writes the zero rows of empty sequences (sequence b is
+// handled by the CTA with b % ncta == blockIdx.x).
 template <typename T>
 __device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w) {
     const int upb = p.Hkv * p.NCH;
@@ -228,6 +370,8 @@ __device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w) {
         total_nt = block_sum(loc, sh->red);
     }
     const long long total = total_nt * upb;
+    if (threadIdx.x == 0) sh->total = total;
+    __syncthreads();
     const long long start = qdiv(total * c, p.ncta);
     const long long end = qdiv(total * (c + 1), p.ncta);
     if (start >= end) return false;
@@ -281,9 +425,83 @@ __device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w) {
     const long long rem = start - pb * upb;
     w.ub = (int)qdiv(rem, w.nt);
     w.ti = (int)(rem - (long long)w.ub * w.nt);
-    if (threadIdx.x == 0) sh->total = total;
-    __syncthreads();
     return true;
+}
+
+// Block-wide, for launches with lens and at most SCHED_MAX_B sequences: exclusive prefix sums of
+// tiles_of(len_b) into prefix[0 .. B] (prefix[B] = the total), so that afterwards ONE thread can
+// locate any range (walker_locate). Also writes the zero rows of empty sequences, like sched_init.
+// Returns the number of tiles of the launch.
+template <typename T>
+__device__ long long sched_prefix(const DecodeParams& p, SchedShared* sh, unsigned int* prefix) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    unsigned int running = 0;
+    for (int base = 0; base < p.B; base += blockDim.x) {
+        const int b = base + threadIdx.x;
+        unsigned int v = 0;
+        if (b < p.B) {
+            const int len = seq_len(p, b);
+            v = (unsigned int)tiles_of(len);
+            if (len == 0 && (b % p.ncta) == (int)blockIdx.x) zero_rows<T>(p, b);
+        }
+        unsigned int inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned int t = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        __syncthreads();
+        if (lane == 31) sh->red[warp] = inc;
+        __syncthreads();
+        unsigned int before = running, chunk = 0;
+        for (int i = 0; i < nwarp; ++i) {
+            const unsigned int t = (unsigned int)sh->red[i];
+            if (i < warp) before += t;
+            chunk += t;
+        }
+        if (b < p.B) prefix[b] = before + inc - v;
+        running += chunk;
+    }
+    if (threadIdx.x == 0) {
+        prefix[p.B] = running;
+        sh->total = (long long)running * (p.Hkv * p.NCH);
+    }
+    __syncthreads();
+    return sh->total;
+}
+
+// Walker at global tile `start` (one thread; `prefix` from sched_prefix, or null when every sequence
+// has p.T rows). `end` is the range's end.
+__device__ __forceinline__ Walker walker_locate(const DecodeParams& p, const unsigned int* prefix, long long start,
+                                                long long end) {
+    const int upb = p.Hkv * p.NCH;
+    Walker w;
+    w.g = start;
+    w.end = end;
+    const long long x = qdiv(start, upb);
+    long long pb;
+    if (!prefix) {
+        const int nt = tiles_of(p.T);
+        w.b = (int)qdiv(x, nt);
+        pb = (long long)w.b * nt;
+    } else {
+        // last b with prefix[b] <= x (it has tiles, because prefix[b + 1] > x)
+        int lo = 0, hi = p.B;            // invariant: prefix[lo] <= x < prefix[hi]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if ((long long)prefix[mid] <= x) lo = mid;
+            else hi = mid;
+        }
+        w.b = lo;
+        pb = prefix[lo];
+    }
+    w.len = seq_len(p, w.b);
+    w.nt = tiles_of(w.len);
+    const long long rem = start - pb * upb;
+    w.ub = (int)qdiv(rem, w.nt);
+    w.ti = (int)(rem - (long long)w.ub * w.nt);
+    return w;
 }
 
 // Step to the next tile (skipping empty sequences).
@@ -293,17 +511,12 @@ __device__ __forceinline__ void walker_advance(const DecodeParams& p, Walker& w)
     w.ti = 0;
     if (++w.ub < p.Hkv * p.NCH) return;
     w.ub = 0;
-    if (w.g >= w.end) return;          // nothing follows in this CTA's range
+    if (w.g >= w.end) return;          // nothing follows in this range
     do {
         ++w.b;
         w.len = seq_len(p, w.b);
         w.nt = tiles_of(w.len);
     } while (w.nt == 0 && w.b + 1 < p.B);
-}
-
-// CTA that owns global tile x when `total` tiles are split over n CTAs.
-__device__ __forceinline__ int owner_of(long long x, long long total, int n) {
-    return (int)qdiv((x + 1) * n - 1, total);
 }
 
 // Where a finished segment goes.
@@ -313,15 +526,12 @@ struct SegDest {
     long long unit;      // global unit index
     int b, h0;           // sequence and first query head of the unit
     int gvalid;          // query heads in this unit
-    int c_first, c_last; // CTAs holding the unit's first and last tile
-    int nparts;          // CTAs that deliver a partial for this unit
+    int r_first, r_last; // ranges holding the unit's first and last tile
+    int nparts;          // ranges that deliver a partial for this unit
 };
 
-__device__ __forceinline__ bool cta_range_empty(long long total, int n, int c) {
-    return qdiv(total * c, n) == qdiv(total * (c + 1), n);
-}
-
-__device__ __forceinline__ SegDest seg_dest(const DecodeParams& p, const Walker& w, long long total,
+// `w` stands on the segment's last tile, inside range `r`.
+__device__ __forceinline__ SegDest seg_dest(const DecodeParams& p, const Plan& pl, const Walker& w, int r,
                                             long long seg_first_g) {
     SegDest d;
     const int upb = p.Hkv * p.NCH;
@@ -333,16 +543,16 @@ __device__ __forceinline__ SegDest seg_dest(const DecodeParams& p, const Walker&
     d.h0 = kv * p.G + ch * p.GC;
     d.gvalid = min(p.GC, p.G - ch * p.GC);
     d.whole = (seg_first_g == u_start) && (w.g + 1 == u_end);
-    d.slot = (size_t)blockIdx.x + (size_t)d.unit;
-    d.c_first = d.c_last = (int)blockIdx.x;
+    d.slot = (size_t)r + (size_t)d.unit;
+    d.r_first = d.r_last = r;
     d.nparts = 1;
     if (!d.whole) {
-        d.c_first = owner_of(u_start, total, p.ncta);
-        d.c_last = owner_of(u_end - 1, total, p.ncta);
-        d.nparts = d.c_last - d.c_first + 1;
-        if (p.ncta > total)                          // more CTAs than tiles: some ranges are empty
-            for (int c = d.c_first + 1; c < d.c_last; ++c)
-                if (cta_range_empty(total, p.ncta, c)) --d.nparts;
+        d.r_first = range_of(pl, u_start);
+        d.r_last = range_of(pl, u_end - 1);
+        d.nparts = d.r_last - d.r_first + 1;
+        if (!pl.per && pl.ncta > pl.total)           // more CTAs than tiles: some ranges are empty
+            for (int c = d.r_first + 1; c < d.r_last; ++c)
+                if (range_empty(pl, c)) --d.nparts;
     }
     return d;
 }
@@ -373,22 +583,22 @@ __device__ __forceinline__ void emit_final2(const DecodeParams& p, int b, int h,
 // partials with l <= 0 are skipped, the first live one is adopted verbatim,
 // later ones are max-rescaled, then the row is divided by l.
 template <typename T>
-__device__ __forceinline__ void merge_unit(const DecodeParams& p, const SegDest& d, long long total, int tid,
+__device__ __forceinline__ void merge_unit(const DecodeParams& p, const Plan& pl, const SegDest& d, int tid,
                                            int nthreads) {
     constexpr int BATCH = 8;                      // slots fetched together: one L2 round trip per batch
     const int D = p.D, halfd = D >> 1;
-    const bool sparse = p.ncta > total;
+    const bool sparse = !pl.per && pl.ncta > pl.total;
     for (int e = tid; e < d.gvalid * halfd; e += nthreads) {
         const int g = e / halfd, dd = (e % halfd) * 2;
         float m = -INFINITY, l = 0.0f, a0 = 0.0f, a1 = 0.0f;
-        for (int c0 = d.c_first; c0 <= d.c_last; c0 += BATCH) {
+        for (int c0 = d.r_first; c0 <= d.r_last; c0 += BATCH) {
             float2 ml[BATCH], x[BATCH];
 #pragma unroll
             for (int j = 0; j < BATCH; ++j) {
                 const int c = c0 + j;
                 ml[j] = make_float2(0.0f, 0.0f);
                 x[j] = make_float2(0.0f, 0.0f);
-                if (c <= d.c_last && !(sparse && cta_range_empty(total, p.ncta, c))) {
+                if (c <= d.r_last && !(sparse && range_empty(pl, c))) {
                     const size_t pr = ((size_t)c + (size_t)d.unit) * p.GC + g;
                     ml[j] = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + pr * 2));
                     x[j] = __ldcg(reinterpret_cast<const float2*>(p.ws_acc + pr * D + dd));
@@ -421,6 +631,107 @@ __device__ __forceinline__ bool deliver_partial(const DecodeParams& p, const Seg
     const bool last = old == d.nparts - 1;
     if (last) p.counters[d.unit] = 0;          // ready for the next launch
     return last;
+}
+
+// End of a KV-length-split step with direct peer exchange: the warps of the grid share the
+// (sequence, query head) rows; for each of its rows a warp waits - bounded, polling its OWN
+// rank's memory - until all n ranks have flagged the row's unit for this step, then folds the n
+// blocks with the reference's merge rule (src/attention.cu:503-548) and stores the normalised
+// row. `gwarp` of `nwarps` identifies the warp among all participating warps of the grid; every
+// one of them must call this exactly once per launch (the last one advances the step number).
+// Nothing here is waited for by any other rank: flags are raised before any rank starts
+// waiting, so the waits cannot form a cycle.
+template <typename T>
+__device__ void peer_fold(const DecodeParams& p, int gwarp, int nwarps) {
+    const int lane = threadIdx.x & 31;
+    unsigned int* mine = p.peer_hdr[p.peer_rank];
+    const unsigned int e = __ldcg(p.peer_epoch) + 1u;         // this step
+    const unsigned int parity = e & 1u;
+    const long long rows = (long long)p.B * p.Hq;
+    const int D = p.D, chunks = D >> 2, n = p.n_peers;
+    const float* parts = p.peer_blocks[p.peer_rank] + (size_t)parity * n * (size_t)p.peer_nf;
+    T* out = reinterpret_cast<T*>(p.out);
+    bool ok = true;
+    for (long long r = gwarp; r < rows && ok; r += nwarps) {
+        const int b = (int)(r / p.Hq), h = (int)(r % p.Hq);
+        const int kv = h / p.G, ch = (h % p.G) / p.GC;
+        const long long unit = ((long long)b * p.Hkv + kv) * p.NCH + ch;
+        // lane j watches rank j's flag
+        if (lane < n) {
+            const unsigned int* f = mine + XCHG_FLAG_WORD + (size_t)unit * n + lane;
+            if ((int)(ld_acquire_sys(f) - e) < 0) {
+                unsigned long long t0, t1;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+                for (unsigned int it = 1; (int)(ld_acquire_sys(f) - e) < 0; ++it) {
+                    if ((it & 63u) == 0) {
+                        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                        if (t1 - t0 > XCHG_WAIT_NS) {     // a peer never delivered: give up, report, stay usable
+                            atomicCAS(p.status, ST_OK, ST_PEER_TIMEOUT);
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        float4 o[4];                                          // head dim <= 512: at most 4 chunks per lane
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        float m = -INFINITY, l = 0.0f;
+        for (int s = 0; s < n; ++s) {
+            const float* base = parts + (size_t)s * (size_t)p.peer_nf;
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)r * 2));
+            if (ml.y <= 0.0f) continue;
+            const float* a = base + p.triple_acc_off + (size_t)r * D;
+            if (l == 0.0f) {
+                m = ml.x;
+                l = ml.y;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int cc = lane + 32 * j;
+                    if (cc < chunks) o[j] = __ldcg(reinterpret_cast<const float4*>(a + cc * 4));
+                }
+                continue;
+            }
+            const float m_new = fmaxf(m, ml.x);
+            const float r_old = expf(m - m_new), r_new = expf(ml.x - m_new);
+            l = l * r_old + ml.y * r_new;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int cc = lane + 32 * j;
+                if (cc < chunks) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(a + cc * 4));
+                    o[j].x = o[j].x * r_old + v.x * r_new;
+                    o[j].y = o[j].y * r_old + v.y * r_new;
+                    o[j].z = o[j].z * r_old + v.z * r_new;
+                    o[j].w = o[j].w * r_old + v.w * r_new;
+                }
+            }
+            m = m_new;
+        }
+        T* orow = out + (size_t)r * D;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int cc = lane + 32 * j;
+            if (cc < chunks) {
+                float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (l > 0.0f) y = make_float4(o[j].x / l, o[j].y / l, o[j].z / l, o[j].w / l);
+                Store<T>::st4(orow + cc * 4, y);
+            }
+        }
+    }
+    // every warp has read the step number before it arrives here; the last one advances it
+    __syncwarp();
+    if (lane == 0) {
+        const unsigned int arrived = atomicAdd(mine + 1, 1u);
+        if (arrived == (unsigned int)nwarps - 1u) {
+            mine[1] = 0;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned int*>(mine) = e;
+        }
+    }
 }
 
 }  // namespace ftk

@@ -140,9 +140,13 @@ decode_simt_kernel(const DecodeParams p) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         have_work = sched_init<T>(p, &sh, w);   // reads lens
     }
-    if (!have_work) return;
-    const long long total = sh.total;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (!have_work) {
+        if (p.n_peers) peer_fold<T>(p, (int)blockIdx.x * SIMT_WARPS + warp, p.ncta * SIMT_WARPS);
+        return;
+    }
+    const Plan pl = make_plan(sh.total, p.ncta, 0, 0);     // this kernel always runs the equal split: one range per CTA
+    const int r = (int)blockIdx.x;
     const int D = p.D;
     const int chunks = D >> 2;
     const T* kbase = reinterpret_cast<const T*>(p.k);
@@ -292,7 +296,7 @@ decode_simt_kernel(const DecodeParams p) {
 
         const bool seg_end = (w.ti == w.nt - 1) || (w.g + 1 == w.end);
         if (seg_end) {
-            const SegDest dst = seg_dest(p, w, total, seg_first);
+            const SegDest dst = seg_dest(p, pl, w, r, seg_first);
             __syncthreads();                                  // scratch free
 #pragma unroll
             for (int g = 0; g < GC; ++g) {
@@ -342,6 +346,7 @@ decode_simt_kernel(const DecodeParams p) {
                     if (d == 0) *reinterpret_cast<float2*>(p.ws_ml + pr * 2) = ml;
                 }
             }
+            bool unit_done = dst.whole;
             if (!dst.whole) {
                 // publish the partial; the CTA that publishes a unit's last one merges it
                 __threadfence();
@@ -350,12 +355,21 @@ decode_simt_kernel(const DecodeParams p) {
                 __syncthreads();
                 if (s_last) {
                     __threadfence();
-                    merge_unit<T>(p, dst, total, threadIdx.x, SIMT_THREADS);
+                    merge_unit<T>(p, pl, dst, threadIdx.x, SIMT_THREADS);
+                    unit_done = true;
                 }
+            }
+            if (p.n_peers && unit_done) {
+                // the unit's rows are in every rank's exchange buffer: order them before the flags
+                __threadfence_system();
+                __syncthreads();
+                if (threadIdx.x == 0) peer_signal_unit(p, dst.unit);
             }
         }
         walker_advance(p, w);
     }
+    // KV-length split: fold this CTA's share of the rows over the n ranks (every warp of the grid takes part)
+    if (p.n_peers) peer_fold<T>(p, (int)blockIdx.x * SIMT_WARPS + warp, p.ncta * SIMT_WARPS);
 }
 
 }  // namespace ftk

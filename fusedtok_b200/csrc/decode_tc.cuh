@@ -1,5 +1,5 @@
-// Split-KV partial kernel for 16-bit caches (bf16 / fp16), head dim 64 or 128,
-// up to 16 query heads per kv head and chunk: the sm_100a counterpart of the
+// Split-KV partial kernel for 16-bit caches (bf16 / fp16), head dims that are a
+// multiple of 16 up to 256, up to 16 query heads per kv head and chunk: the sm_100a counterpart of the
 // reference's attn_decode_kernel / attn_split_kernel / attn_split_paged_kernel
 // (src/attention.cu:195-319, 336-466, 567-693), redesigned around the memory
 // system instead of translated.
@@ -26,6 +26,14 @@
 //    memory and either finished in place or written to the workspace; the
 //    CTA that delivers the last partial of a unit merges them (no second
 //    launch).
+//  * The CTA works through RANGES of the tile sequence (common.cuh): its static
+//    range first, then tail ranges that the producer takes from an atomic
+//    counter (asked for while the previous range's last tile goes out, so the
+//    round trip is hidden) and announces to the consumers through a small
+//    ring of range descriptors in shared memory.
+//  * KV-length split across GPUs: finished units are stored into every rank's
+//    exchange buffer and flagged; at its end the CTA folds its share of the
+//    rows over the n ranks (peer_fold) - one launch per step and rank.
 //
 // Every wait on an mbarrier is bounded (wall-clock limit); on expiry the
 // kernel records a status code, stops waiting and still runs to completion,
@@ -43,6 +51,17 @@ namespace ftk {
 constexpr int NCW = 8;                        // consumer warps
 constexpr int TC_THREADS = (NCW + 1) * 32;    // + 1 producer warp
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+// A range as the producer announces it to the consumers: the walker at its first tile and its index
+// (r < 0: no more ranges for this CTA).
+struct RangeDesc {
+    long long g, end;
+    int b, ub, ti, nt, len, r;
+};
+// Descriptors in flight. The producer writes descriptor j only after it has a free ring stage for the
+// range's first tile, i.e. when the consumers are inside range j - NS or later (every range has at
+// least one tile), so a ring of more than NS + 1 descriptors is never overwritten while still unread.
+constexpr int QD = 16;
 
 template <int D> struct TcCfg {
     static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head dim: a multiple of 16 up to 256");
@@ -72,7 +91,10 @@ template <int D> struct TcCfg {
     static constexpr int OFF_BAR = OFF_ML + NCW * 8 * 8;             // full[NS], empty[NS]
     static constexpr int OFF_SCHED = OFF_BAR + 2 * NS * 8;
     static constexpr int OFF_ABORT = OFF_SCHED + (int)sizeof(SchedShared);
-    static constexpr int SMEM_BYTES = OFF_ABORT + 16;
+    static constexpr int OFF_DESC = (OFF_ABORT + 16 + 15) & ~15;               // RangeDesc[QD]
+    static constexpr int OFF_DBAR = OFF_DESC + QD * (int)sizeof(RangeDesc);    // "descriptor written" barriers
+    static constexpr int OFF_PREFIX = OFF_DBAR + QD * 8;                       // tile prefix sums per sequence
+    static constexpr int SMEM_BYTES = OFF_PREFIX + (SCHED_MAX_B + 1) * 4 + 12;
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
@@ -195,16 +217,47 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     return d;
 }
 __device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory"); }
+// Barrier over the consumer warps that also ORs a predicate: every consumer thread gets the same answer.
+__device__ __forceinline__ bool consumers_any(bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, 1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)pred), "n"(NCW * 32)
+        : "memory");
+    return r != 0;
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 
+// ---- optional timeline (diagnostic builds only: -DFTK_TIMELINE) ----------------
+// Per-CTA wall-clock stamps and accumulated durations of the last launch, written by one thread of
+// consumer warp 0 (and one stamp by the producer); read back with ftk_debug_timeline(). Slots:
+// 0 entry, 1 dependency wait done, 2 schedule done, 3 first tile landed, 4 producer issued its last
+// copy, 5 last tile consumed, 6 exit, 7 ns spent at segment ends (sum), 8 segment ends, 9 ns spent
+// waiting for tiles (sum), 10 ns in the final publish, 11 ranges processed, 12 ns waiting for range
+// descriptors (sum).
+#ifdef FTK_TIMELINE
+__device__ unsigned long long g_timeline[1024][16];
+#define FTK_STAMP(cond, slot) do { if (cond) g_timeline[blockIdx.x][slot] = global_ns(); } while (0)
+#define FTK_ADD(cond, slot, v) do { if (cond) g_timeline[blockIdx.x][slot] += (v); } while (0)
+#define FTK_NOW() global_ns()
+#else
+#define FTK_STAMP(cond, slot) do { } while (0)
+#define FTK_ADD(cond, slot, v) do { } while (0)
+#define FTK_NOW() 0ull
+#endif
+
 // ---- the kernel ------------------------------------------------------------
 // T: __nv_bfloat16 or __half. D: a multiple of 16 up to 256 (above 128, and where not a multiple of 64, with GP = 8 only). GP: 8 or 16 = query-head rows of
 // the MMA tile that carry data (heads per unit <= GP). PAGED selects the
-// block-table front end; PAGE_LE_TILE says whether a page is at most one tile.
+// block-table front end.
 template <typename T, int D, int GP, bool PAGED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -213,10 +266,18 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     extern __shared__ __align__(1024) uint8_t smem[];
     SchedShared* sh = reinterpret_cast<SchedShared*>(smem + Cfg::OFF_SCHED);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_ABORT);
+    RangeDesc* desc = reinterpret_cast<RangeDesc*>(smem + Cfg::OFF_DESC);
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t bar_full = smem_base + Cfg::OFF_BAR;
     const uint32_t bar_empty = bar_full + Cfg::NS * 8;
+    const uint32_t bar_desc = smem_base + Cfg::OFF_DBAR;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef FTK_TIMELINE
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 16; ++i) g_timeline[blockIdx.x][i] = 0;
+        g_timeline[blockIdx.x][0] = global_ns();
+    }
+#endif
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -228,6 +289,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             mbar_init(bar_full + s * 8, 1);
             mbar_init(bar_empty + s * 8, 4);     // the 4 warps of the group that consumed the stage
         }
+        for (int s = 0; s < QD; ++s) mbar_init(bar_desc + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
@@ -239,27 +301,40 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     // written, which must wait for that kernel to have completed. Letting our
     // own dependents start early is always safe: they wait the same way.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    Walker w;
-    bool have_work;                             // block-uniform
+    const int upb = p.Hkv * p.NCH;
+    const int upb_nch = p.NCH;
+    const unsigned int* prefix = nullptr;       // tile prefix sums, when the schedule needs them
+    Walker w0;                                  // equal-split range of this CTA (more sequences than the table holds)
+    bool have0 = false, by_scan = false;
+    long long total;
     if (!p.lens) {
         // every sequence has p.T rows: the schedule is arithmetic on kernel parameters and
         // belongs to the part that may overlap the previous kernel
-        have_work = sched_init<T>(p, sh, w);
+        total = (long long)p.B * tiles_of(p.T) * upb;
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        FTK_STAMP(threadIdx.x == 0, 1);
     } else {
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        have_work = sched_init<T>(p, sh, w);    // reads lens
+        FTK_STAMP(threadIdx.x == 0, 1);
+        if (p.sched_table) {
+            unsigned int* table = reinterpret_cast<unsigned int*>(smem + Cfg::OFF_PREFIX);
+            total = sched_prefix<T>(p, sh, table);              // reads lens
+            prefix = table;
+        } else {
+            by_scan = true;                                     // the host disables the dynamic tail for these
+            have0 = sched_init<T>(p, sh, w0);
+            total = sh->total;
+        }
     }
-    if (!have_work) return;
-    const long long total = sh->total;
-    const int upb_nch = p.NCH;
+    if (*abort_flag) return;
+    const Plan pl = make_plan(total, p.ncta, by_scan ? 0 : p.dyn_chunk, p.dyn_tail_max);
+    FTK_STAMP(threadIdx.x == 0, 2);
 
     if (warp == NCW) {
         // ===================== producer warp =====================
         // Everything a tile's copies need (row coordinates, block-table
         // entries, byte count) is worked out BEFORE the wait for its ring
         // stage, so that the copies go out the moment the stage is free.
-        if (*abort_flag) return;
         const uint64_t pol = policy_evict_first();
         int issued = 0;
         int kv = 0, unit_row0 = 0;          // of the current unit
@@ -269,6 +344,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         // fetched with one coalesced load and reused for the tiles they cover
         int tbl_b = -1, tbl_base = 0, tbl_val = 0;
         bool new_unit = true;
+        Walker w = {};
         auto prepare = [&]() {
             if (new_unit) {
                 kv = w.ub / upb_nch;
@@ -299,42 +375,87 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 }
             }
         };
-        prepare();
-        int s = 0;                 // ring stage of tile i
+        int s = 0;                 // ring stage of the next tile
         uint32_t ph = 0;           // phase parity of that stage's current use
-        for (int i = 0; w.g < w.end; ++i) {
-            const bool ok = mbar_wait(bar_empty + s * 8, ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY_TIMEOUT);
-            if (!ok) break;
-            const uint32_t dst_k = smem_base + s * Cfg::STAGE_BYTES;
-            const uint32_t dst_v = dst_k + Cfg::KV_BYTES;
-            const uint32_t fb = bar_full + s * 8;
-            if (lane == 0) mbar_expect_tx(fb, bytes);
-            const uint32_t panel_bytes = (uint32_t)p.box_rows * 128u;
-            auto copy_box = [&](uint32_t dst, const CUtensorMap* map) {
-                if constexpr (Cfg::SPLIT) tma_load_rows_split<Cfg::NH>(dst, map, row, panel_bytes, fb, pol);
-                else tma_load_rows(dst, map, row, fb, pol);
-            };
-            if (!PAGED || p.page > TILE) {
-                if (lane == 0) {
-                    copy_box(dst_k, &tm_k);
-                    copy_box(dst_v, &tm_v);
+        int nd = 0;                // ranges announced so far
+        int r = static_range(pl, (int)blockIdx.x);               // the first range is this CTA's own
+        const int tail_ranges = pl.ndyn;                         // 0 under the equal split
+        int* next_tail = p.counters + (size_t)p.B * upb;         // hands out the tail ranges of this launch
+        bool more = by_scan ? have0 : (total > 0 && !range_empty(pl, r));
+        bool gave_up = false;
+        while (more) {
+            w = by_scan ? w0 : walker_locate(p, prefix, range_start(pl, r), range_start(pl, r + 1));
+            bool announce = true;
+            new_unit = true;
+            prepare();
+            int taken = 0;
+            while (w.g < w.end) {
+                // ask for the next tail range while this range's last tile goes out: the answer is
+                // only needed after the copies below have been issued
+                if (pl.per && w.g + 1 == w.end && lane == 0) taken = atomicAdd(next_tail, 1);
+                if (!mbar_wait(bar_empty + s * 8, ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY_TIMEOUT)) {
+                    gave_up = true;
+                    break;
                 }
-            } else {
-                __syncwarp();                                            // expect_tx before any complete_tx
-                if (lane < npg) {
-                    const uint32_t off = (uint32_t)(lane * p.page) * (uint32_t)(Cfg::DP * 2);   // page-major stage
-                    copy_box(dst_k + off, &tm_k);
-                    copy_box(dst_v + off, &tm_v);
+                if (announce) {
+                    if (lane == 0) {
+                        RangeDesc* dsc = desc + (nd % QD);
+                        dsc->g = w.g; dsc->end = w.end;
+                        dsc->b = w.b; dsc->ub = w.ub; dsc->ti = w.ti; dsc->nt = w.nt; dsc->len = w.len;
+                        dsc->r = r;
+                        mbar_arrive(bar_desc + (nd % QD) * 8);            // release: the descriptor is visible
+                    }
+                    ++nd;
+                    announce = false;
+                }
+                const uint32_t dst_k = smem_base + s * Cfg::STAGE_BYTES;
+                const uint32_t dst_v = dst_k + Cfg::KV_BYTES;
+                const uint32_t fb = bar_full + s * 8;
+                if (lane == 0) mbar_expect_tx(fb, bytes);
+                const uint32_t panel_bytes = (uint32_t)p.box_rows * 128u;
+                auto copy_box = [&](uint32_t dst, const CUtensorMap* map) {
+                    if constexpr (Cfg::SPLIT) tma_load_rows_split<Cfg::NH>(dst, map, row, panel_bytes, fb, pol);
+                    else tma_load_rows(dst, map, row, fb, pol);
+                };
+                if (!PAGED || p.page > TILE) {
+                    if (lane == 0) {
+                        copy_box(dst_k, &tm_k);
+                        copy_box(dst_v, &tm_v);
+                    }
+                } else {
+                    __syncwarp();                                            // expect_tx before any complete_tx
+                    if (lane < npg) {
+                        const uint32_t off = (uint32_t)(lane * p.page) * (uint32_t)(Cfg::DP * 2);   // page-major stage
+                        copy_box(dst_k + off, &tm_k);
+                        copy_box(dst_v + off, &tm_v);
+                    }
+                }
+                ++issued;
+                const int ub_before = w.ub, b_before = w.b;
+                walker_advance(p, w);
+                if (++s == Cfg::NS) { s = 0; ph ^= 1u; }
+                if (w.g < w.end) {
+                    new_unit = (w.ub != ub_before) || (w.b != b_before);
+                    prepare();
                 }
             }
-            ++issued;
-            const int ub_before = w.ub, b_before = w.b;
-            walker_advance(p, w);
-            if (++s == Cfg::NS) { s = 0; ph ^= 1u; }
-            if (w.g < w.end) {
-                new_unit = (w.ub != ub_before) || (w.b != b_before);
-                prepare();
+            if (gave_up) break;
+            more = false;
+            if (pl.per) {
+                // every CTA takes from the counter until it is told "none left": tail_ranges + ncta
+                // takes per launch in all, and whoever makes the last one leaves the counter at zero
+                taken = __shfl_sync(0xffffffffu, taken, 0);
+                if (lane == 0 && taken == tail_ranges + pl.ncta - 1) *next_tail = 0;
+                if (taken < tail_ranges) {
+                    r = dyn_range(pl, taken);
+                    more = true;
+                }
             }
+        }
+        FTK_STAMP(lane == 0, 4);
+        if (!gave_up && lane == 0) {
+            desc[nd % QD].r = -1;                                 // no more ranges for this CTA
+            mbar_arrive(bar_desc + (nd % QD) * 8);
         }
         // If something went wrong, do not leave the CTA while our own copies
         // may still be landing in its shared memory: wait (bounded) for the
@@ -376,7 +497,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     uint32_t qb[NBK][KSTEPS][2];        // Q^T as B fragments: head 8*nbk + quad, d = 16*kk + 2*qi + {0,1} (+8)
     float acc[NBK][MT][4];              // O^T: d = 16*mt + quad (+8 for [2],[3]); head 8*nbk + 2*qi + {0,1}
     float m_run[NBK][2], l_run[NBK][2]; // per head 8*nbk + 2*qi + e; l is this thread's share until the epilogue
-    long long seg_first = w.g;
+    long long seg_first = 0;
 
     // Stage layout: boxes of `box_rows` rows back to back; inside a box the
     // D/64 column blocks one after the other, each [box_rows][128 B] with the
@@ -512,6 +633,30 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         }
     };
 
+    // A partial is published one segment late: its stores are issued at the end of its own segment,
+    // but the fence + arrival-counter update (and the merge, if this CTA turns out to be the unit's
+    // last arriver) wait until the end of the NEXT segment, when the stores have long landed and
+    // the round trip of the atomic hides under that segment's fold. The consumers therefore never
+    // sit idle behind a memory fence in the middle of the stream.
+    SegDest pend;
+    bool have_pend = false;             // uniform over the consumer warps
+    pend.whole = true; pend.slot = 0; pend.unit = 0; pend.b = pend.h0 = pend.gvalid = 0;
+    pend.r_first = pend.r_last = pend.nparts = 0;
+    const int tc = warp * 32 + lane;
+
+    for (int nd = 0;; ++nd) {
+        // ---- next range of this CTA, as announced by the producer
+        const unsigned long long tl_d0 = FTK_NOW();
+        const bool got = mbar_wait(bar_desc + (nd % QD) * 8, (uint32_t)((nd / QD) & 1), abort_flag, p.status,
+                                   ST_WAIT_RANGE_TIMEOUT);
+        if (consumers_any(!got)) break;               // the same decision in every consumer warp
+        FTK_ADD(tc == 0, 12, FTK_NOW() - tl_d0);
+        FTK_ADD(tc == 0, 11, 1);
+        const RangeDesc rd = desc[nd % QD];
+        if (rd.r < 0) break;
+        const int r = rd.r;
+        Walker w;
+        w.g = rd.g; w.end = rd.end; w.b = rd.b; w.ub = rd.ub; w.ti = rd.ti; w.nt = rd.nt; w.len = rd.len;
     while (w.g < w.end) {
         // ---- segment begins: its tiles are local indices [i0, i0 + n)
         const long long left = w.end - w.g;
@@ -540,7 +685,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         }
         // ---- this group's tiles of the segment
         for (; own < i0 + n; own += 2) {
+            const unsigned long long tl_w0 = FTK_NOW();
             const bool ok = mbar_wait(bar_full + s * 8, ph, abort_flag, p.status, ST_WAIT_FULL_TIMEOUT);
+            FTK_ADD(tc == 0, 9, FTK_NOW() - tl_w0);
+#ifdef FTK_TIMELINE
+            if (tc == 0 && g_timeline[blockIdx.x][3] == 0) g_timeline[blockIdx.x][3] = global_ns();
+#endif
             const int rows_valid = w.len - (w.ti + (own - i0)) * TILE;      // >= 1
             if (ok) {
                 if (rows_valid >= TILE) process(std::false_type{}, TILE);
@@ -557,7 +707,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         w.ti += n - 1;
         {
             // ---- fold the 8 warp states and emit
-            const SegDest dst = seg_dest(p, w, total, seg_first);
+            const unsigned long long tl_s0 = FTK_NOW();
+            FTK_STAMP(tc == 0, 5);
+            const SegDest dst = seg_dest(p, pl, w, r, seg_first);
 #pragma unroll
             for (int nbk = 0; nbk < NBK; ++nbk)
 #pragma unroll
@@ -568,10 +720,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     l += __shfl_xor_sync(0xffffffffu, l, 16);
                     l_run[nbk][e] = l;
                 }
-            const int tc = warp * 32 + lane;
+            if (have_pend) __threadfence();                        // the previous partial: stored a segment ago
+            int arrivals = 0;
 #pragma unroll
             for (int hh = 0; hh < NBK; ++hh) {
-                bar_consumers();                                   // scratch is free again
+                bar_consumers();                                   // scratch is free again (and the fences above are done)
+                // publish the previous partial; the answer is only looked at after this segment's fold
+                if (hh == 0 && have_pend && tc == 0) arrivals = atomicAdd(p.counters + pend.unit, 1);
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     float* my = s_acc + ((size_t)warp * 8 + qi * 2 + e) * Cfg::ACC_STRIDE + quad;
@@ -617,20 +772,59 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     }
                 }
             }
-            if (!dst.whole) {
-                // publish the partial; the CTA that publishes a unit's last one merges it
-                __threadfence();
-                bar_consumers();
-                if (tc == 0) *s_last = deliver_partial(p, dst) ? 1 : 0;
+            bool merged = false;
+            if (have_pend) {
+                // was that the unit's last partial? then this CTA merges the unit
+                if (tc == 0) {
+                    const bool last = arrivals == pend.nparts - 1;
+                    if (last) p.counters[pend.unit] = 0;           // ready for the next launch
+                    *s_last = last ? 1 : 0;
+                }
                 bar_consumers();
                 if (*s_last) {
                     __threadfence();
-                    merge_unit<T>(p, dst, total, tc, NCW * 32);
+                    merge_unit<T>(p, pl, pend, tc, NCW * 32);
+                    merged = true;
                 }
             }
+            if (p.n_peers && (merged || dst.whole)) {
+                // a unit's rows are in every rank's exchange buffer: order them before the flags
+                __threadfence_system();
+                bar_consumers();
+                if (tc == 0) {
+                    if (merged) peer_signal_unit(p, pend.unit);
+                    if (dst.whole) peer_signal_unit(p, dst.unit);
+                }
+            }
+            have_pend = !dst.whole;
+            pend = dst;
+            FTK_ADD(tc == 0, 7, FTK_NOW() - tl_s0);
+            FTK_ADD(tc == 0, 8, 1);
         }
         walker_advance(p, w);
     }
+    }
+    const unsigned long long tl_f0 = FTK_NOW();
+    if (have_pend) {
+        // the last partial of this CTA: publish it now; the CTA that publishes a unit's last one merges it
+        __threadfence();
+        bar_consumers();
+        if (tc == 0) *s_last = deliver_partial(p, pend) ? 1 : 0;
+        bar_consumers();
+        if (*s_last) {
+            __threadfence();
+            merge_unit<T>(p, pl, pend, tc, NCW * 32);
+            if (p.n_peers) {
+                __threadfence_system();
+                bar_consumers();
+                if (tc == 0) peer_signal_unit(p, pend.unit);
+            }
+        }
+    }
+    FTK_ADD(tc == 0, 10, FTK_NOW() - tl_f0);
+    // KV-length split: fold this CTA's share of the rows over the n ranks (every consumer warp of the grid takes part)
+    if (p.n_peers) peer_fold<T>(p, (int)blockIdx.x * NCW + warp, p.ncta * NCW);
+    FTK_STAMP(tc == 0, 6);
 }
 
 }  // namespace ftk

@@ -174,14 +174,12 @@ constexpr size_t kCountersMin = 1u << 16;    // units covered by the first count
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-// Workspace for `units` units split over `ncta` CTAs. Grow-only; allocation is
-// refused while the stream is being captured.
-int get_arena(DeviceState& d, cudaStream_t cs, size_t units, int ncta, int gc, int dim, bool need_smem_attr,
+// Workspace of `ml_b + acc_b` bytes of partial slots and `words` counter words. Grow-only;
+// allocation is refused while the stream is being captured.
+int get_arena(DeviceState& d, cudaStream_t cs, size_t words, size_t ml_b, size_t acc_b, bool need_smem_attr,
               Arena* a) {
-    const size_t slots = units + (size_t)ncta;
-    const size_t ml_b = align_up(slots * gc * 2 * sizeof(float), 256);
-    const size_t acc_b = align_up(slots * gc * (size_t)dim * sizeof(float), 256);
     const size_t need = ml_b + acc_b;
+    const size_t units = words;
     std::lock_guard<std::mutex> lock(g_mutex);
     const bool first = d.status == nullptr || (need_smem_attr && !d.smem_attr_set);
     if (first || need > d.arena_bytes || units > d.counters_cap) {
@@ -344,29 +342,193 @@ template <typename T> void launch_simt_t(const DecodeParams& p, int lc, cudaStre
 #undef FTK_GO
 }
 
+// ---- launch plan ---------------------------------------------------------------
+// Everything about a decode launch that follows from the shapes, the operand alignment and the SM
+// count: which kernel, how the GQA group is chunked, the grid, how the tile sequence is cut into
+// ranges, and the layout of the split-KV scratch. Both the allocating launchers and the
+// allocation-free one launch from the same plan, so they run the same kernel on the same split.
+struct DecodePlan {
+    bool use_tc = false, paged = false;
+    int GC = 1, NCH = 1, lc = 1, gp = 8;
+    int ncta = 1;
+    int box_rows = TILE, box_shift = 6;
+    int dyn_chunk = 0, dyn_tail_max = 0;          // static + dynamic-tail ranges (0: equal split)
+    int sched_table = 0;                           // per-sequence tile prefix sums fit the kernel's table
+    unsigned long long units = 0, map_rows = 0;
+    size_t words = 0;                              // counter words: one per unit + the tail-range counter
+    size_t slots = 0, ml_b = 0, acc_b = 0;         // partial slots and their two regions
+};
+
+// The fixed scratch of the allocation-free launcher: [256 B header | counters | (m, l) slots | acc slots].
+constexpr size_t kNoAllocBytes = 4u << 20;          // the stated maximum: 4 MiB of scratch
+constexpr size_t kNoAllocUnits = 16384;             // counter words it holds (64 KiB)
+// Finer tail ranges mean more partial slots. The plan only refines while the slots stay inside what
+// the fixed scratch can hold, so that every launcher runs a shape on the same split.
+constexpr size_t kSlotBudgetBytes = kNoAllocBytes - 256 - kNoAllocUnits * sizeof(int) - 512;
+constexpr int kDynTailMax = 32;                     // most tiles per CTA handed out dynamically
+
+// The static + dynamic plan is off unless FUSEDTOK_DYN_CHUNK (tiles per dynamic range) is set in the
+// environment: measured on B200 it evens out the finish times of the CTAs but every additional range end
+// stalls a CTA's consumers for about 2 us, during which its ring of copies drains, and that costs more
+// than the balance gains (configuration 2: 79 us equal split, 88-98 us with 1-4 dynamic ranges per CTA).
+// FUSEDTOK_DYN_TAIL overrides the number of tiles per CTA that are handed out dynamically.
+const int g_env_dyn_chunk = [] {
+    const char* e = std::getenv("FUSEDTOK_DYN_CHUNK");
+    return e ? std::atoi(e) : -1;
+}();
+const int g_env_dyn_tail = [] {
+    const char* e = std::getenv("FUSEDTOK_DYN_TAIL");
+    return e ? std::atoi(e) : -1;
+}();
+
 inline bool is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
 // head dims the tensor-core decode kernel is instantiated for
 inline bool tc_head_dim(int d) {
     return d == 32 || d == 64 || d == 80 || d == 96 || d == 112 || d == 128 || d == 160 || d == 192 || d == 256;
 }
 
-// The one launcher behind every zero-copy entry point.
-// table == nullptr: contiguous cache with `rows` cache rows per (b, kv).
-// table != nullptr: paged pools, page rows per block, tbl_width entries per sequence.
-// partial != nullptr: emit raw triples instead of the normalised output.
+DecodePlan plan_decode(int dt, const void* q, const void* k, const void* v, bool paged, bool has_lens, int batch,
+                       int hq, int hkv, int rows, int page, int dim, int sm_count) {
+    DecodePlan pl;
+    const int G = hq / hkv;
+    pl.paged = paged;
+    pl.map_rows = paged ? 0ull : (unsigned long long)batch * hkv * (unsigned long long)rows;
+    pl.use_tc = dt != F32 && tc_head_dim(dim) &&
+                ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
+                ((reinterpret_cast<uintptr_t>(q)) & 3u) == 0;
+    if (pl.use_tc && !paged && pl.map_rows >= (1ull << 31)) pl.use_tc = false;
+    if (pl.use_tc && paged && !(is_pow2(page) && page >= 8)) pl.use_tc = false;
+    if (pl.use_tc) {
+        pl.GC = std::min(G, (dim == 64 || dim == 128) ? 16 : 8);   // only these two have the 16-head MMA tile
+        pl.gp = pl.GC <= 8 ? 8 : 16;
+        pl.box_rows = paged ? std::min(page, TILE) : TILE;
+        pl.box_shift = 0;
+        while ((1 << pl.box_shift) < pl.box_rows) ++pl.box_shift;
+    } else {
+        pl.lc = dim <= 128 ? 1 : (dim <= 256 ? 2 : 4);
+        if (G == 1) pl.GC = 1;
+        else if (pl.lc == 1) pl.GC = G <= 4 ? 4 : 8;
+        else if (pl.lc == 2) pl.GC = 4;
+        else pl.GC = 2;
+    }
+    pl.NCH = (G + pl.GC - 1) / pl.GC;
+    pl.units = (unsigned long long)batch * hkv * pl.NCH;
+    const unsigned long long tiles_per_seq = (unsigned long long)((rows + TILE - 1) / TILE);
+    const unsigned long long max_tiles = pl.units * tiles_per_seq;
+    pl.ncta = (int)std::min<unsigned long long>((unsigned long long)sm_count * (pl.use_tc ? 1 : 2), max_tiles);
+    if (pl.ncta < 1) pl.ncta = 1;
+    pl.words = (size_t)pl.units + 1;
+
+    const size_t slot_bytes = (size_t)pl.GC * (dim + 2) * sizeof(float);
+    size_t ranges = (size_t)pl.ncta;
+    if (pl.use_tc) {
+        pl.sched_table = has_lens && batch <= SCHED_MAX_B && (unsigned long long)batch * tiles_per_seq < (1ull << 31);
+        const unsigned long long per_max = max_tiles / (unsigned long long)pl.ncta;
+        if (g_env_dyn_chunk > 0 && (!has_lens || pl.sched_table) && per_max >= (unsigned long long)DYN_MIN_PER &&
+            per_max < (1ull << 30)) {
+            int tail = (int)std::min<unsigned long long>(per_max / 6, (unsigned long long)kDynTailMax);
+            if (g_env_dyn_tail > 0) tail = g_env_dyn_tail;
+            const size_t base = (size_t)pl.units + (size_t)pl.ncta;
+            for (int chunk = 2; chunk <= 16 && !pl.dyn_chunk; chunk *= 2) {
+                if (g_env_dyn_chunk >= 0) chunk = g_env_dyn_chunk;
+                if (chunk <= 0 || tail < chunk) break;
+                const size_t tail_ranges = (size_t)pl.ncta * (tail / chunk) + (size_t)pl.ncta / chunk + 2;
+                if (g_env_dyn_chunk > 0 || (base + tail_ranges) * slot_bytes <= kSlotBudgetBytes) {
+                    pl.dyn_chunk = chunk;
+                    pl.dyn_tail_max = tail;
+                    ranges = (size_t)pl.ncta + tail_ranges;
+                }
+                if (g_env_dyn_chunk >= 0) break;
+            }
+        }
+    }
+    pl.slots = (size_t)pl.units + ranges;
+    pl.ml_b = align_up(pl.slots * pl.GC * 2 * sizeof(float), 256);
+    pl.acc_b = align_up(pl.slots * pl.GC * (size_t)dim * sizeof(float), 256);
+    return pl;
+}
+
+// Split-KV scratch of one launch, wherever it lives.
+struct Scratch {
+    int* status;
+    int* counters;
+    float* ws_ml;
+    float* ws_acc;
+};
+
 struct PeerDest {                    // direct peer exchange of the raw triples (KV-length split)
     void* const* bases;              // host array: every rank's exchange buffer, own included
     int n, rank;
 };
 
+// Operands must be aligned to 4 elements (the kernels read and write 4 elements, or 16 bytes, at a time);
+// views that start at an odd element offset are refused here rather than faulting on the device.
+int check_aligned4(int dt, std::initializer_list<const void*> ptrs) {
+    uintptr_t all = 0;
+    for (const void* ptr : ptrs) all |= reinterpret_cast<uintptr_t>(ptr);
+    if (all & (4 * dtype_size(dt) - 1))
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "attention operands must be aligned to 4 elements");
+    return FUSEDTOK_OK;
+}
+
+// Fill the kernel parameters from the plan and launch. table == nullptr: contiguous cache with `rows`
+// cache rows per (b, kv); otherwise paged pools with `page` rows per block and `tbl_width` entries per
+// sequence. partial != nullptr (or peers): emit raw triples instead of the normalised output.
+int decode_launch(const DecodePlan& pl, const Scratch& sc, int dt, const void* q, const void* k, const void* v,
+                  const int* table, const int* lens, void* out, float* partial, int batch, int hq, int hkv, int rows,
+                  int page, int tbl_width, int dim, cudaStream_t cs, const PeerDest* peers) {
+    const long long out_rows = (long long)batch * hq;
+    DecodeParams p;
+    memset(&p, 0, sizeof(p));
+    p.q = q; p.k = k; p.v = v; p.out = out; p.lens = lens; p.table = table;
+    p.triple_ml = partial;
+    p.triple_acc_off = triple_acc_offset(out_rows);
+    if (peers) {
+        p.n_peers = peers->n;
+        p.peer_rank = peers->rank;
+        p.peer_nf = (long long)p.triple_acc_off + out_rows * dim;
+        const size_t data_off = xchg_data_off(out_rows, peers->n);
+        for (int j = 0; j < peers->n; ++j) {
+            p.peer_hdr[j] = static_cast<unsigned int*>(peers->bases[j]);
+            p.peer_blocks[j] = reinterpret_cast<float*>(static_cast<unsigned char*>(peers->bases[j]) + data_off);
+        }
+        p.peer_epoch = p.peer_hdr[peers->rank];
+        p.triple_ml = p.peer_blocks[peers->rank];     // non-null: "emit raw triples"
+    }
+    p.B = batch; p.Hq = hq; p.Hkv = hkv; p.G = hq / hkv; p.T = rows; p.D = dim;
+    p.page = page; p.tbl_width = tbl_width;
+    p.scale = 1.0f / sqrtf((float)dim);
+    p.GC = pl.GC; p.NCH = pl.NCH; p.ncta = pl.ncta;
+    p.box_rows = pl.box_rows; p.box_shift = pl.box_shift;
+    p.dyn_chunk = pl.dyn_chunk; p.dyn_tail_max = pl.dyn_tail_max; p.sched_table = pl.sched_table;
+    p.ws_ml = sc.ws_ml; p.ws_acc = sc.ws_acc; p.counters = sc.counters; p.status = sc.status;
+
+    if (pl.use_tc) {
+        int rc = get_encode_fn();
+        if (rc) return rc;
+        CUtensorMap mk, mv;
+        // paged: pool rows are not known here (table values are trusted): describe the largest range
+        // the int32 TMA coordinate can address; the hardware zero-fills nothing it is not asked for
+        const unsigned long long trows = pl.paged ? (1ull << 31) - 1 : pl.map_rows;
+        if ((rc = encode_map(&mk, dt, k, trows, dim, pl.box_rows))) return rc;
+        if ((rc = encode_map(&mv, dt, v, trows, dim, pl.box_rows))) return rc;
+        if (dt == BF16) launch_tc_t<__nv_bfloat16>(mk, mv, p, pl.gp, pl.paged, cs);
+        else launch_tc_t<__half>(mk, mv, p, pl.gp, pl.paged, cs);
+        return check_launch("attention split-KV tensor-core kernel launch");
+    }
+    if (dt == F32) launch_simt_t<float>(p, pl.lc, cs);
+    else if (dt == BF16) launch_simt_t<__nv_bfloat16>(p, pl.lc, cs);
+    else launch_simt_t<__half>(p, pl.lc, cs);
+    return check_launch("attention split-KV kernel launch");
+}
+
+// The launcher behind every allocating zero-copy entry point.
 int decode_common(int dt, const void* q, const void* k, const void* v, const int* table, const int* lens,
                   void* out, float* partial, int batch, int hq, int hkv, int rows, int page, int tbl_width,
                   int dim, uintptr_t stream, const PeerDest* peers = nullptr) {
     cudaStream_t cs = (cudaStream_t)stream;
     if (batch == 0) return FUSEDTOK_OK;                       // nothing to compute (src/attention.cu:1474)
     const long long out_rows = (long long)batch * hq;
-    const int G = hq / hkv;
-    float* tr_ml = partial;
 
     if (rows == 0 && peers)
         return fail(FUSEDTOK_INVALID_ARGUMENT, "the peer exchange needs at least one cache row per rank");
@@ -375,97 +537,25 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
         if (partial) {
             const long long n = out_rows * dim;
             fill_empty_triple_kernel<<<(unsigned)((n + 255) / 256), 256, 0, cs>>>(
-                tr_ml, tr_ml + triple_acc_offset(out_rows), out_rows, dim);
+                partial, partial + triple_acc_offset(out_rows), out_rows, dim);
             return check_launch("attention empty-triple kernel launch");
         }
         const cudaError_t e = cudaMemsetAsync(out, 0, (size_t)out_rows * dim * dtype_size(dt), cs);
         if (e != cudaSuccess) return cuda_fail("attention zero fill failed", e);
         return FUSEDTOK_OK;
     }
+    int rc = check_aligned4(dt, {q, k, v, out});
+    if (rc) return rc;
 
     DeviceState* dev = nullptr;
-    int rc = device_state(&dev);
-    if (rc) return rc;
-
-    // ---- kernel family and head chunking
-    const bool paged = table != nullptr;
-    const unsigned long long map_rows =
-        paged ? 0ull : (unsigned long long)batch * hkv * (unsigned long long)rows;
-    bool use_tc = dt != F32 && tc_head_dim(dim) &&
-                  ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
-                  ((reinterpret_cast<uintptr_t>(q)) & 3u) == 0;
-    if (use_tc && !paged && map_rows >= (1ull << 31)) use_tc = false;
-    if (use_tc && paged && !(is_pow2(page) && page >= 8)) use_tc = false;
-
-    DecodeParams p;
-    memset(&p, 0, sizeof(p));
-    p.q = q; p.k = k; p.v = v; p.out = out; p.lens = lens; p.table = table;
-    p.triple_ml = tr_ml;
-    p.triple_acc_off = triple_acc_offset(out_rows);
-    if (peers) {
-        p.n_peers = peers->n;
-        p.peer_rank = peers->rank;
-        p.peer_nf = (long long)p.triple_acc_off + out_rows * dim;
-        for (int j = 0; j < peers->n; ++j)
-            p.peer_blocks[j] = reinterpret_cast<float*>(static_cast<unsigned char*>(peers->bases[j]) + XCHG_DATA_BYTES);
-        p.peer_epoch = static_cast<const unsigned int*>(peers->bases[peers->rank]);
-        p.triple_ml = p.peer_blocks[peers->rank];     // non-null: "emit raw triples"
-    }
-    p.B = batch; p.Hq = hq; p.Hkv = hkv; p.G = G; p.T = rows; p.D = dim;
-    p.page = page; p.tbl_width = tbl_width;
-    p.scale = 1.0f / sqrtf((float)dim);
-    int lc = 1, gp = 8;
-    if (use_tc) {
-        p.GC = std::min(G, (dim == 64 || dim == 128) ? 16 : 8);   // only these two have the 16-head MMA tile
-        gp = p.GC <= 8 ? 8 : 16;
-    } else {
-        lc = dim <= 128 ? 1 : (dim <= 256 ? 2 : 4);
-        if (G == 1) p.GC = 1;
-        else if (lc == 1) p.GC = G <= 4 ? 4 : 8;
-        else if (lc == 2) p.GC = 4;
-        else p.GC = 2;
-    }
-    p.NCH = (G + p.GC - 1) / p.GC;
-
-    const unsigned long long units = (unsigned long long)batch * hkv * p.NCH;
-    const unsigned long long max_tiles = units * (unsigned long long)((rows + TILE - 1) / TILE);
-    const int per_sm = use_tc ? 1 : 2;
-    p.ncta = (int)std::min<unsigned long long>((unsigned long long)dev->sm_count * per_sm, max_tiles);
-    if (p.ncta < 1) p.ncta = 1;
-
+    if ((rc = device_state(&dev))) return rc;
+    const DecodePlan pl = plan_decode(dt, q, k, v, table != nullptr, lens != nullptr, batch, hq, hkv, rows, page, dim,
+                                      dev->sm_count);
     Arena a;
-    rc = get_arena(*dev, cs, (size_t)units, p.ncta, p.GC, dim, true, &a);
-    if (rc) return rc;
-    p.ws_ml = a.ws_ml; p.ws_acc = a.ws_acc; p.counters = a.counters; p.status = a.status;
-
-    if (use_tc) {
-        rc = get_encode_fn();
-        if (rc) return rc;
-        CUtensorMap mk, mv;
-        unsigned long long trows;
-        int box_rows;
-        if (paged) {
-            // pool rows are not known here (table values are trusted): describe the largest range
-            // the int32 TMA coordinate can address; the hardware zero-fills nothing it is not asked for
-            trows = (1ull << 31) - 1;
-            box_rows = std::min(page, TILE);
-        } else {
-            trows = map_rows;
-            box_rows = TILE;
-        }
-        p.box_rows = box_rows;
-        p.box_shift = 0;
-        while ((1 << p.box_shift) < box_rows) ++p.box_shift;
-        if ((rc = encode_map(&mk, dt, k, trows, dim, box_rows))) return rc;
-        if ((rc = encode_map(&mv, dt, v, trows, dim, box_rows))) return rc;
-        if (dt == BF16) launch_tc_t<__nv_bfloat16>(mk, mv, p, gp, paged, cs);
-        else launch_tc_t<__half>(mk, mv, p, gp, paged, cs);
-        return check_launch("attention split-KV tensor-core kernel launch");
-    }
-    if (dt == F32) launch_simt_t<float>(p, lc, cs);
-    else if (dt == BF16) launch_simt_t<__nv_bfloat16>(p, lc, cs);
-    else launch_simt_t<__half>(p, lc, cs);
-    return check_launch("attention split-KV kernel launch");
+    if ((rc = get_arena(*dev, cs, pl.words, pl.ml_b, pl.acc_b, true, &a))) return rc;
+    const Scratch sc{a.status, a.counters, a.ws_ml, a.ws_acc};
+    return decode_launch(pl, sc, dt, q, k, v, table, lens, out, partial, batch, hq, hkv, rows, page, tbl_width, dim,
+                         cs, peers);
 }
 
 int decode_contig(int dt, const void* q, const void* k, const void* v, const int* lens, void* out,
@@ -526,6 +616,8 @@ int kv_append_common(int dt, const void* k_new, const void* v_new, const int* ta
     p.rows = rows; p.tbl_width = tbl_width;
     const uintptr_t all = reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new) |
                           reinterpret_cast<uintptr_t>(k_dst) | reinterpret_cast<uintptr_t>(v_dst);
+    if (all & 7u)       // rows are copied 16 or 8 bytes at a time
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "kv append operands must be aligned to 8 bytes");
     const bool wide = (p.row_bytes % 16 == 0) && (all & 15u) == 0;
     const int vec = wide ? 16 : 8;
     const int chunks = hkv * (p.row_bytes / vec);
@@ -1096,7 +1188,8 @@ int fusedtok_exchange_alloc(int n_ranks, int batch, int q_heads, int dim, void**
     if (!buffer || n_ranks < 1 || n_ranks > ftk::MAX_PEERS || batch < 0 || q_heads < 1 || dim < 1)
         return fail(FUSEDTOK_INVALID_ARGUMENT, "exchange buffer: 1..16 ranks, batch>=0, heads>=1, dim>=1");
     const long long nf = fusedtok_attention_partial_floats(batch, q_heads, dim);
-    const size_t total = ftk::XCHG_DATA_BYTES + (size_t)2 * n_ranks * (size_t)nf * sizeof(float);
+    const size_t total = ftk::xchg_data_off((long long)batch * q_heads, n_ranks) +
+                         (size_t)2 * n_ranks * (size_t)nf * sizeof(float);
     void* mem = nullptr;
     cudaError_t e = cudaMalloc(&mem, total);
     if (e != cudaSuccess) return cuda_fail("exchange buffer allocation failed", e);
@@ -1136,50 +1229,37 @@ int fusedtok_attention_decode_exchange_launch(int dtype, const void* q, const vo
     if (dtype < 0 || dtype > 2) return fail(FUSEDTOK_INVALID_ARGUMENT, "dtype must be 0 (f32), 1 (bf16) or 2 (fp16)");
     if (!buffers || n_ranks < 1 || n_ranks > ftk::MAX_PEERS || rank < 0 || rank >= n_ranks)
         return fail(FUSEDTOK_INVALID_ARGUMENT, "exchange needs 1..16 ranks and 0 <= rank < ranks");
-    for (int j = 0; j < n_ranks; ++j)
+    for (int j = 0; j < n_ranks; ++j) {
         if (!buffers[j]) return fail(FUSEDTOK_INVALID_ARGUMENT, "exchange buffer pointers must not be null");
+        for (int i = 0; i < j; ++i)
+            if (buffers[i] == buffers[j])
+                return fail(FUSEDTOK_INVALID_ARGUMENT, "exchange buffers of different ranks must be distinct");
+    }
     int rc = attention_check(batch, q_heads, kv_heads, cache_rows, dim);
     if (rc) return rc;
     if (batch == 0) return FUSEDTOK_OK;
-    PeerDest pd{buffers, n_ranks, rank};
-    rc = decode_common(dtype, q, k, v, nullptr, lens, nullptr, nullptr, batch, q_heads, kv_heads, cache_rows, 0, 0, dim,
-                       stream, &pd);
-    if (rc) return rc;
-    DeviceState* dev = nullptr;
-    if ((rc = device_state(&dev))) return rc;
-    ftk::ExchangeParams x;
-    memset(&x, 0, sizeof(x));
-    for (int j = 0; j < n_ranks; ++j) x.base[j] = static_cast<unsigned int*>(buffers[j]);
-    x.n = n_ranks; x.rank = rank;
-    x.nf = fusedtok_attention_partial_floats(batch, q_heads, dim);
-    x.status = dev->status;
-    const long long rows = (long long)batch * q_heads;
-    const unsigned grid = (unsigned)((rows + ftk::MERGE_WARPS - 1) / ftk::MERGE_WARPS);
-    cudaStream_t cs = (cudaStream_t)stream;
-    if (dtype == F32) ftk::merge_peers_kernel<float><<<grid, ftk::MERGE_WARPS * 32, 0, cs>>>(x, (float*)out, rows, dim);
-    else if (dtype == BF16) ftk::merge_peers_kernel<__nv_bfloat16><<<grid, ftk::MERGE_WARPS * 32, 0, cs>>>(x, (__nv_bfloat16*)out, rows, dim);
-    else ftk::merge_peers_kernel<__half><<<grid, ftk::MERGE_WARPS * 32, 0, cs>>>(x, (__half*)out, rows, dim);
-    return check_launch("attention peer-exchange merge kernel launch");
-}
-
-int fusedtok_attention_device_status(int* status) {
-    if (!status) return fail(FUSEDTOK_INVALID_ARGUMENT, "status pointer must not be null");
-    *status = 0;
-    DeviceState* dev = nullptr;
-    const int rc = device_state(&dev);
-    if (rc) return rc;
-    cudaError_t e = cudaDeviceSynchronize();
-    if (e != cudaSuccess) return cuda_fail("device synchronize failed", e);
-    if (!dev->status) return FUSEDTOK_OK;
-    if ((e = cudaMemcpy(status, dev->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
-        return cuda_fail("status read failed", e);
-    if (*status != 0) {
-        // a launch that gave up may have left arrival counters half-way: start clean
-        if ((e = cudaMemset(dev->status, 0, sizeof(int))) != cudaSuccess) return cuda_fail("status clear failed", e);
-        if (dev->counters && (e = cudaMemset(dev->counters, 0, dev->counters_cap * sizeof(int))) != cudaSuccess)
-            return cuda_fail("counter clear failed", e);
+    if (!out) return fail(FUSEDTOK_INVALID_ARGUMENT, "null attention operand");
+    {
+        // this rank's own buffer has to be memory of the device the kernel runs on: its flags are polled
+        // there. Checked once per buffer and thread (the answer cannot change while the buffer lives).
+        thread_local const void* checked = nullptr;
+        if (checked != buffers[rank]) {
+            int cur = -1;
+            cudaPointerAttributes at;
+            if (cudaGetDevice(&cur) != cudaSuccess || cudaPointerGetAttributes(&at, buffers[rank]) != cudaSuccess) {
+                cudaGetLastError();
+                return fail(FUSEDTOK_INVALID_ARGUMENT, "this rank's exchange buffer is not a CUDA allocation");
+            }
+            if (at.type != cudaMemoryTypeDevice || at.device != cur)
+                return fail(FUSEDTOK_INVALID_ARGUMENT,
+                            "this rank's exchange buffer must be device memory of the current device (device " +
+                                std::to_string(cur) + "), allocated with fusedtok_exchange_alloc");
+            checked = buffers[rank];
+        }
     }
-    return FUSEDTOK_OK;
+    PeerDest pd{buffers, n_ranks, rank};
+    return decode_common(dtype, q, k, v, nullptr, lens, out, nullptr, batch, q_heads, kv_heads, cache_rows, 0, 0, dim,
+                         stream, &pd);
 }
 
 // ---------------------------------------------------------------------------
@@ -1198,18 +1278,21 @@ int fusedtok_attention_device_status(int* status) {
 // The array's name is only a host-side handle; its device address is looked up
 // with cudaGetSymbolAddress once per device (with that device current), on the
 // first call made on that device, together with the kernels' shared-memory
-// attribute. Make that first call outside any stream capture.
+// attribute. That first call must come before any stream capture; one that
+// arrives while the stream is capturing is refused.
 //
 // All calls on a device share the one array and it keeps whatever the previous
-// call left there. The status header is cleared (stream-ordered) at the start
-// of every call; the per-unit arrival counters are left at zero by the kernels
-// themselves; everything else is written before it is read within a call. Two
-// calls that overlap on the GPU (different streams) race on it.
+// call left there. Its first 256 bytes hold the status word of this path
+// (reported and cleared by fusedtok_attention_device_status together with the
+// allocating path's word); the arrival counters that follow are left at zero by
+// the kernels themselves (and cleared by fusedtok_attention_device_status after
+// a launch that gave up); everything else is written before it is read within a
+// call. Two calls that overlap on the GPU (different streams) race on it.
 // ---------------------------------------------------------------------------
+}  // extern "C"
+
 namespace {
 
-constexpr size_t kNoAllocBytes = 4u << 20;          // the stated maximum: 4 MiB of scratch
-constexpr size_t kNoAllocUnits = 16384;             // (sequence, kv head, head chunk) units it can track (64 KiB)
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 struct NoAllocDevice {
@@ -1219,7 +1302,7 @@ struct NoAllocDevice {
 NoAllocDevice g_noalloc_dev[kMaxDevices];
 std::mutex g_noalloc_mutex;
 
-int noalloc_setup(unsigned char** base_out, int* sm_count) {
+int noalloc_setup(cudaStream_t cs, unsigned char** base_out, int* sm_count) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail("cudaGetDevice", e);
@@ -1229,6 +1312,10 @@ int noalloc_setup(unsigned char** base_out, int* sm_count) {
     std::lock_guard<std::mutex> lock(g_noalloc_mutex);
     NoAllocDevice& d = g_noalloc_dev[dev];
     if (!d.ready) {
+        if (stream_is_capturing(cs))
+            return fail(FUSEDTOK_RUNTIME_ERROR,
+                        "the first allocation-free decode call on a device sets the library up and cannot be "
+                        "captured - warm the shape up once before capturing");
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
         if (e != cudaSuccess || !ptr) return cuda_fail("cudaGetSymbolAddress(static scratch)", e);
@@ -1242,6 +1329,8 @@ int noalloc_setup(unsigned char** base_out, int* sm_count) {
 }
 
 }  // namespace
+
+extern "C" {
 
 int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const void* k, const void* v,
                                              const int* lens, void* out, int batch, int q_heads, int kv_heads,
@@ -1257,80 +1346,124 @@ int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const voi
         if (e != cudaSuccess) return cuda_fail("attention zero fill failed", e);
         return FUSEDTOK_OK;
     }
+    if ((rc = check_aligned4(dtype, {q, k, v, out}))) return rc;
     unsigned char* base = nullptr;
     int sm_count = 0;
-    if ((rc = noalloc_setup(&base, &sm_count))) return rc;
+    if ((rc = noalloc_setup(cs, &base, &sm_count))) return rc;
 
-    // same kernel selection as the allocating launcher
-    const int G = q_heads / kv_heads;
-    const unsigned long long map_rows = (unsigned long long)batch * kv_heads * (unsigned long long)cache_rows;
-    const bool use_tc = dtype != F32 && tc_head_dim(dim) && map_rows < (1ull << 31) &&
-                        ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
-                        ((reinterpret_cast<uintptr_t>(q)) & 3u) == 0;
-    DecodeParams p;
-    memset(&p, 0, sizeof(p));
-    p.q = q; p.k = k; p.v = v; p.out = out; p.lens = lens;
-    p.B = batch; p.Hq = q_heads; p.Hkv = kv_heads; p.G = G; p.T = cache_rows; p.D = dim;
-    p.scale = 1.0f / sqrtf((float)dim);
-    int lc = 1, gp = 8;
-    if (use_tc) {
-        p.GC = std::min(G, (dim == 64 || dim == 128) ? 16 : 8);   // only these two have the 16-head MMA tile
-        gp = p.GC <= 8 ? 8 : 16;
-    } else {
-        lc = dim <= 128 ? 1 : (dim <= 256 ? 2 : 4);
-        if (G == 1) p.GC = 1;
-        else if (lc == 1) p.GC = G <= 4 ? 4 : 8;
-        else if (lc == 2) p.GC = 4;
-        else p.GC = 2;
-    }
-    p.NCH = (G + p.GC - 1) / p.GC;
-    const unsigned long long units = (unsigned long long)batch * kv_heads * p.NCH;
-    const unsigned long long max_tiles = units * (unsigned long long)((cache_rows + TILE - 1) / TILE);
-    p.ncta = (int)std::min<unsigned long long>((unsigned long long)sm_count * (use_tc ? 1 : 2), max_tiles);
-    if (p.ncta < 1) p.ncta = 1;
-
-    // carve the static array: [256 B header | arrival counters (fixed size) | (m, l) slots | acc slots].
+    // the same plan as the allocating launcher: same kernel, same split, same slot layout
+    const DecodePlan pl = plan_decode(dtype, q, k, v, false, lens != nullptr, batch, q_heads, kv_heads, cache_rows, 0,
+                                      dim, sm_count);
+    // carve the static array: [256 B header | counters (fixed size) | (m, l) slots | acc slots].
     // The counter region has a fixed place and size so that it is never reused as slot storage:
-    // counters must read zero at the start of every call whatever shape ran before (the kernels
-    // leave them at zero; the array itself starts zeroed).
-    const size_t slots = (size_t)units + (size_t)p.ncta;
+    // counters must read zero at the start of every call whatever shape ran before.
     const size_t cnt_b = kNoAllocUnits * sizeof(int);
-    const size_t ml_b = align_up(slots * p.GC * 2 * sizeof(float), 256);
-    const size_t acc_b = align_up(slots * p.GC * (size_t)dim * sizeof(float), 256);
-    const size_t need = 256 + cnt_b + ml_b + acc_b;
-    if (units > kNoAllocUnits)
+    const size_t need = 256 + cnt_b + pl.ml_b + pl.acc_b;
+    if (pl.words > kNoAllocUnits)
         return fail(FUSEDTOK_INVALID_ARGUMENT,
-                    "shape has " + std::to_string(units) + " (sequence, kv head) units but the allocation-free "
-                    "entry point is limited to " + std::to_string(kNoAllocUnits));
+                    "shape has " + std::to_string(pl.units) + " (sequence, kv head) units but the allocation-free "
+                    "entry point is limited to " + std::to_string(kNoAllocUnits - 1));
     if (need > kNoAllocBytes)
         return fail(FUSEDTOK_INVALID_ARGUMENT,
                     "shape needs " + std::to_string(need) + " bytes of split-KV scratch but the allocation-free "
                     "entry point has a fixed " + std::to_string(kNoAllocBytes) + " bytes; use "
                     "fusedtok_attention_decode_launch* for this shape");
-    p.status = reinterpret_cast<int*>(base);
-    p.counters = reinterpret_cast<int*>(base + 256);
-    p.ws_ml = reinterpret_cast<float*>(base + 256 + cnt_b);
-    p.ws_acc = reinterpret_cast<float*>(base + 256 + cnt_b + ml_b);
-    cudaError_t e = cudaMemsetAsync(base, 0, 256, cs);          // header must start at zero
-    if (e != cudaSuccess) return cuda_fail("static scratch header clear failed", e);
-
-    if (use_tc) {
-        if ((rc = get_encode_fn())) return rc;
-        CUtensorMap mk, mv;
-        p.box_rows = TILE;
-        p.box_shift = 6;
-        if ((rc = encode_map(&mk, dtype, k, map_rows, dim, TILE))) return rc;
-        if ((rc = encode_map(&mv, dtype, v, map_rows, dim, TILE))) return rc;
-        if (dtype == BF16) launch_tc_t<__nv_bfloat16>(mk, mv, p, gp, false, cs);
-        else launch_tc_t<__half>(mk, mv, p, gp, false, cs);
-        return check_launch("attention split-KV tensor-core kernel launch");
-    }
-    if (dtype == F32) launch_simt_t<float>(p, lc, cs);
-    else if (dtype == BF16) launch_simt_t<__nv_bfloat16>(p, lc, cs);
-    else launch_simt_t<__half>(p, lc, cs);
-    return check_launch("attention split-KV kernel launch");
+    const Scratch sc{reinterpret_cast<int*>(base), reinterpret_cast<int*>(base + 256),
+                     reinterpret_cast<float*>(base + 256 + cnt_b),
+                     reinterpret_cast<float*>(base + 256 + cnt_b + pl.ml_b)};
+    return decode_launch(pl, sc, dtype, q, k, v, nullptr, lens, out, nullptr, batch, q_heads, kv_heads, cache_rows, 0,
+                         0, dim, cs, nullptr);
 }
 
+int fusedtok_attention_device_status(int* status) {
+    if (!status) return fail(FUSEDTOK_INVALID_ARGUMENT, "status pointer must not be null");
+    *status = 0;
+    DeviceState* dev = nullptr;
+    const int rc = device_state(&dev);
+    if (rc) return rc;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail("device synchronize failed", e);
+    int word = 0;
+    if (dev->status) {
+        if ((e = cudaMemcpy(&word, dev->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+            return cuda_fail("status read failed", e);
+        if (word != 0) {
+            // a launch that gave up may have left arrival counters half-way: start clean
+            if ((e = cudaMemset(dev->status, 0, sizeof(int))) != cudaSuccess) return cuda_fail("status clear failed", e);
+            if (dev->counters && (e = cudaMemset(dev->counters, 0, dev->counters_cap * sizeof(int))) != cudaSuccess)
+                return cuda_fail("counter clear failed", e);
+            *status = word;
+        }
+    }
+    // the allocation-free path keeps its own word in the header of its static scratch (no allocation here
+    // either: the address was cached by that path's first call)
+    int cur = 0;
+    unsigned char* fixed = nullptr;
+    if (cudaGetDevice(&cur) == cudaSuccess && cur >= 0 && cur < kMaxDevices) {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (g_noalloc_dev[cur].ready) fixed = g_noalloc_dev[cur].base;
+    }
+    if (fixed) {
+        if ((e = cudaMemcpy(&word, fixed, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+            return cuda_fail("status read failed", e);
+        if (word != 0) {
+            if ((e = cudaMemset(fixed, 0, 256 + kNoAllocUnits * sizeof(int))) != cudaSuccess)
+                return cuda_fail("static scratch clear failed", e);
+            if (*status == 0) *status = word;
+        }
+    }
+    return FUSEDTOK_OK;
+}
+
+int fusedtok_debug_poke_status(int which, int code, int counter_index) {
+    DeviceState* dev = nullptr;
+    int rc = device_state(&dev);
+    if (rc) return rc;
+    int* word = nullptr;
+    int* counters = nullptr;
+    if (which == 0) {
+        word = dev->status;
+        counters = dev->counters;
+    } else {
+        int cur = 0;
+        if (cudaGetDevice(&cur) != cudaSuccess) return cuda_fail("cudaGetDevice", cudaGetLastError());
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (g_noalloc_dev[cur].ready) {
+            word = reinterpret_cast<int*>(g_noalloc_dev[cur].base);
+            counters = reinterpret_cast<int*>(g_noalloc_dev[cur].base + 256);
+        }
+    }
+    if (!word) return fail(FUSEDTOK_RUNTIME_ERROR, "that path has not run on this device yet");
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail("device synchronize failed", e);
+    if (code >= 0 && (e = cudaMemcpy(word, &code, sizeof(int), cudaMemcpyHostToDevice)) != cudaSuccess)
+        return cuda_fail("status write failed", e);
+    if (counter_index >= 0) {
+        if (code >= 0) {
+            const int one = 1;
+            if ((e = cudaMemcpy(counters + counter_index, &one, sizeof(int), cudaMemcpyHostToDevice)) != cudaSuccess)
+                return cuda_fail("counter write failed", e);
+        } else {
+            int v = 0;
+            if ((e = cudaMemcpy(&v, counters + counter_index, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+                return cuda_fail("counter read failed", e);
+            return 100 + v;
+        }
+    }
+    return FUSEDTOK_OK;
+}
+
+#ifdef FTK_TIMELINE
+// Diagnostic builds only: copies the per-CTA timeline of the last tensor-core decode launch (1024 x 16
+// 64-bit words, see decode_tc.cuh) to `host` after synchronising the device.
+int ftk_debug_timeline(void* host) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail("device synchronize failed", e);
+    e = cudaMemcpyFromSymbol(host, ftk::g_timeline, sizeof(unsigned long long) * 1024 * 16);
+    if (e != cudaSuccess) return cuda_fail("timeline read failed", e);
+    return FUSEDTOK_OK;
+}
+#endif
 
 long long fusedtok_attention_launch_count(int reset) {
     const long long n = g_launches;

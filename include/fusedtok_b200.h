@@ -27,7 +27,10 @@
  * out [B, Hq, D] in the storage type. Query head h reads kv head
  * h / (Hq / Hkv). Rows at and past lens[b] are never used; lens[b] == 0 or
  * T == 0 gives an exact zero row. D % 4 == 0, D <= 512, Hq % Hkv == 0.
- * Softmax scale 1/sqrt(D); accumulation in float32.
+ * Softmax scale 1/sqrt(D); accumulation in float32. q, k, v and out must be
+ * aligned to 4 elements (16 bytes for float32, 8 for the 16-bit types): a view
+ * that starts at an odd element offset is refused with
+ * FUSEDTOK_INVALID_ARGUMENT instead of faulting on the device.
  */
 #ifndef FUSEDTOK_B200_H
 #define FUSEDTOK_B200_H
@@ -226,17 +229,19 @@ int fusedtok_attention_merge_partials_launch(int dtype, const float* partials, i
 /* ---- KV-length split with direct peer exchange (no counterpart in the
  * reference) ------------------------------------------------------------------
  * The same split as above, but the ranks exchange their raw triples themselves
- * instead of through a collective library: every rank owns an exchange buffer
+ * instead of through a collective library, inside the ONE kernel a step
+ * launches per rank: every rank owns an exchange buffer
  * (fusedtok_exchange_alloc), exports it (fusedtok_exchange_export: a 64-byte
  * CUDA IPC handle to hand to the other processes by any means) and maps its
- * peers' buffers (fusedtok_exchange_open). One call then runs two kernels on
- * `stream`: the split-KV kernel stores this rank's triple block into EVERY
- * rank's buffer with plain stores over NVLink, and a merge kernel raises this
- * rank's "landed" flag on every peer, waits - bounded, on local memory - for
- * the n flags of the step and folds the n blocks into `out` on every rank.
- * `buffers` is a HOST array of n device pointers, entry `rank` being the rank's
- * own buffer. All ranks must make the same sequence of calls with the same
- * shapes. The step number lives in the buffer, so a captured CUDA graph can be
+ * peers' buffers (fusedtok_exchange_open). The split-KV kernel stores the rows
+ * of every (sequence, kv head) unit it finishes into EVERY rank's buffer with
+ * plain stores over NVLink and raises a per-unit flag there; at its end each
+ * CTA waits - bounded, polling its own rank's memory only - for the n flags of
+ * its share of the rows and folds the n blocks into `out` (every rank gets the
+ * whole output). `buffers` is a HOST array of n distinct device pointers, entry
+ * `rank` being the rank's own buffer, which must be memory of the current
+ * device. All ranks must make the same sequence of calls with the same shapes.
+ * The step number lives in the buffer, so a captured CUDA graph can be
  * replayed. A peer that never delivers makes the wait expire after 2 s: the
  * call's output is then invalid, fusedtok_attention_device_status reports 5,
  * the context stays usable. */
@@ -253,21 +258,25 @@ int fusedtok_attention_decode_exchange_launch(int dtype, const void* q, const vo
                                               uintptr_t stream);
 
 /* ---- allocation-free launcher (no counterpart in the reference, whose split
- * path always owns a cudaMalloc'ed workspace) -------------------------------
- * For hosts that must not allocate device memory after start-up (a server that
- * gave its whole budget to its own pool, a process under an allocator-policing
- * shim, a latency-critical loop that cannot take cudaMalloc's implicit sync).
+ * path always allocates its workspace with cudaMalloc) -------------------------
+ * For callers that may not allocate device memory once they are running (a
+ * server that pre-budgets all of HBM into its own pool, a host under an
+ * allocator-policing shim, a latency-critical loop that cannot take
+ * cudaMalloc's implicit sync).
  * Same inputs, outputs and results as fusedtok_attention_decode_launch{,_bf16,
- * _fp16} (dtype 0 float32, 1 bfloat16, 2 float16), but the split-KV scratch is
- * a fixed 4 MiB array inside the library image, held by every GPU that loads
- * the library until the process exits. Calls no cudaMalloc / cudaFree and no
- * allocating library routine. Shapes whose scratch would exceed 4 MiB
- * (64 KiB of counters + (batch*kv_heads*chunks + CTAs) * heads_per_chunk *
- * (dim + 2) floats), or with more than 16384 (sequence, kv head, chunk) units,
- * are rejected with FUSEDTOK_INVALID_ARGUMENT. The first call
- * on a device looks up the array's device address and sets kernel attributes:
- * make it before any stream capture. All calls on a device share the array;
- * calls that overlap on the GPU race on it. */
+ * _fp16} (dtype 0 float32, 1 bfloat16, 2 float16) - same kernel, same split -
+ * but the split-KV scratch is a fixed 4 MiB array inside the library image,
+ * held by every GPU that loads the library until the process exits. Calls no
+ * cudaMalloc / cudaFree and no allocating library routine. Shapes whose scratch
+ * would exceed 4 MiB (256 B header + 64 KiB of counters + slots *
+ * heads_per_chunk * (dim + 2) floats, slots = units + ranges of the launch), or
+ * with more than 16383 (sequence, kv head, chunk) units, are rejected with
+ * FUSEDTOK_INVALID_ARGUMENT. The first call on a device looks up the array's
+ * device address and sets kernel attributes: make it before any stream capture
+ * (a first call that arrives during a capture fails with
+ * FUSEDTOK_RUNTIME_ERROR). All calls on a device share the array; calls that
+ * overlap on the GPU race on it. Its header holds this path's status word,
+ * which fusedtok_attention_device_status reports and clears. */
 int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const void* k, const void* v,
                                              const int* lens, void* out, int batch, int q_heads,
                                              int kv_heads, int cache_rows, int dim, uintptr_t stream);
@@ -276,12 +285,23 @@ int fusedtok_attention_decode_launch_noalloc(int dtype, const void* q, const voi
  * Every device-side wait in the kernels is bounded; a wait that expires stores
  * a non-zero code in a per-device status word and the kernel still completes.
  * This call synchronises the current device, returns the word through
- * `status` (0 = ok) and clears it. */
+ * `status` (0 = ok) and clears it. It covers both the workspace the allocating
+ * launchers own and the static scratch of the allocation-free launcher (the
+ * first non-zero of the two is returned); after a non-zero word the arrival
+ * counters of that path are cleared too, so the next launch starts clean. */
 int fusedtok_attention_device_status(int* status);
 
 /* Number of kernels this library has launched on this thread since the last
  * call with reset != 0 (benchmark bookkeeping). */
 long long fusedtok_attention_launch_count(int reset);
+
+/* Test hook for the status path (no GPU fault involved): with the device idle,
+ * writes `code` (>= 0) into the status word of the allocating path (which == 0)
+ * or of the allocation-free path (which == 1) and, when counter_index >= 0,
+ * sets that arrival counter to 1 - the state a launch that gave up would leave.
+ * With code < 0 it instead returns 100 + the current value of that counter.
+ * Fails if the chosen path has not run on the current device yet. */
+int fusedtok_debug_poke_status(int which, int code, int counter_index);
 
 #ifdef __cplusplus
 }

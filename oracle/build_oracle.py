@@ -12,6 +12,11 @@ benchmark's CPU-baseline leg - never by the shipped package:
   its GPU launchers (timed beside ours). Only built when a reference checkout
   is present; the prebuilt file travels with the repository snapshot.
 
+The reference checkout is found through the environment variable
+``FUSEDTOK_REFERENCE_DIR`` or, when that is unset, as a directory named
+``reference`` beside this repository. ``python oracle/build_oracle.py --ref``
+fails with a message if neither exists.
+
 Run ``python oracle/build_oracle.py`` (``--force`` rebuilds).
 """
 
@@ -20,7 +25,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_DIR = os.environ.get("FUSEDTOK_REFERENCE_DIR", "/root/reference")
+REF_DIR = os.environ.get("FUSEDTOK_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libfusedtok_ref.so")
 
@@ -70,4 +75,7 @@ def build_ref(force=False):
 if __name__ == "__main__":
     force = "--force" in sys.argv
     print(build_oracle(force))
+    if "--ref" in sys.argv and not reference_present():
+        raise SystemExit("no reference checkout: set FUSEDTOK_REFERENCE_DIR to fusedtok's source tree "
+                         "(looked in %s)" % REF_DIR)
     print(build_ref(force))

@@ -103,3 +103,70 @@ def test_c_abi_status_codes():
     # batch 0 is a no-op
     assert lib.fusedtok_attention_decode_launch(1, 1, 1, None, 1, 0, 4, 2, 8, 32, 0) == 0
     assert _fusedtok.attention_partial_floats(3, 5, 8) == 32 + 3 * 5 * 8
+
+
+def test_misaligned_operands_are_refused_before_any_launch():
+    """Operands must be aligned to 4 elements; a view that starts at an odd element offset is an invalid
+    argument, not a device fault. Dummy pointers: the check precedes every CUDA call."""
+    from fusedtok_b200 import _fusedtok
+    lib = _fusedtok._lib
+    ok = 4096
+    for bad in ((ok + 2, ok, ok, ok), (ok, ok + 4, ok, ok), (ok, ok, ok + 6, ok), (ok, ok, ok, ok + 2)):
+        q, k, v, out = bad
+        rc = lib.fusedtok_attention_decode_launch_bf16(q, k, v, None, out, 1, 4, 2, 8, 32, 0)
+        assert rc == 1 and b"aligned" in lib.fusedtok_last_error()
+    rc = lib.fusedtok_attention_decode_launch(ok + 8, ok, ok, None, ok, 1, 4, 2, 8, 32, 0)      # float32: 16 bytes
+    assert rc == 1 and b"aligned" in lib.fusedtok_last_error()
+    rc = lib.fusedtok_attention_decode_paged_launch_fp16(ok, ok + 4, ok, ok, None, ok, 1, 4, 2, 16, 4, 32, 0)
+    assert rc == 1 and b"aligned" in lib.fusedtok_last_error()
+    rc = lib.fusedtok_kv_append_launch_bf16(ok + 4, ok, ok, ok, ok, 1, 2, 32, 8, 0)
+    assert rc == 1 and b"aligned" in lib.fusedtok_last_error()
+    rc = lib.fusedtok_attention_decode_partial_launch(1, ok, ok + 2, ok, None, ok, 1, 4, 2, 8, 32, 0)
+    assert rc == 1 and b"aligned" in lib.fusedtok_last_error()
+
+
+def test_exchange_launch_argument_checks():
+    from fusedtok_b200 import _fusedtok
+    lib = _fusedtok._lib
+    two = (ctypes.c_void_p * 2)(4096, 8192)
+    same = (ctypes.c_void_p * 2)(4096, 4096)
+    hole = (ctypes.c_void_p * 2)(4096, None)
+    args = (1, 4, 2, 64, 32, 0)
+    assert lib.fusedtok_attention_decode_exchange_launch(1, 256, 256, 256, None, 256, two, 2, 2, *args) == 1
+    assert lib.fusedtok_attention_decode_exchange_launch(1, 256, 256, 256, None, 256, two, 17, 0, *args) == 1
+    assert lib.fusedtok_attention_decode_exchange_launch(1, 256, 256, 256, None, 256, hole, 2, 0, *args) == 1
+    assert lib.fusedtok_attention_decode_exchange_launch(1, 256, 256, 256, None, 256, same, 2, 0, *args) == 1
+    assert b"distinct" in lib.fusedtok_last_error()
+    assert lib.fusedtok_attention_decode_exchange_launch(1, 256, 256, 256, None, 256, two, 2, 0, 1, 5, 2, 64, 32, 0) == 1
+    assert lib.fusedtok_attention_decode_exchange_launch(9, 256, 256, 256, None, 256, two, 2, 0, *args) == 1
+
+
+def test_host_route_is_validated_before_it_is_refused():
+    import fusedtok_b200 as ft
+    k = np.zeros((1, 2, 4, 8), np.float32)
+    with pytest.raises(ValueError):                                  # 3 query heads over 2 kv heads
+        ft.attention_decode(np.zeros((1, 3, 8), np.float32), k, k.copy())
+    with pytest.raises(ValueError, match="head counts"):
+        ft.attention_decode(np.zeros((2, 0, 4), np.float32), np.zeros((2, 1, 8, 4), np.float32),
+                            np.zeros((2, 1, 8, 4), np.float32))
+    with pytest.raises(ValueError):                                  # paged group of 3
+        ft.attention_decode_paged(np.zeros((1, 6, 8), np.float32), np.zeros((4, 2, 2, 8), np.float32),
+                                  np.zeros((4, 2, 2, 8), np.float32), np.zeros((1, 2), np.int32))
+    with pytest.raises(TypeError):                                   # non-integral lens
+        ft.attention_decode(np.zeros((1, 4, 8), np.float32), k, k.copy(), [1.5])
+    with pytest.raises(ValueError):                                  # lens beyond the cache
+        ft.attention_decode(np.zeros((1, 4, 8), np.float32), k, k.copy(), [5])
+    with pytest.raises(ft.NoHostPathError):
+        ft.attention_decode(np.zeros((1, 4, 8), np.float32), k, k.copy(), [4])
+    kc = np.zeros((1, 2, 8, 4), np.float32)
+    kn = np.zeros((1, 2, 4), np.float32)
+    with pytest.raises(ValueError):                                  # same size, other shape
+        ft.kv_append(kc, np.zeros((1, 2, 4, 8), np.float32), kn, np.zeros((1, 2, 8), np.float32), [0])
+    with pytest.raises(TypeError):
+        ft.kv_append(kc, kc.copy(), kn, kn.copy(), [1.5])
+    with pytest.raises(ValueError):                                  # the append bound is exclusive
+        ft.kv_append(kc, kc.copy(), kn, kn.copy(), [8])
+    assert ft.kv_append(np.zeros((0, 2, 8, 4), np.float32), np.zeros((0, 2, 8, 4), np.float32),
+                        np.zeros((0, 2, 4), np.float32), np.zeros((0, 2, 4), np.float32), []) is None
+    with pytest.raises(ft.NoHostPathError):
+        ft.kv_append(kc, kc.copy(), kn, kn.copy(), [3])

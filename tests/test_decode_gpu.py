@@ -225,13 +225,115 @@ def test_half_other_tensor_core_head_dims(dt, tol, d, hq, hkv):
 
 
 @pytest.mark.parametrize("dt,tol", HALF)
-def test_half_other_dims_take_generic_kernel(dt, tol):
+def test_half_small_tensor_core_head_dims_short_cache(dt, tol):
     rng = np.random.default_rng(7)
     for d in (32, 96, 256):
         q, k, v, lens = cases.make_case(rng, 2, 8, 2, 300, d, True)
         qt, kt, vt, (qr, kr, vr) = half_case(dt, q, k, v)
         y = ft.attention_decode(qt, kt, vt, torch.from_numpy(lens).cuda()).float().cpu().numpy()
         assert np.abs(y - oracle.decode(qr, kr, vr, lens)).max() <= tol
+
+
+@pytest.mark.parametrize("dt,tol", HALF)
+@pytest.mark.parametrize("d", [4, 8, 16, 48, 144, 512])
+@pytest.mark.parametrize("group", [1, 4, 5, 8])
+def test_half_cuda_core_kernel_head_dims(dt, tol, d, group):
+    """16-bit caches whose head dim the tensor-core kernel is not built for run on the CUDA-core kernel: every
+    chunks-per-lane variant (dims up to 128, 256, 512) x heads-per-unit variant (group 1, 4, 5 -> 8 or 4 + 1, 8),
+    contiguous cache, ragged lengths that cross tile boundaries and include an empty sequence."""
+    hkv = 2
+    rng = np.random.default_rng(d * 31 + group)
+    b, t = 4, 600
+    q, k, v, lens = cases.make_case(rng, b, hkv * group, hkv, t, d, True)
+    lens[:] = [t, 0, 65, 333]
+    qt, kt, vt, (qr, kr, vr) = half_case(dt, q, k, v)
+    out = ft.attention_decode(qt, kt, vt, torch.from_numpy(lens).cuda())
+    y = out.float().cpu().numpy()
+    ref = oracle.decode(qr, kr, vr, lens)
+    assert np.abs(y - ref).max() <= tol
+    assert mean_rel(y, ref) <= 1e-2
+    assert np.all(y[1] == 0)
+    # and a cache long enough that units are split over CTAs and merged
+    q, k, v, _ = cases.make_case(rng, 1, hkv * group, hkv, 3000, d, False)
+    qt, kt, vt, (qr, kr, vr) = half_case(dt, q, k, v)
+    y = ft.attention_decode(qt, kt, vt).float().cpu().numpy()
+    assert np.abs(y - oracle.decode(qr, kr, vr)).max() <= tol
+    assert_status_ok()
+
+
+@pytest.mark.parametrize("dt,tol", HALF)
+def test_half_unaligned_cache_falls_back_to_cuda_core_kernel(dt, tol):
+    """A D=128 cache that starts 8 bytes into its allocation cannot be described to TMA (16-byte rule): the
+    launcher must route it to the CUDA-core kernel, whose 8-byte copies it satisfies, and the result must match
+    the aligned call closely (other kernel, other summation order)."""
+    rng = np.random.default_rng(88)
+    b, hq, hkv, t, d = 2, 16, 4, 900, 128
+    q, k, v, lens = cases.make_case(rng, b, hq, hkv, t, d, True)
+    lens[0] = t
+    qt, kt, vt, (qr, kr, vr) = half_case(dt, q, k, v)
+    lt = torch.from_numpy(lens).cuda()
+
+    def shifted(x):
+        raw = torch.empty(x.numel() + 8, dtype=x.dtype, device="cuda")
+        view = raw[4:4 + x.numel()].view(x.shape)
+        view.copy_(x)
+        assert view.data_ptr() % 16 == 8 and view.is_contiguous()
+        return view
+
+    ks, vs = shifted(kt), shifted(vt)
+    y = ft.attention_decode(qt, ks, vs, lt).float().cpu().numpy()
+    ref = oracle.decode(qr, kr, vr, lens)
+    assert np.abs(y - ref).max() <= tol
+    aligned = ft.attention_decode(qt, kt, vt, lt).float().cpu().numpy()
+    assert np.abs(y - aligned).max() <= tol
+    # two elements in is not aligned to 4 elements: refused, nothing launched
+    raw = torch.empty(kt.numel() + 8, dtype=dt, device="cuda")
+    bad = raw[2:2 + kt.numel()].view(kt.shape)
+    with pytest.raises(ValueError):
+        ft.attention_decode(qt, bad, vt, lt)
+    assert_status_ok()
+
+
+# ---- the range scheduler --------------------------------------------------------
+
+@pytest.mark.parametrize("dt,tol", HALF)
+def test_dynamic_tail_with_ragged_lens_matches_oracle_and_repeats(dt, tol):
+    """Large enough for the static + dynamic-tail plan (more than 24 tiles per SM) with lengths that put range
+    boundaries inside units, empty sequences and a one-row sequence. Which SM computes a tail range changes from
+    launch to launch; the output must not."""
+    rng = np.random.default_rng(4242)
+    b, hq, hkv, t, d = 24, 32, 8, 2048, 128
+    q, k, v, lens = cases.make_case(rng, b, hq, hkv, t, d, True)
+    lens[:6] = [t, 0, 1, 64, 65, 0]
+    qt, kt, vt, (qr, kr, vr) = half_case(dt, q, k, v)
+    lt = torch.from_numpy(lens).cuda()
+    first = ft.attention_decode(qt, kt, vt, lt)
+    y = first.float().cpu().numpy()
+    ref = oracle.decode(qr, kr, vr, lens)
+    assert np.abs(y - ref).max() <= tol
+    assert mean_rel(y, ref) <= 1e-2
+    assert np.all(y[1] == 0) and np.all(y[5] == 0)
+    for _ in range(20):
+        assert torch.equal(ft.attention_decode(qt, kt, vt, lt), first)
+    assert_status_ok()
+
+
+def test_more_sequences_than_the_schedule_table_holds():
+    """Over 2048 sequences with lens: the per-sequence prefix table does not fit, the kernel finds its range with
+    the block-wide scan and keeps the equal split."""
+    rng = np.random.default_rng(9)
+    b, hq, hkv, t, d = 2500, 4, 2, 96, 64
+    q, k, v, lens = cases.make_case(rng, b, hq, hkv, t, d, True)
+    lens[:4] = [t, 0, 1, 65]
+    qt, kt, vt, (qr, kr, vr) = half_case(torch.bfloat16, q, k, v)
+    lt = torch.from_numpy(lens).cuda()
+    out = ft.attention_decode(qt, kt, vt, lt)
+    y = out.float().cpu().numpy()
+    ref = oracle.decode(qr, kr, vr, lens)
+    assert np.abs(y - ref).max() <= 2e-2
+    assert np.all(y[1] == 0)
+    assert torch.equal(ft.attention_decode(qt, kt, vt, lt), out)
+    assert_status_ok()
 
 
 @pytest.mark.parametrize("dt,tol", HALF)
@@ -438,8 +540,8 @@ def test_partial_triples_merge_to_full_result(dt, code, tol):
 @pytest.mark.gpu
 def test_missing_peer_expires_with_a_status_and_the_context_stays_usable():
     """Failure detection without a fault: a KV-split step whose peer never delivers. The second exchange buffer
-    here belongs to no rank, so nothing ever raises this rank's flag for it; the merge kernel's wait (2 s limit)
-    must run out, report status 5 and return, and the next ordinary call must work."""
+    here belongs to no rank, so nothing ever raises that rank's flags in this rank's buffer; the wait at the end of
+    the kernel (2 s limit) must run out, report status 5 and return, and the next ordinary call must work."""
     import time
     b, hq, hkv, d, t = 2, 8, 2, 64, 128
     g = torch.Generator().manual_seed(11)

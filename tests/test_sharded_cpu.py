@@ -116,3 +116,72 @@ def test_kv_length_split_over_two_gloo_ranks(tmp_path):
     out_path = str(tmp_path / "merged.npy")
     mp.spawn(_rank_main, args=(2, port, out_path), nprocs=2, join=True)
     assert os.path.exists(out_path)
+
+
+# ---- host-side failure handling of the split decoders: every mistake is caught before any launch ----------
+
+def _disagreeing_rank(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        notes = []
+        # ranks that were given different shapes: both learn of it, as a ValueError, in the constructor
+        try:
+            sharded._SplitBase(3 + rank, 8, 2, 32, torch.float32, "cpu", None, None)
+            notes.append("no error")
+        except ValueError as exc:
+            notes.append("shape:" + ("disagree" in str(exc) and "ok" or str(exc)))
+        # ... and ranks that were given different dtypes
+        try:
+            sharded._SplitBase(3, 8, 2, 32, torch.float32 if rank == 0 else torch.float16, "cpu", None, None)
+            notes.append("no error")
+        except ValueError as exc:
+            notes.append("dtype:" + ("disagree" in str(exc) and "ok" or str(exc)))
+        # a decoder built for another number of ranks than the group has
+        try:
+            sharded._SplitBase(3, 8, 2, 32, torch.float32, "cpu", None, world + 1)
+            notes.append("no error")
+        except ValueError as exc:
+            notes.append("world:" + ("process group has" in str(exc) and "ok" or str(exc)))
+        # agreement passes when the ranks do agree; per-call checks are local
+        base = sharded._SplitBase(3, 8, 2, 32, torch.float32, "cpu", None, world)
+        q = torch.zeros(3, 8, 32)
+        k = torch.zeros(3, 2, 64, 32)
+        assert base._check_call(q, k, k.clone(), None, torch.empty_like(q)) == 64
+        assert base._check_call(q, k, k.clone(), torch.zeros(3, dtype=torch.int32), torch.empty_like(q)) == 64
+        bad_calls = [
+            (TypeError, (q.half(), k, k.clone(), None, torch.empty_like(q))),                  # dtype
+            (ValueError, (q[:2], k, k.clone(), None, torch.empty_like(q[:2]))),                # batch
+            (ValueError, (q, k[:, :1], k[:, :1].clone(), None, torch.empty_like(q))),          # kv heads
+            (ValueError, (q, k, k[:, :, :32].clone(), None, torch.empty_like(q))),             # v rows
+            (ValueError, (q, k.transpose(1, 2), k.clone(), None, torch.empty_like(q))),        # not contiguous
+            (ValueError, (q, k, k.clone(), torch.zeros(3, dtype=torch.int64), torch.empty_like(q))),   # lens type
+            (ValueError, (q, k, k.clone(), torch.zeros(2, dtype=torch.int32), torch.empty_like(q))),   # lens size
+            (TypeError, (q.numpy(), k, k.clone(), None, torch.empty_like(q))),                 # not a tensor
+        ]
+        for kind, args in bad_calls:
+            with pytest.raises(kind):
+                base._check_call(*args)
+        notes.append("calls:ok")
+        # ranks that would run different numbers of cache rows
+        try:
+            sharded.agree_across_ranks(dist, None, "cache rows per rank", 64 + rank)
+            notes.append("no error")
+        except ValueError as exc:
+            notes.append("rows:" + ("cache rows" in str(exc) and "ok" or str(exc)))
+        open(os.path.join(out_dir, "notes%d" % rank), "w").write(",".join(notes))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_split_decoders_refuse_inconsistent_ranks_before_any_launch(tmp_path):
+    """Two gloo ranks on CPU: shape, dtype and rank-count disagreement and every per-call mistake raise on the
+    host (no GPU, no fault, nothing launched)."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_disagreeing_rank, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        notes = open(str(tmp_path / ("notes%d" % r))).read()
+        assert notes == "shape:ok,dtype:ok,world:ok,calls:ok,rows:ok", notes
