@@ -483,9 +483,6 @@ def run_ours(args, w, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
-        # NCCL_DEBUG is left as the caller set it; whatever NCCL logs goes to a file so that stdout stays one JSON line
-        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-        os.environ.setdefault("NCCL_DEBUG_FILE", os.path.join(ROOT, "gpurun_out", "nccl_debug.%h.%p.log"))
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", device_id=device)
@@ -1093,6 +1090,11 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1 or args.gpus > 1:
+        # NCCL_DEBUG is left as the caller set it; whatever NCCL logs goes to a file (set before NCCL is
+        # loaded) so that stdout stays one JSON line
+        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+        os.environ.setdefault("NCCL_DEBUG_FILE", os.path.join(ROOT, "gpurun_out", "nccl_debug.%h.%p.log"))
     if args.workload == "refrows":
         if rank == 0:
             run_reference_rows(args)

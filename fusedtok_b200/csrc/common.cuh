@@ -98,7 +98,7 @@ constexpr int MAX_PEERS = 16;
 // Where destination j of a raw triple block lives. Exchange buffers are double-buffered by the
 // parity of the step number, so a rank that runs one step ahead never overwrites a block its
 // peer is still merging.
-__device__ __forceinline__ float* triple_block(const struct DecodeParams& p, int j);
+__device__ __forceinline__ float* triple_block(const struct DecodeParams& p, int j, unsigned int step);
 
 // ---- storage types ---------------------------------------------------------
 template <typename T> struct Store;
@@ -152,10 +152,21 @@ template <> struct Store<__half> {
     }
 };
 
-__device__ __forceinline__ float* triple_block(const DecodeParams& p, int j) {
+// acc * r_old + x * r_new with the rounding spelled out (one rounded product, one fused multiply-add),
+// so that every place that folds partials - inside a kernel, across kernels, across GPUs - produces the
+// same bits whatever the compiler would otherwise choose to contract.
+__device__ __forceinline__ float lse_fold(float acc, float r_old, float x, float r_new) {
+    return fmaf(acc, r_old, __fmul_rn(x, r_new));
+}
+
+// Step number of this launch of a peer-exchange kernel (0 otherwise). Read once per thread, right after
+// the dependency wait, from L2 (the word changes between launches, so no read-only cache).
+__device__ __forceinline__ unsigned int peer_step(const DecodeParams& p) {
+    return p.n_peers ? __ldcg(p.peer_epoch) + 1u : 0u;
+}
+__device__ __forceinline__ float* triple_block(const DecodeParams& p, int j, unsigned int step) {
     if (!p.n_peers) return p.triple_ml;
-    const unsigned int parity = (__ldcg(p.peer_epoch) + 1u) & 1u;   // L2: the word changes between launches
-    return p.peer_blocks[j] + ((size_t)parity * p.n_peers + p.peer_rank) * (size_t)p.peer_nf;
+    return p.peer_blocks[j] + ((size_t)(step & 1u) * p.n_peers + p.peer_rank) * (size_t)p.peer_nf;
 }
 
 // ---- scheduler -------------------------------------------------------------
@@ -294,53 +305,54 @@ __device__ __forceinline__ long long block_sum(long long v, long long* red) {
 // ---- direct peer exchange (KV-length split) -----------------------------------
 // Exchange buffer of one rank (allocated by the library, mapped into every peer
 // through CUDA IPC): a header of 32-bit words - [0] steps completed (epoch),
-// [1] count of warps that have finished the current step, and from word
-// XCHG_FLAG_WORD on one flag per (unit, rank): "rank's rows of this unit have
-// landed for step <value>" - then, from byte xchg_data_off(rows) on, the triple
-// blocks gather[2][n][nf], double-buffered by step parity.
-constexpr int XCHG_FLAG_WORD = 16;
+// [1] count of warps that have finished the current step - and, from byte
+// XCHG_DATA_BYTES on, the blocks gather[2][n][nf], double-buffered by step
+// parity. A block carries one rank's raw triples with the step number riding
+// beside every value: per (sequence, query head) row one 16-byte word
+// {m, step, l, step}, then per row D/2 words {acc[d], step, acc[d+1], step}.
+// Every 8-byte half is written by one store and validates itself, so the
+// reader needs no separate flag and the writer no fence: it polls the data
+// until the step number in it is the current one.
+constexpr int XCHG_DATA_BYTES = 1024;
 constexpr unsigned long long XCHG_WAIT_NS = 2000000000ull;      // bounded wait: 2 s
-__host__ __device__ __forceinline__ size_t xchg_data_off(long long rows, int n) {
-    // at most one unit per (sequence, query head) row
-    return (((size_t)XCHG_FLAG_WORD + (size_t)rows * n) * 4 + 1023) & ~(size_t)1023;
+// floats per block and offset of its acc part
+__host__ __device__ __forceinline__ size_t xchg_acc_off(long long rows) { return (size_t)rows * 4; }
+__host__ __device__ __forceinline__ size_t xchg_block_floats(long long rows, int dim) {
+    return (size_t)rows * 4 + (size_t)rows * dim * 2;
 }
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+// 16-byte load that bypasses L1 (the words are written by other GPUs)
+__device__ __forceinline__ uint4 ld_peer16(const float* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// One thread, after every thread of the CTA that wrote rows of `unit` has executed
-// __threadfence_system() and the CTA has synchronised: tell every rank that this rank's rows of
-// the unit are in its buffer for the current step.
-__device__ __forceinline__ void peer_signal_unit(const DecodeParams& p, long long unit) {
-    const unsigned int e = __ldcg(p.peer_epoch) + 1u;
-    for (int j = 0; j < p.n_peers; ++j)
-        st_release_sys(p.peer_hdr[j] + XCHG_FLAG_WORD + (size_t)unit * p.n_peers + p.peer_rank, e);
 }
 
 // Zero row for an empty sequence (len == 0): the reference's convention
 // (src/attention.cu:211-216). One thread writes the whole [Hq, D] row.
 template <typename T>
-__device__ void zero_rows(const DecodeParams& p, int b) {
-    if (p.triple_ml) {
-        const int nd = p.n_peers ? p.n_peers : 1;
-        for (int j = 0; j < nd; ++j) {
-            float* blk = triple_block(p, j);
+__device__ void zero_rows(const DecodeParams& p, int b, unsigned int step) {
+    if (p.n_peers) {
+        const float e = __uint_as_float(step);
+        for (int j = 0; j < p.n_peers; ++j) {
+            float* blk = triple_block(p, j, step);
             for (int h = 0; h < p.Hq; ++h) {
                 const size_t r = (size_t)b * p.Hq + h;
-                blk[r * 2] = -INFINITY;
-                blk[r * 2 + 1] = 0.0f;
-                for (int d = 0; d < p.D; d += 4)
-                    *reinterpret_cast<float4*>(blk + p.triple_acc_off + r * p.D + d) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(blk + r * 4) = make_float4(-INFINITY, e, 0.0f, e);
+                for (int d = 0; d < p.D; d += 2)
+                    *reinterpret_cast<float4*>(blk + p.triple_acc_off + (r * p.D + d) * 2) = make_float4(0.f, e, 0.f, e);
             }
         }
-        if (p.n_peers) {
-            __threadfence_system();
-            const int upb = p.Hkv * p.NCH;
-            for (int u = 0; u < upb; ++u) peer_signal_unit(p, (long long)b * upb + u);
+        return;
+    }
+    if (p.triple_ml) {
+        float* blk = p.triple_ml;
+        for (int h = 0; h < p.Hq; ++h) {
+            const size_t r = (size_t)b * p.Hq + h;
+            blk[r * 2] = -INFINITY;
+            blk[r * 2 + 1] = 0.0f;
+            for (int d = 0; d < p.D; d += 4)
+                *reinterpret_cast<float4*>(blk + p.triple_acc_off + r * p.D + d) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
         return;
     }
@@ -354,7 +366,7 @@ __device__ void zero_rows(const DecodeParams& p, int b) {
 // an empty range. Also writes the zero rows of empty sequences (sequence b is
 // handled by the CTA with b % ncta == blockIdx.x).
 template <typename T>
-__device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w) {
+__device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w, unsigned int step) {
     const int upb = p.Hkv * p.NCH;
     const int c = blockIdx.x;
     long long total_nt;
@@ -365,7 +377,7 @@ __device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w) {
         for (int b = threadIdx.x; b < p.B; b += blockDim.x) {
             const int len = seq_len(p, b);
             loc += tiles_of(len);
-            if (len == 0 && (b % p.ncta) == c) zero_rows<T>(p, b);
+            if (len == 0 && (b % p.ncta) == c) zero_rows<T>(p, b, step);
         }
         total_nt = block_sum(loc, sh->red);
     }
@@ -433,7 +445,7 @@ __device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w) {
 // locate any range (walker_locate). Also writes the zero rows of empty sequences, like sched_init.
 // Returns the number of tiles of the launch.
 template <typename T>
-__device__ long long sched_prefix(const DecodeParams& p, SchedShared* sh, unsigned int* prefix) {
+__device__ long long sched_prefix(const DecodeParams& p, SchedShared* sh, unsigned int* prefix, unsigned int step) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nwarp = (blockDim.x + 31) >> 5;
     unsigned int running = 0;
@@ -443,7 +455,7 @@ __device__ long long sched_prefix(const DecodeParams& p, SchedShared* sh, unsign
         if (b < p.B) {
             const int len = seq_len(p, b);
             v = (unsigned int)tiles_of(len);
-            if (len == 0 && (b % p.ncta) == (int)blockIdx.x) zero_rows<T>(p, b);
+            if (len == 0 && (b % p.ncta) == (int)blockIdx.x) zero_rows<T>(p, b, step);
         }
         unsigned int inc = v;
 #pragma unroll
@@ -560,17 +572,24 @@ __device__ __forceinline__ SegDest seg_dest(const DecodeParams& p, const Plan& p
 // Final store of two adjacent elements (d, d+1) of head h of sequence b:
 // normalised output in the storage type, or the raw triple for the
 // multi-GPU layer.
-template <typename T>
-__device__ __forceinline__ void emit_final2(const DecodeParams& p, int b, int h, int d, float m_nat,
-                                            float l, float a0, float a1, bool write_ml) {
+// PEERS = false compiles the peer-exchange destination out (kernels that are short of registers have a
+// variant of their own for the KV-length split).
+template <typename T, bool PEERS = true>
+__device__ __forceinline__ void emit_final2(const DecodeParams& p, unsigned int step, int b, int h, int d,
+                                            float m_nat, float l, float a0, float a1, bool write_ml) {
     const size_t r = (size_t)b * p.Hq + h;
-    if (p.triple_ml) {
-        const int nd = p.n_peers ? p.n_peers : 1;
-        for (int j = 0; j < nd; ++j) {
-            float* blk = triple_block(p, j);
-            *reinterpret_cast<float2*>(blk + p.triple_acc_off + r * p.D + d) = make_float2(a0, a1);
-            if (write_ml) *reinterpret_cast<float2*>(blk + r * 2) = make_float2(m_nat, l);
+    if (PEERS && p.n_peers) {
+        // one 16-byte word per element pair, the step number beside each value, into every rank's buffer
+        const float e = __uint_as_float(step);
+        for (int j = 0; j < p.n_peers; ++j) {
+            float* blk = triple_block(p, j, step);
+            *reinterpret_cast<float4*>(blk + p.triple_acc_off + (r * p.D + d) * 2) = make_float4(a0, e, a1, e);
+            if (write_ml) *reinterpret_cast<float4*>(blk + r * 4) = make_float4(m_nat, e, l, e);
         }
+    } else if (p.triple_ml) {
+        float* blk = p.triple_ml;
+        *reinterpret_cast<float2*>(blk + p.triple_acc_off + r * p.D + d) = make_float2(a0, a1);
+        if (write_ml) *reinterpret_cast<float2*>(blk + r * 2) = make_float2(m_nat, l);
     } else {
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         Store<T>::st2(reinterpret_cast<T*>(p.out) + r * p.D + d, a0 * inv, a1 * inv);
@@ -582,9 +601,9 @@ __device__ __forceinline__ void emit_final2(const DecodeParams& p, int b, int h,
 // The reference's rule (attn_reduce_kernel, src/attention.cu:503-548):
 // partials with l <= 0 are skipped, the first live one is adopted verbatim,
 // later ones are max-rescaled, then the row is divided by l.
-template <typename T>
-__device__ __forceinline__ void merge_unit(const DecodeParams& p, const Plan& pl, const SegDest& d, int tid,
-                                           int nthreads) {
+template <typename T, bool PEERS = true>
+__device__ __forceinline__ void merge_unit(const DecodeParams& p, const Plan& pl, const SegDest& d, unsigned int step,
+                                           int tid, int nthreads) {
     constexpr int BATCH = 8;                      // slots fetched together: one L2 round trip per batch
     const int D = p.D, halfd = D >> 1;
     const bool sparse = !pl.per && pl.ncta > pl.total;
@@ -613,13 +632,13 @@ __device__ __forceinline__ void merge_unit(const DecodeParams& p, const Plan& pl
                 }
                 const float m_new = fmaxf(m, ml[j].x);
                 const float r_old = expf(m - m_new), r_new = expf(ml[j].x - m_new);
-                l = l * r_old + ml[j].y * r_new;
-                a0 = a0 * r_old + x[j].x * r_new;
-                a1 = a1 * r_old + x[j].y * r_new;
+                l = lse_fold(l, r_old, ml[j].y, r_new);
+                a0 = lse_fold(a0, r_old, x[j].x, r_new);
+                a1 = lse_fold(a1, r_old, x[j].y, r_new);
                 m = m_new;
             }
         }
-        emit_final2<T>(p, d.b, d.h0 + g, dd, m, l, a0, a1, dd == 0);
+        emit_final2<T, PEERS>(p, step, d.b, d.h0 + g, dd, m, l, a0, a1, dd == 0);
     }
 }
 
@@ -634,83 +653,145 @@ __device__ __forceinline__ bool deliver_partial(const DecodeParams& p, const Seg
 }
 
 // End of a KV-length-split step with direct peer exchange: the warps of the grid share the
-// (sequence, query head) rows; for each of its rows a warp waits - bounded, polling its OWN
-// rank's memory - until all n ranks have flagged the row's unit for this step, then folds the n
-// blocks with the reference's merge rule (src/attention.cu:503-548) and stores the normalised
-// row. `gwarp` of `nwarps` identifies the warp among all participating warps of the grid; every
-// one of them must call this exactly once per launch (the last one advances the step number).
-// Nothing here is waited for by any other rank: flags are raised before any rank starts
+// (sequence, query head) rows; for each of its rows a warp reads the n ranks' words of the row from
+// its OWN rank's buffer, polling - bounded - until the step number in them is the current one, folds
+// the n triples with the reference's merge rule (src/attention.cu:503-548) and stores the normalised
+// row. `gwarp` of `nwarps` identifies the warp among all participating warps of the grid; every one
+// of them must call this exactly once per launch (the last one advances the step number). Nothing
+// here is waited for by any other rank: a rank stores its rows as it finishes them, before it starts
 // waiting, so the waits cannot form a cycle.
+// What peer_fold needs, by value: it is deliberately not inlined (it runs once, at the very end of a
+// kernel, and must not cost the streaming loop any registers), and a reference to the kernel's parameter
+// block would force a copy of the whole block onto the stack.
+struct PeerFoldArgs {
+    const float* parts;      // this rank's gather blocks of the current step parity: [n][nf]
+    unsigned int* hdr;       // this rank's exchange-buffer header
+    int* status;
+    void* out;
+    long long rows, nf;
+    size_t acc_off;
+    int D, n;
+};
+__device__ __forceinline__ PeerFoldArgs peer_fold_args(const DecodeParams& p, unsigned int step) {
+    PeerFoldArgs a;
+    a.parts = p.peer_blocks[p.peer_rank] + (size_t)(step & 1u) * p.n_peers * (size_t)p.peer_nf;
+    a.hdr = p.peer_hdr[p.peer_rank];
+    a.status = p.status;
+    a.out = p.out;
+    a.rows = (long long)p.B * p.Hq;
+    a.nf = p.peer_nf;
+    a.acc_off = p.triple_acc_off;
+    a.D = p.D;
+    a.n = p.n_peers;
+    return a;
+}
+
 template <typename T>
-__device__ void peer_fold(const DecodeParams& p, int gwarp, int nwarps) {
+__device__ __noinline__ void peer_fold(const PeerFoldArgs p, unsigned int step, int gwarp, int nwarps) {
+    constexpr int RB = 4;                                     // ranks whose words are in flight together
     const int lane = threadIdx.x & 31;
-    unsigned int* mine = p.peer_hdr[p.peer_rank];
-    const unsigned int e = __ldcg(p.peer_epoch) + 1u;         // this step
-    const unsigned int parity = e & 1u;
-    const long long rows = (long long)p.B * p.Hq;
-    const int D = p.D, chunks = D >> 2, n = p.n_peers;
-    const float* parts = p.peer_blocks[p.peer_rank] + (size_t)parity * n * (size_t)p.peer_nf;
+    unsigned int* mine = p.hdr;
+    const unsigned int e = step;
+    const long long rows = p.rows;
+    const int D = p.D, chunks = D >> 2, n = p.n;
+    const float* parts = p.parts;
     T* out = reinterpret_cast<T*>(p.out);
     bool ok = true;
-    for (long long r = gwarp; r < rows && ok; r += nwarps) {
-        const int b = (int)(r / p.Hq), h = (int)(r % p.Hq);
-        const int kv = h / p.G, ch = (h % p.G) / p.GC;
-        const long long unit = ((long long)b * p.Hkv + kv) * p.NCH + ch;
-        // lane j watches rank j's flag
-        if (lane < n) {
-            const unsigned int* f = mine + XCHG_FLAG_WORD + (size_t)unit * n + lane;
-            if ((int)(ld_acquire_sys(f) - e) < 0) {
-                unsigned long long t0, t1;
-                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-                for (unsigned int it = 1; (int)(ld_acquire_sys(f) - e) < 0; ++it) {
-                    if ((it & 63u) == 0) {
-                        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-                        if (t1 - t0 > XCHG_WAIT_NS) {     // a peer never delivered: give up, report, stay usable
-                            atomicCAS(p.status, ST_OK, ST_PEER_TIMEOUT);
-                            ok = false;
-                            break;
+    unsigned long long t0 = 0;
+    // true once both 8-byte halves of a word {x, step, y, step} carry this step
+    auto ready = [&](const uint4& v) { return v.y == e && v.w == e; };
+    // give up after XCHG_WAIT_NS of polling in this call (a peer never delivered): report, stay usable
+    auto expired = [&]() {
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t0 == 0) t0 = t1;
+        if (t1 - t0 > XCHG_WAIT_NS) {
+            atomicCAS(p.status, ST_OK, ST_PEER_TIMEOUT);
+            ok = false;
+        }
+        return !ok;
+    };
+    for (long long r = gwarp; r < rows; r += nwarps) {
+        float m = -INFINITY, l = 0.0f;
+        float4 o[4];                                          // head dim <= 512: at most 4 chunks per lane
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < n && ok; s0 += RB) {
+            // the (m, l) words of up to RB ranks, all requested before any is looked at
+            uint4 wml[RB];
+#pragma unroll
+            for (int q = 0; q < RB; ++q)
+                if (s0 + q < n) wml[q] = ld_peer16(parts + (size_t)(s0 + q) * (size_t)p.nf + (size_t)r * 4);
+#pragma unroll
+            for (int q = 0; q < RB; ++q)
+                if (s0 + q < n)
+                    for (unsigned int it = 1; !ready(wml[q]); ++it) {
+                        if ((it & 63u) == 0 && expired()) break;
+                        wml[q] = ld_peer16(parts + (size_t)(s0 + q) * (size_t)p.nf + (size_t)r * 4);
+                    }
+            // rescale factors of these ranks in order (the reference's rule: skip l <= 0, adopt the first)
+            float r_old[RB], r_new[RB];
+            bool adopt[RB], live[RB];
+#pragma unroll
+            for (int q = 0; q < RB; ++q) {
+                r_old[q] = 1.0f; r_new[q] = 0.0f; adopt[q] = false; live[q] = false;
+                if (s0 + q < n) {
+                    const float mq = __uint_as_float(wml[q].x), lq = __uint_as_float(wml[q].z);
+                    if (lq > 0.0f) {
+                        live[q] = true;
+                        if (l == 0.0f) {
+                            adopt[q] = true;
+                            m = mq;
+                            l = lq;
+                        } else {
+                            const float m_new = fmaxf(m, mq);
+                            r_old[q] = expf(m - m_new);
+                            r_new[q] = expf(mq - m_new);
+                            l = lse_fold(l, r_old[q], lq, r_new[q]);
+                            m = m_new;
                         }
                     }
                 }
             }
-        }
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        float4 o[4];                                          // head dim <= 512: at most 4 chunks per lane
-#pragma unroll
-        for (int j = 0; j < 4; ++j) o[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-        float m = -INFINITY, l = 0.0f;
-        for (int s = 0; s < n; ++s) {
-            const float* base = parts + (size_t)s * (size_t)p.peer_nf;
-            const float2 ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)r * 2));
-            if (ml.y <= 0.0f) continue;
-            const float* a = base + p.triple_acc_off + (size_t)r * D;
-            if (l == 0.0f) {
-                m = ml.x;
-                l = ml.y;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int cc = lane + 32 * j;
-                    if (cc < chunks) o[j] = __ldcg(reinterpret_cast<const float4*>(a + cc * 4));
-                }
-                continue;
-            }
-            const float m_new = fmaxf(m, ml.x);
-            const float r_old = expf(m - m_new), r_new = expf(ml.x - m_new);
-            l = l * r_old + ml.y * r_new;
+            // the acc words, one chunk (4 elements = two words) of all RB ranks at a time
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int cc = lane + 32 * j;
-                if (cc < chunks) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(a + cc * 4));
-                    o[j].x = o[j].x * r_old + v.x * r_new;
-                    o[j].y = o[j].y * r_old + v.y * r_new;
-                    o[j].z = o[j].z * r_old + v.z * r_new;
-                    o[j].w = o[j].w * r_old + v.w * r_new;
-                }
+                if (cc >= chunks) continue;
+                uint4 lo[RB], hi[RB];
+#pragma unroll
+                for (int q = 0; q < RB; ++q)
+                    if (s0 + q < n) {
+                        const float* a = parts + (size_t)(s0 + q) * (size_t)p.nf + p.acc_off +
+                                         ((size_t)r * D + (size_t)cc * 4) * 2;
+                        lo[q] = ld_peer16(a);
+                        hi[q] = ld_peer16(a + 4);
+                    }
+#pragma unroll
+                for (int q = 0; q < RB; ++q)
+                    if (s0 + q < n) {
+                        const float* a = parts + (size_t)(s0 + q) * (size_t)p.nf + p.acc_off +
+                                         ((size_t)r * D + (size_t)cc * 4) * 2;
+                        for (unsigned int it = 1; !(ready(lo[q]) && ready(hi[q])); ++it) {
+                            if ((it & 63u) == 0 && expired()) break;
+                            lo[q] = ld_peer16(a);
+                            hi[q] = ld_peer16(a + 4);
+                        }
+                        if (!live[q]) continue;
+                        const float4 x = make_float4(__uint_as_float(lo[q].x), __uint_as_float(lo[q].z),
+                                                     __uint_as_float(hi[q].x), __uint_as_float(hi[q].z));
+                        if (adopt[q]) {
+                            o[j] = x;
+                        } else {
+                            o[j].x = lse_fold(o[j].x, r_old[q], x.x, r_new[q]);
+                            o[j].y = lse_fold(o[j].y, r_old[q], x.y, r_new[q]);
+                            o[j].z = lse_fold(o[j].z, r_old[q], x.z, r_new[q]);
+                            o[j].w = lse_fold(o[j].w, r_old[q], x.w, r_new[q]);
+                        }
+                    }
             }
-            m = m_new;
         }
+        if (!__all_sync(0xffffffffu, ok)) break;              // the row is incomplete: leave it unwritten
         T* orow = out + (size_t)r * D;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {

@@ -114,8 +114,9 @@ __device__ __forceinline__ float lane_transpose_reduce(float (&v)[N], int lane) 
 }
 
 // GC: query heads per unit (1, 2, 4, 8); LC: 4-element chunks per lane
-// (head dim <= 128 * LC).
-template <typename T, int GC, int LC>
+// (head dim <= 128 * LC); PEERS: the KV-length split with direct peer exchange (its end-of-kernel fold is
+// compiled into a variant of its own so that the ordinary kernel carries none of it).
+template <typename T, int GC, int LC, bool PEERS>
 __global__ void __launch_bounds__(SIMT_THREADS)
 decode_simt_kernel(const DecodeParams p) {
     constexpr int R = (LC == 1) ? 4 : (LC == 2 ? 2 : 1);
@@ -133,20 +134,23 @@ decode_simt_kernel(const DecodeParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     Walker w;
     bool have_work;                             // block-uniform
+    // (the step number of a KV-length split with peer exchange is re-read where it is needed - at segment
+    // ends and at the very end - rather than carried in a register through the streaming loop)
     if (!p.lens) {
-        have_work = sched_init<T>(p, &sh, w);
+        have_work = sched_init<T>(p, &sh, w, 0u);
         asm volatile("griddepcontrol.wait;" ::: "memory");
     } else {
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        have_work = sched_init<T>(p, &sh, w);   // reads lens
+        have_work = sched_init<T>(p, &sh, w, PEERS ? peer_step(p) : 0u);   // reads lens
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (!have_work) {
-        if (p.n_peers) peer_fold<T>(p, (int)blockIdx.x * SIMT_WARPS + warp, p.ncta * SIMT_WARPS);
+        if constexpr (PEERS) {
+            const unsigned int step = peer_step(p);
+            peer_fold<T>(peer_fold_args(p, step), step, (int)blockIdx.x * SIMT_WARPS + warp, p.ncta * SIMT_WARPS);
+        }
         return;
     }
-    const Plan pl = make_plan(sh.total, p.ncta, 0, 0);     // this kernel always runs the equal split: one range per CTA
-    const int r = (int)blockIdx.x;
     const int D = p.D;
     const int chunks = D >> 2;
     const T* kbase = reinterpret_cast<const T*>(p.k);
@@ -296,7 +300,10 @@ decode_simt_kernel(const DecodeParams p) {
 
         const bool seg_end = (w.ti == w.nt - 1) || (w.g + 1 == w.end);
         if (seg_end) {
-            const SegDest dst = seg_dest(p, pl, w, r, seg_first);
+            // this kernel always runs the equal split: one range per CTA
+            const Plan pl = make_plan(sh.total, p.ncta, 0, 0);
+            const unsigned int step = PEERS ? peer_step(p) : 0u;
+            const SegDest dst = seg_dest(p, pl, w, (int)blockIdx.x, seg_first);
             __syncthreads();                                  // scratch free
 #pragma unroll
             for (int g = 0; g < GC; ++g) {
@@ -339,14 +346,13 @@ decode_simt_kernel(const DecodeParams p) {
                 }
                 const float2 ml = s_glob[g];
                 if (dst.whole) {
-                    emit_final2<T>(p, dst.b, dst.h0 + g, d, ml.x, ml.y, a0, a1, d == 0);
+                    emit_final2<T, PEERS>(p, step, dst.b, dst.h0 + g, d, ml.x, ml.y, a0, a1, d == 0);
                 } else {
                     const size_t pr = dst.slot * p.GC + g;
                     *reinterpret_cast<float2*>(p.ws_acc + pr * D + d) = make_float2(a0, a1);
                     if (d == 0) *reinterpret_cast<float2*>(p.ws_ml + pr * 2) = ml;
                 }
             }
-            bool unit_done = dst.whole;
             if (!dst.whole) {
                 // publish the partial; the CTA that publishes a unit's last one merges it
                 __threadfence();
@@ -355,21 +361,17 @@ decode_simt_kernel(const DecodeParams p) {
                 __syncthreads();
                 if (s_last) {
                     __threadfence();
-                    merge_unit<T>(p, pl, dst, threadIdx.x, SIMT_THREADS);
-                    unit_done = true;
+                    merge_unit<T, PEERS>(p, pl, dst, step, threadIdx.x, SIMT_THREADS);
                 }
-            }
-            if (p.n_peers && unit_done) {
-                // the unit's rows are in every rank's exchange buffer: order them before the flags
-                __threadfence_system();
-                __syncthreads();
-                if (threadIdx.x == 0) peer_signal_unit(p, dst.unit);
             }
         }
         walker_advance(p, w);
     }
     // KV-length split: fold this CTA's share of the rows over the n ranks (every warp of the grid takes part)
-    if (p.n_peers) peer_fold<T>(p, (int)blockIdx.x * SIMT_WARPS + warp, p.ncta * SIMT_WARPS);
+    if constexpr (PEERS) {
+        const unsigned int step = peer_step(p);
+        peer_fold<T>(peer_fold_args(p, step), step, (int)blockIdx.x * SIMT_WARPS + warp, p.ncta * SIMT_WARPS);
+    }
 }
 
 }  // namespace ftk

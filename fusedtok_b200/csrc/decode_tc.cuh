@@ -32,8 +32,9 @@
 //    round trip is hidden) and announces to the consumers through a small
 //    ring of range descriptors in shared memory.
 //  * KV-length split across GPUs: finished units are stored into every rank's
-//    exchange buffer and flagged; at its end the CTA folds its share of the
-//    rows over the n ranks (peer_fold) - one launch per step and rank.
+//    exchange buffer, the step number riding beside every value; at its end
+//    the CTA folds its share of the rows over the n ranks (peer_fold) - one
+//    launch per step and rank, no fence and no flag on the way.
 //
 // Every wait on an mbarrier is bounded (wall-clock limit); on expiry the
 // kernel records a status code, stops waiting and still runs to completion,
@@ -242,7 +243,7 @@ __device__ __forceinline__ float ex2(float x) {
 // 0 entry, 1 dependency wait done, 2 schedule done, 3 first tile landed, 4 producer issued its last
 // copy, 5 last tile consumed, 6 exit, 7 ns spent at segment ends (sum), 8 segment ends, 9 ns spent
 // waiting for tiles (sum), 10 ns in the final publish, 11 ranges processed, 12 ns waiting for range
-// descriptors (sum).
+// descriptors (sum), 13 the SM the CTA ran on, 14 units merged by this CTA.
 #ifdef FTK_TIMELINE
 __device__ unsigned long long g_timeline[1024][16];
 #define FTK_STAMP(cond, slot) do { if (cond) g_timeline[blockIdx.x][slot] = global_ns(); } while (0)
@@ -276,6 +277,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     if (threadIdx.x == 0) {
         for (int i = 0; i < 16; ++i) g_timeline[blockIdx.x][i] = 0;
         g_timeline[blockIdx.x][0] = global_ns();
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_timeline[blockIdx.x][13] = smid;
     }
 #endif
 
@@ -307,22 +311,25 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     Walker w0;                                  // equal-split range of this CTA (more sequences than the table holds)
     bool have0 = false, by_scan = false;
     long long total;
+    unsigned int step = 0;                      // step number of a KV-length split with peer exchange
     if (!p.lens) {
         // every sequence has p.T rows: the schedule is arithmetic on kernel parameters and
         // belongs to the part that may overlap the previous kernel
         total = (long long)p.B * tiles_of(p.T) * upb;
         asm volatile("griddepcontrol.wait;" ::: "memory");
         FTK_STAMP(threadIdx.x == 0, 1);
+        step = peer_step(p);
     } else {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         FTK_STAMP(threadIdx.x == 0, 1);
+        step = peer_step(p);
         if (p.sched_table) {
             unsigned int* table = reinterpret_cast<unsigned int*>(smem + Cfg::OFF_PREFIX);
-            total = sched_prefix<T>(p, sh, table);              // reads lens
+            total = sched_prefix<T>(p, sh, table, step);              // reads lens
             prefix = table;
         } else {
             by_scan = true;                                     // the host disables the dynamic tail for these
-            have0 = sched_init<T>(p, sh, w0);
+            have0 = sched_init<T>(p, sh, w0, step);
             total = sh->total;
         }
     }
@@ -388,11 +395,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             bool announce = true;
             new_unit = true;
             prepare();
+            // Ask for the range after this one right away: the answer is only needed once this whole range
+            // has been issued, so the atomic's round trip (microseconds under full memory load) never holds
+            // up a copy. A CTA thus always has one dynamic range in reserve.
             int taken = 0;
+            if (pl.per && lane == 0) taken = atomicAdd(next_tail, 1);
             while (w.g < w.end) {
-                // ask for the next tail range while this range's last tile goes out: the answer is
-                // only needed after the copies below have been issued
-                if (pl.per && w.g + 1 == w.end && lane == 0) taken = atomicAdd(next_tail, 1);
                 if (!mbar_wait(bar_empty + s * 8, ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY_TIMEOUT)) {
                     gave_up = true;
                     break;
@@ -646,7 +654,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 
     for (int nd = 0;; ++nd) {
         // ---- next range of this CTA, as announced by the producer
-        const unsigned long long tl_d0 = FTK_NOW();
+        [[maybe_unused]] const unsigned long long tl_d0 = FTK_NOW();
         const bool got = mbar_wait(bar_desc + (nd % QD) * 8, (uint32_t)((nd / QD) & 1), abort_flag, p.status,
                                    ST_WAIT_RANGE_TIMEOUT);
         if (consumers_any(!got)) break;               // the same decision in every consumer warp
@@ -685,7 +693,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         }
         // ---- this group's tiles of the segment
         for (; own < i0 + n; own += 2) {
-            const unsigned long long tl_w0 = FTK_NOW();
+            [[maybe_unused]] const unsigned long long tl_w0 = FTK_NOW();
             const bool ok = mbar_wait(bar_full + s * 8, ph, abort_flag, p.status, ST_WAIT_FULL_TIMEOUT);
             FTK_ADD(tc == 0, 9, FTK_NOW() - tl_w0);
 #ifdef FTK_TIMELINE
@@ -707,7 +715,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         w.ti += n - 1;
         {
             // ---- fold the 8 warp states and emit
-            const unsigned long long tl_s0 = FTK_NOW();
+            [[maybe_unused]] const unsigned long long tl_s0 = FTK_NOW();
             FTK_STAMP(tc == 0, 5);
             const SegDest dst = seg_dest(p, pl, w, r, seg_first);
 #pragma unroll
@@ -764,7 +772,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     }
                     const float2 ml = make_float2(mg * p.scale, lg);   // m from raw score units to natural-log units
                     if (dst.whole) {
-                        emit_final2<T>(p, dst.b, dst.h0 + g, d, ml.x, ml.y, a0, a1, d == 0);
+                        emit_final2<T>(p, step, dst.b, dst.h0 + g, d, ml.x, ml.y, a0, a1, d == 0);
                     } else {
                         const size_t pr = dst.slot * p.GC + g;
                         *reinterpret_cast<float2*>(p.ws_acc + pr * D + d) = make_float2(a0, a1);
@@ -772,7 +780,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     }
                 }
             }
-            bool merged = false;
             if (have_pend) {
                 // was that the unit's last partial? then this CTA merges the unit
                 if (tc == 0) {
@@ -783,17 +790,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 bar_consumers();
                 if (*s_last) {
                     __threadfence();
-                    merge_unit<T>(p, pl, pend, tc, NCW * 32);
-                    merged = true;
-                }
-            }
-            if (p.n_peers && (merged || dst.whole)) {
-                // a unit's rows are in every rank's exchange buffer: order them before the flags
-                __threadfence_system();
-                bar_consumers();
-                if (tc == 0) {
-                    if (merged) peer_signal_unit(p, pend.unit);
-                    if (dst.whole) peer_signal_unit(p, dst.unit);
+                    merge_unit<T>(p, pl, pend, step, tc, NCW * 32);
+                    FTK_ADD(tc == 0, 14, 1);
                 }
             }
             have_pend = !dst.whole;
@@ -804,7 +802,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         walker_advance(p, w);
     }
     }
-    const unsigned long long tl_f0 = FTK_NOW();
+    [[maybe_unused]] const unsigned long long tl_f0 = FTK_NOW();
     if (have_pend) {
         // the last partial of this CTA: publish it now; the CTA that publishes a unit's last one merges it
         __threadfence();
@@ -813,17 +811,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         bar_consumers();
         if (*s_last) {
             __threadfence();
-            merge_unit<T>(p, pl, pend, tc, NCW * 32);
-            if (p.n_peers) {
-                __threadfence_system();
-                bar_consumers();
-                if (tc == 0) peer_signal_unit(p, pend.unit);
-            }
+            merge_unit<T>(p, pl, pend, step, tc, NCW * 32);
+            FTK_ADD(tc == 0, 14, 1);
         }
     }
     FTK_ADD(tc == 0, 10, FTK_NOW() - tl_f0);
     // KV-length split: fold this CTA's share of the rows over the n ranks (every consumer warp of the grid takes part)
-    if (p.n_peers) peer_fold<T>(p, (int)blockIdx.x * NCW + warp, p.ncta * NCW);
+    if (p.n_peers) peer_fold<T>(peer_fold_args(p, step), step, (int)blockIdx.x * NCW + warp, p.ncta * NCW);
     FTK_STAMP(tc == 0, 6);
 }
 

@@ -115,17 +115,16 @@ int set_all_smem_attrs() {
     FTK_SET_ALL(__half)
 #undef FTK_SET_ALL
 #undef FTK_SET
-#define FTK_SET_SIMT(T)                                                                             \
-    if ((rc = set_smem(decode_simt_kernel<T, 1, 1>, SIMT_STAGE_BYTES))) return rc;                  \
-    if ((rc = set_smem(decode_simt_kernel<T, 4, 1>, SIMT_STAGE_BYTES))) return rc;                  \
-    if ((rc = set_smem(decode_simt_kernel<T, 8, 1>, SIMT_STAGE_BYTES))) return rc;                  \
-    if ((rc = set_smem(decode_simt_kernel<T, 1, 2>, SIMT_STAGE_BYTES))) return rc;                  \
-    if ((rc = set_smem(decode_simt_kernel<T, 4, 2>, SIMT_STAGE_BYTES))) return rc;                  \
-    if ((rc = set_smem(decode_simt_kernel<T, 1, 4>, SIMT_STAGE_BYTES))) return rc;                  \
-    if ((rc = set_smem(decode_simt_kernel<T, 2, 4>, SIMT_STAGE_BYTES))) return rc;
+#define FTK_SET_SIMT1(T, GC, LC)                                                                      \
+    if ((rc = set_smem(decode_simt_kernel<T, GC, LC, false>, SIMT_STAGE_BYTES))) return rc;           \
+    if ((rc = set_smem(decode_simt_kernel<T, GC, LC, true>, SIMT_STAGE_BYTES))) return rc;
+#define FTK_SET_SIMT(T)                                                                               \
+    FTK_SET_SIMT1(T, 1, 1) FTK_SET_SIMT1(T, 4, 1) FTK_SET_SIMT1(T, 8, 1) FTK_SET_SIMT1(T, 1, 2)       \
+    FTK_SET_SIMT1(T, 4, 2) FTK_SET_SIMT1(T, 1, 4) FTK_SET_SIMT1(T, 2, 4)
     FTK_SET_SIMT(float)
     FTK_SET_SIMT(__nv_bfloat16)
     FTK_SET_SIMT(__half)
+#undef FTK_SET_SIMT1
 #undef FTK_SET_SIMT
     return rc;
 }
@@ -335,7 +334,11 @@ template <typename T> void launch_simt_t(const DecodeParams& p, int lc, cudaStre
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-#define FTK_GO(GC, LC) cudaLaunchKernelEx(&cfg, decode_simt_kernel<T, GC, LC>, p)
+#define FTK_GO(GC, LC)                                                                 \
+    do {                                                                               \
+        if (p.n_peers) cudaLaunchKernelEx(&cfg, decode_simt_kernel<T, GC, LC, true>, p); \
+        else cudaLaunchKernelEx(&cfg, decode_simt_kernel<T, GC, LC, false>, p);        \
+    } while (0)
     if (lc == 1) { if (p.GC == 1) FTK_GO(1, 1); else if (p.GC == 4) FTK_GO(4, 1); else FTK_GO(8, 1); }
     else if (lc == 2) { if (p.GC == 1) FTK_GO(1, 2); else FTK_GO(4, 2); }
     else { if (p.GC == 1) FTK_GO(1, 4); else FTK_GO(2, 4); }
@@ -486,11 +489,11 @@ int decode_launch(const DecodePlan& pl, const Scratch& sc, int dt, const void* q
     if (peers) {
         p.n_peers = peers->n;
         p.peer_rank = peers->rank;
-        p.peer_nf = (long long)p.triple_acc_off + out_rows * dim;
-        const size_t data_off = xchg_data_off(out_rows, peers->n);
+        p.triple_acc_off = xchg_acc_off(out_rows);
+        p.peer_nf = (long long)xchg_block_floats(out_rows, dim);
         for (int j = 0; j < peers->n; ++j) {
             p.peer_hdr[j] = static_cast<unsigned int*>(peers->bases[j]);
-            p.peer_blocks[j] = reinterpret_cast<float*>(static_cast<unsigned char*>(peers->bases[j]) + data_off);
+            p.peer_blocks[j] = reinterpret_cast<float*>(static_cast<unsigned char*>(peers->bases[j]) + XCHG_DATA_BYTES);
         }
         p.peer_epoch = p.peer_hdr[peers->rank];
         p.triple_ml = p.peer_blocks[peers->rank];     // non-null: "emit raw triples"
@@ -1187,9 +1190,8 @@ int fusedtok_attention_merge_partials_launch(int dtype, const float* partials, i
 int fusedtok_exchange_alloc(int n_ranks, int batch, int q_heads, int dim, void** buffer, long long* bytes) {
     if (!buffer || n_ranks < 1 || n_ranks > ftk::MAX_PEERS || batch < 0 || q_heads < 1 || dim < 1)
         return fail(FUSEDTOK_INVALID_ARGUMENT, "exchange buffer: 1..16 ranks, batch>=0, heads>=1, dim>=1");
-    const long long nf = fusedtok_attention_partial_floats(batch, q_heads, dim);
-    const size_t total = ftk::xchg_data_off((long long)batch * q_heads, n_ranks) +
-                         (size_t)2 * n_ranks * (size_t)nf * sizeof(float);
+    const size_t nf = ftk::xchg_block_floats((long long)batch * q_heads, dim);
+    const size_t total = ftk::XCHG_DATA_BYTES + (size_t)2 * n_ranks * nf * sizeof(float);
     void* mem = nullptr;
     cudaError_t e = cudaMalloc(&mem, total);
     if (e != cudaSuccess) return cuda_fail("exchange buffer allocation failed", e);

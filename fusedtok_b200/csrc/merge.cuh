@@ -45,16 +45,16 @@ merge_parts_kernel(const float* __restrict__ parts, int n, T* __restrict__ out, 
         }
         const float m_new = fmaxf(m, ml.x);
         const float r_old = expf(m - m_new), r_new = expf(ml.x - m_new);
-        l = l * r_old + ml.y * r_new;
+        l = lse_fold(l, r_old, ml.y, r_new);
 #pragma unroll
         for (int j = 0; j < MAX_LANE_CHUNKS; ++j) {
             const int cc = lane + 32 * j;
             if (cc < chunks) {
                 const float4 x = *reinterpret_cast<const float4*>(a + cc * 4);
-                o[j].x = o[j].x * r_old + x.x * r_new;
-                o[j].y = o[j].y * r_old + x.y * r_new;
-                o[j].z = o[j].z * r_old + x.z * r_new;
-                o[j].w = o[j].w * r_old + x.w * r_new;
+                o[j].x = lse_fold(o[j].x, r_old, x.x, r_new);
+                o[j].y = lse_fold(o[j].y, r_old, x.y, r_new);
+                o[j].z = lse_fold(o[j].z, r_old, x.z, r_new);
+                o[j].w = lse_fold(o[j].w, r_old, x.w, r_new);
             }
         }
         m = m_new;

@@ -235,9 +235,11 @@ int fusedtok_attention_merge_partials_launch(int dtype, const float* partials, i
  * CUDA IPC handle to hand to the other processes by any means) and maps its
  * peers' buffers (fusedtok_exchange_open). The split-KV kernel stores the rows
  * of every (sequence, kv head) unit it finishes into EVERY rank's buffer with
- * plain stores over NVLink and raises a per-unit flag there; at its end each
- * CTA waits - bounded, polling its own rank's memory only - for the n flags of
- * its share of the rows and folds the n blocks into `out` (every rank gets the
+ * plain stores over NVLink, the step number riding beside every value (each
+ * 8-byte half validates itself: no fence, no separate flag); at its end each
+ * CTA reads the n ranks' words of its share of the rows from its own rank's
+ * memory - polling, bounded, until they carry the current step - and folds the
+ * n blocks into `out` (every rank gets the
  * whole output). `buffers` is a HOST array of n distinct device pointers, entry
  * `rank` being the rank's own buffer, which must be memory of the current
  * device. All ranks must make the same sequence of calls with the same shapes.
