@@ -84,6 +84,8 @@ struct DecodeParams {
     int dyn_chunk;        // tiles per tail range of the static + dynamic plan; 0 = equal split only
     int dyn_tail_max;     // most tiles per CTA that go to the dynamic tail
     int sched_table;      // lens given and the per-sequence tile prefix sums fit the kernel's table
+    int cost_split;       // cut the ranges at equal cost (tiles + unit ends) instead of equal tile counts
+    int cost_a, cost_b;   // ... a tile counts cost_a, a unit end cost_b
     float scale;          // 1/sqrt(D)
 };
 
@@ -210,6 +212,16 @@ struct Plan {
     int ndyn;            // dynamic ranges in all: ncta * nd + those of the leftover
     int R;               // ranges (equal split: one per CTA, some possibly empty)
     int ncta;
+    // Cost-weighted equal split (tensor-core kernel): a unit of nt tiles counts ka * nt + kb (nt + 1 unless
+    // overridden) - every unit that ENDS inside a range costs its CTA a fold and a fresh set of query fragments,
+    // about one tile's worth of streaming (measured: 1 : 1 and 2 : 3 do best on ragged batches, 2 : 1 and 1 : 2
+    // within 0.5 % of them) - and the ranges are cut at equal cost instead of equal tile counts, so that a CTA
+    // whose range is full of short sequences is given fewer tiles. ctot == 0: off.
+    long long ctot;                 // cost of the whole launch
+    const unsigned int* pre;        // per sequence: tiles before it (units of one kv head); null without lens
+    const unsigned int* zpre;       // per sequence: non-empty sequences before it; null without lens
+    int upb, nt_uniform;            // units per sequence; tiles per unit when every sequence has p.T rows
+    int ka, kb;                     // cost of a tile and of a unit end
 };
 
 // dyn_chunk == 0: equal split. Otherwise a block keeps all but min(per / 6, dyn_tail_max) of its
@@ -226,6 +238,11 @@ __device__ __forceinline__ Plan make_plan(long long total, int ncta, int dyn_chu
     pl.ndyn = 0;
     pl.R = ncta;
     pl.ncta = ncta;
+    pl.ctot = 0;
+    pl.pre = pl.zpre = nullptr;
+    pl.upb = pl.nt_uniform = 0;
+    pl.ka = 1;
+    pl.kb = 1;
     if (dyn_chunk > 0) {
         const long long per = qdiv(total, ncta);
         if (per >= DYN_MIN_PER && per < (1ll << 30)) {
@@ -269,8 +286,33 @@ __device__ __forceinline__ int range_of(const Plan& pl, long long x) {
     return pl.nstat + (int)qdiv(x - blocks_end, pl.chunk);
 }
 __device__ __forceinline__ bool range_empty(const Plan& pl, int r) {
-    return !pl.per && qdiv(pl.total * r, pl.ncta) == qdiv(pl.total * (r + 1), pl.ncta);
+    return !pl.per && !pl.ctot && qdiv(pl.total * r, pl.ncta) == qdiv(pl.total * (r + 1), pl.ncta);
 }
+// ---- cost-weighted equal split
+// Switch it on for a launch of `total_nt` tiles per kv-head unit row and `nonempty` non-empty sequences (only
+// when every range is then certain to hold a tile: at least 4 cost units per range).
+__device__ __forceinline__ void plan_enable_cost(Plan& pl, long long total_nt, long long nonempty, int upb,
+                                                 const unsigned int* pre, const unsigned int* zpre, int nt_uniform,
+                                                 int ka, int kb) {
+    // (tiles sit ka apart in cost, ka + kb across a unit end: ranges of at least ka + kb + 1 always hold a tile)
+    const long long ctot = (ka * total_nt + kb * nonempty) * upb;
+    if (pl.per || ka < 1 || kb < 0 || ctot < (long long)(ka + kb + 1) * pl.ncta) return;
+    pl.ka = ka;
+    pl.kb = kb;
+    pl.ctot = ctot;
+    pl.pre = pre;
+    pl.zpre = zpre;
+    pl.upb = upb;
+    pl.nt_uniform = nt_uniform;
+}
+// cost position of tile 0 of unit (b, ub); nt = tiles of sequence b
+__device__ __forceinline__ long long cost_of_unit(const Plan& pl, int b, int ub, int nt) {
+    const long long pb = pl.pre ? (long long)pl.pre[b] : (long long)b * pl.nt_uniform;
+    const long long zb = pl.zpre ? (long long)pl.zpre[b] : (long long)b;
+    return (pl.ka * pb + pl.kb * zb) * pl.upb + (long long)ub * (pl.ka * nt + pl.kb);
+}
+__device__ __forceinline__ long long cost_start(const Plan& pl, int r) { return qdiv(pl.ctot * r, pl.ncta); }
+__device__ __forceinline__ int cost_owner(const Plan& pl, long long c) { return (int)qdiv((c + 1) * pl.ncta - 1, pl.ctot); }
 // static range of CTA c, and the i-th dynamic range in hand-out order
 __device__ __forceinline__ int static_range(const Plan& pl, int c) { return pl.per ? c * (1 + pl.nd) : c; }
 __device__ __forceinline__ int dyn_range(const Plan& pl, int i) {
@@ -445,10 +487,11 @@ __device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w, un
 // locate any range (walker_locate). Also writes the zero rows of empty sequences, like sched_init.
 // Returns the number of tiles of the launch.
 template <typename T>
-__device__ long long sched_prefix(const DecodeParams& p, SchedShared* sh, unsigned int* prefix, unsigned int step) {
+__device__ long long sched_prefix(const DecodeParams& p, SchedShared* sh, unsigned int* prefix, unsigned int* zprefix,
+                                  unsigned int step) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nwarp = (blockDim.x + 31) >> 5;
-    unsigned int running = 0;
+    unsigned int running = 0, zrunning = 0;
     for (int base = 0; base < p.B; base += blockDim.x) {
         const int b = base + threadIdx.x;
         unsigned int v = 0;
@@ -457,26 +500,34 @@ __device__ long long sched_prefix(const DecodeParams& p, SchedShared* sh, unsign
             v = (unsigned int)tiles_of(len);
             if (len == 0 && (b % p.ncta) == (int)blockIdx.x) zero_rows<T>(p, b, step);
         }
-        unsigned int inc = v;
+        // two scans at once: tiles in the low half of a 64-bit word, non-empty sequences in the high half
+        const unsigned long long both = (unsigned long long)v | ((unsigned long long)(v > 0 ? 1u : 0u) << 32);
+        unsigned long long inc = both;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const unsigned int t = __shfl_up_sync(0xffffffffu, inc, o);
+            const unsigned long long t = __shfl_up_sync(0xffffffffu, inc, o);
             if (lane >= o) inc += t;
         }
         __syncthreads();
-        if (lane == 31) sh->red[warp] = inc;
+        if (lane == 31) sh->red[warp] = (long long)inc;
         __syncthreads();
-        unsigned int before = running, chunk = 0;
+        unsigned long long before = 0, chunk = 0;
         for (int i = 0; i < nwarp; ++i) {
-            const unsigned int t = (unsigned int)sh->red[i];
+            const unsigned long long t = (unsigned long long)sh->red[i];
             if (i < warp) before += t;
             chunk += t;
         }
-        if (b < p.B) prefix[b] = before + inc - v;
-        running += chunk;
+        if (b < p.B) {
+            const unsigned long long excl = before + inc - both;
+            prefix[b] = running + (unsigned int)excl;
+            zprefix[b] = zrunning + (unsigned int)(excl >> 32);
+        }
+        running += (unsigned int)chunk;
+        zrunning += (unsigned int)(chunk >> 32);
     }
     if (threadIdx.x == 0) {
         prefix[p.B] = running;
+        zprefix[p.B] = zrunning;
         sh->total = (long long)running * (p.Hkv * p.NCH);
     }
     __syncthreads();
@@ -513,6 +564,61 @@ __device__ __forceinline__ Walker walker_locate(const DecodeParams& p, const uns
     const long long rem = start - pb * upb;
     w.ub = (int)qdiv(rem, w.nt);
     w.ti = (int)(rem - (long long)w.ub * w.nt);
+    return w;
+}
+
+// Walker at the first tile whose cost position is >= X under the cost-weighted split (one thread); X ==
+// pl.ctot gives the end of the sequence (w.g == pl.total). `end` is stored as the range's end.
+__device__ __forceinline__ Walker walker_locate_cost(const DecodeParams& p, const Plan& pl, long long X, long long end) {
+    Walker w;
+    w.end = end;
+    w.b = 0; w.ub = 0; w.ti = 0; w.nt = 0; w.len = 0;
+    if (X >= pl.ctot) {
+        w.g = pl.total;
+        return w;
+    }
+    const int upb = pl.upb;
+    long long pb, zb;
+    if (!pl.pre) {
+        const long long per_seq = (long long)upb * (pl.ka * pl.nt_uniform + pl.kb);
+        w.b = (int)qdiv(X, per_seq);
+        pb = (long long)w.b * pl.nt_uniform;
+        zb = w.b;
+    } else {
+        int lo = 0, hi = p.B;            // invariant: cost(lo) <= X < cost(hi)
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (((long long)pl.ka * pl.pre[mid] + (long long)pl.kb * pl.zpre[mid]) * upb <= X) lo = mid;
+            else hi = mid;
+        }
+        w.b = lo;
+        pb = pl.pre[lo];
+        zb = pl.zpre[lo];
+    }
+    w.len = seq_len(p, w.b);
+    w.nt = tiles_of(w.len);
+    const long long rem = X - (pl.ka * pb + pl.kb * zb) * upb;
+    const int unit_cost = pl.ka * w.nt + pl.kb;
+    w.ub = (int)qdiv(rem, unit_cost);
+    const int o = (int)(rem - (long long)w.ub * unit_cost);
+    w.ti = (o + pl.ka - 1) / pl.ka;      // first tile at or after the boundary
+    if (w.ti >= w.nt) {                  // the boundary fell behind the unit's last tile: the next unit starts the range
+        w.ti = 0;
+        if (++w.ub >= upb) {
+            w.ub = 0;
+            pb += w.nt;
+            do {
+                ++w.b;
+                w.len = w.b < p.B ? seq_len(p, w.b) : 0;
+                w.nt = tiles_of(w.len);
+            } while (w.nt == 0 && w.b < p.B);
+            if (w.b >= p.B) {
+                w.g = pl.total;
+                return w;
+            }
+        }
+    }
+    w.g = pb * upb + (long long)w.ub * w.nt + w.ti;
     return w;
 }
 
@@ -558,7 +664,12 @@ __device__ __forceinline__ SegDest seg_dest(const DecodeParams& p, const Plan& p
     d.slot = (size_t)r + (size_t)d.unit;
     d.r_first = d.r_last = r;
     d.nparts = 1;
-    if (!d.whole) {
+    if (!d.whole && pl.ctot) {
+        const long long c0 = cost_of_unit(pl, w.b, w.ub, w.nt);
+        d.r_first = cost_owner(pl, c0);
+        d.r_last = cost_owner(pl, c0 + (long long)pl.ka * (w.nt - 1));
+        d.nparts = d.r_last - d.r_first + 1;
+    } else if (!d.whole) {
         d.r_first = range_of(pl, u_start);
         d.r_last = range_of(pl, u_end - 1);
         d.nparts = d.r_last - d.r_first + 1;
@@ -606,7 +717,7 @@ __device__ __forceinline__ void merge_unit(const DecodeParams& p, const Plan& pl
                                            int tid, int nthreads) {
     constexpr int BATCH = 8;                      // slots fetched together: one L2 round trip per batch
     const int D = p.D, halfd = D >> 1;
-    const bool sparse = !pl.per && pl.ncta > pl.total;
+    const bool sparse = !pl.per && !pl.ctot && pl.ncta > pl.total;
     for (int e = tid; e < d.gvalid * halfd; e += nthreads) {
         const int g = e / halfd, dd = (e % halfd) * 2;
         float m = -INFINITY, l = 0.0f, a0 = 0.0f, a1 = 0.0f;

@@ -95,7 +95,8 @@ template <int D> struct TcCfg {
     static constexpr int OFF_DESC = (OFF_ABORT + 16 + 15) & ~15;               // RangeDesc[QD]
     static constexpr int OFF_DBAR = OFF_DESC + QD * (int)sizeof(RangeDesc);    // "descriptor written" barriers
     static constexpr int OFF_PREFIX = OFF_DBAR + QD * 8;                       // tile prefix sums per sequence
-    static constexpr int SMEM_BYTES = OFF_PREFIX + (SCHED_MAX_B + 1) * 4 + 12;
+    static constexpr int OFF_ZPRE = OFF_PREFIX + (SCHED_MAX_B + 1) * 4;          // non-empty sequences before each one
+    static constexpr int SMEM_BYTES = OFF_ZPRE + (SCHED_MAX_B + 1) * 4 + 8;
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
@@ -308,6 +309,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const int upb = p.Hkv * p.NCH;
     const int upb_nch = p.NCH;
     const unsigned int* prefix = nullptr;       // tile prefix sums, when the schedule needs them
+    const unsigned int* zprefix = nullptr;      // ... and the count of non-empty sequences before each one
     Walker w0;                                  // equal-split range of this CTA (more sequences than the table holds)
     bool have0 = false, by_scan = false;
     long long total;
@@ -325,8 +327,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         step = peer_step(p);
         if (p.sched_table) {
             unsigned int* table = reinterpret_cast<unsigned int*>(smem + Cfg::OFF_PREFIX);
-            total = sched_prefix<T>(p, sh, table, step);              // reads lens
+            unsigned int* ztable = reinterpret_cast<unsigned int*>(smem + Cfg::OFF_ZPRE);
+            total = sched_prefix<T>(p, sh, table, ztable, step);      // reads lens
             prefix = table;
+            zprefix = ztable;
         } else {
             by_scan = true;                                     // the host disables the dynamic tail for these
             have0 = sched_init<T>(p, sh, w0, step);
@@ -334,7 +338,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         }
     }
     if (*abort_flag) return;
-    const Plan pl = make_plan(total, p.ncta, by_scan ? 0 : p.dyn_chunk, p.dyn_tail_max);
+    Plan plan = make_plan(total, p.ncta, by_scan ? 0 : p.dyn_chunk, p.dyn_tail_max);
+    if (p.cost_split && !by_scan && total > 0) {
+        if (prefix) plan_enable_cost(plan, prefix[p.B], zprefix[p.B], upb, prefix, zprefix, 0, p.cost_a, p.cost_b);
+        else plan_enable_cost(plan, (long long)p.B * tiles_of(p.T), p.B, upb, nullptr, nullptr, tiles_of(p.T), p.cost_a,
+                              p.cost_b);
+    }
+    const Plan pl = plan;
     FTK_STAMP(threadIdx.x == 0, 2);
 
     if (warp == NCW) {
@@ -389,9 +399,15 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         const int tail_ranges = pl.ndyn;                         // 0 under the equal split
         int* next_tail = p.counters + (size_t)p.B * upb;         // hands out the tail ranges of this launch
         bool more = by_scan ? have0 : (total > 0 && !range_empty(pl, r));
+        if (pl.ctot) {
+            // cost-weighted split: this CTA's range is [first tile at cost >= X_r, first tile at cost >= X_{r+1})
+            const Walker e1 = walker_locate_cost(p, pl, cost_start(pl, r + 1), 0);
+            w0 = walker_locate_cost(p, pl, cost_start(pl, r), e1.g);
+            more = w0.g < w0.end;
+        }
         bool gave_up = false;
         while (more) {
-            w = by_scan ? w0 : walker_locate(p, prefix, range_start(pl, r), range_start(pl, r + 1));
+            w = (by_scan || pl.ctot) ? w0 : walker_locate(p, prefix, range_start(pl, r), range_start(pl, r + 1));
             bool announce = true;
             new_unit = true;
             prepare();

@@ -379,6 +379,20 @@ const int g_env_dyn_chunk = [] {
     const char* e = std::getenv("FUSEDTOK_DYN_CHUNK");
     return e ? std::atoi(e) : -1;
 }();
+// FUSEDTOK_COST_SPLIT=0 cuts the ranges at equal tile counts instead of equal cost (for A/B measurements).
+const bool g_env_cost_split = [] {
+    const char* e = std::getenv("FUSEDTOK_COST_SPLIT");
+    return !(e && e[0] == '0');
+}();
+// FUSEDTOK_COST_A / FUSEDTOK_COST_B: cost of a tile and of a unit end under the cost-weighted split (1 and 1).
+const int g_env_cost_a = [] {
+    const char* e = std::getenv("FUSEDTOK_COST_A");
+    return e ? std::max(1, std::atoi(e)) : 1;
+}();
+const int g_env_cost_b = [] {
+    const char* e = std::getenv("FUSEDTOK_COST_B");
+    return e ? std::max(0, std::atoi(e)) : 1;
+}();
 const int g_env_dyn_tail = [] {
     const char* e = std::getenv("FUSEDTOK_DYN_TAIL");
     return e ? std::atoi(e) : -1;
@@ -504,6 +518,9 @@ int decode_launch(const DecodePlan& pl, const Scratch& sc, int dt, const void* q
     p.GC = pl.GC; p.NCH = pl.NCH; p.ncta = pl.ncta;
     p.box_rows = pl.box_rows; p.box_shift = pl.box_shift;
     p.dyn_chunk = pl.dyn_chunk; p.dyn_tail_max = pl.dyn_tail_max; p.sched_table = pl.sched_table;
+    p.cost_split = (g_env_cost_split && pl.use_tc && !pl.dyn_chunk) ? 1 : 0;
+    p.cost_a = g_env_cost_a;
+    p.cost_b = g_env_cost_b;
     p.ws_ml = sc.ws_ml; p.ws_acc = sc.ws_acc; p.counters = sc.counters; p.status = sc.status;
 
     if (pl.use_tc) {

@@ -572,3 +572,50 @@ def test_missing_peer_expires_with_a_status_and_the_context_stays_usable():
         torch.cuda.synchronize()
         _fusedtok.exchange_free(mine)
         _fusedtok.exchange_free(ghost)
+
+
+_DYN_SCRIPT = r"""
+import sys, os
+import numpy as np, torch
+import cases, oracle
+import fusedtok_b200 as ft
+from fusedtok_b200 import _fusedtok
+rng = np.random.default_rng(4242)
+b, hq, hkv, t, d = 24, 32, 8, 2048, 128
+q, k, v, lens = cases.make_case(rng, b, hq, hkv, t, d, True)
+lens[:6] = [t, 0, 1, 64, 65, 0]
+qt, kt, vt = (torch.from_numpy(x).cuda().to(torch.bfloat16) for x in (q, k, v))
+lt = torch.from_numpy(lens).cuda()
+first = ft.attention_decode(qt, kt, vt, lt)
+for _ in range(30):
+    assert torch.equal(ft.attention_decode(qt, kt, vt, lt), first)
+full = ft.attention_decode(qt, kt, vt)                      # no lens: the schedule is arithmetic
+for _ in range(10):
+    assert torch.equal(ft.attention_decode(qt, kt, vt), full)
+ref = oracle.decode(qt.float().cpu().numpy(), kt.float().cpu().numpy(), vt.float().cpu().numpy(), lens)
+err = float(np.abs(first.float().cpu().numpy() - ref).max())
+assert err <= 2e-2, err
+assert _fusedtok.attention_device_status() == 0
+np.save(sys.argv[1], first.float().cpu().numpy())
+print("ok", err)
+"""
+
+
+def test_dynamic_range_plan_when_enabled(tmp_path):
+    """The static + dynamic plan is off by default (it measured slower) but stays in the library behind
+    FUSEDTOK_DYN_CHUNK. Run it in a process of its own (the switch is read when the library loads): ranges handed
+    out by an atomic counter, partials keyed by range - the result must match the oracle, repeat bit for bit although
+    which SM computes which range changes from launch to launch, and agree with the equal split to rounding."""
+    import subprocess
+    import sys
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    outs = {}
+    for name, env_extra in (("static", {}), ("dynamic", {"FUSEDTOK_DYN_CHUNK": "4", "FUSEDTOK_DYN_TAIL": "16"})):
+        env = dict(os.environ, PYTHONPATH=os.pathsep.join([root, os.path.join(root, "tests")]), **env_extra)
+        path = str(tmp_path / (name + ".npy"))
+        res = subprocess.run([sys.executable, "-c", _DYN_SCRIPT, path], env=env, capture_output=True, text=True,
+                             timeout=600)
+        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+        outs[name] = np.load(path)
+    assert np.abs(outs["static"] - outs["dynamic"]).max() <= 2e-2
