@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include "decode_simt.cuh"
 #include "decode_tc.cuh"
+#include "decode_ring.cuh"
 #include "kv_append.cuh"
 #include "prefill_simt.cuh"
 #include "prefill_tc.cuh"
@@ -125,6 +126,12 @@ int set_all_smem_attrs() {
     FTK_SET_SIMT(__nv_bfloat16)
     FTK_SET_SIMT(__half)
 #undef FTK_SET_SIMT1
+#define FTK_SET_RING(D, GC)                                                                                  \
+    if ((rc = set_smem(decode_ring_f32_kernel<D, GC, false>, RfCfg<D, GC>::SMEM_BYTES))) return rc;          \
+    if ((rc = set_smem(decode_ring_f32_kernel<D, GC, true>, RfCfg<D, GC>::SMEM_BYTES))) return rc;
+    FTK_SET_RING(64, 1) FTK_SET_RING(64, 4) FTK_SET_RING(64, 8)
+    FTK_SET_RING(128, 1) FTK_SET_RING(128, 4) FTK_SET_RING(128, 8)
+#undef FTK_SET_RING
 #undef FTK_SET_SIMT
     return rc;
 }
@@ -286,6 +293,45 @@ int encode_map(CUtensorMap* map, int dt, const void* base, unsigned long long ro
     return FUSEDTOK_OK;
 }
 
+// The float32 cache as a rank-2 tensor (D floats, rows), no swizzle: a box [D, box_rows] lands row-major.
+int encode_map_f32(CUtensorMap* map, const void* base, unsigned long long rows, int dim, int box_rows) {
+    const cuuint64_t gdim[2] = {(cuuint64_t)dim, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)dim * 4};
+    const cuuint32_t box[2] = {(cuuint32_t)dim, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), gdim, gstride, box,
+                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(FUSEDTOK_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed (code " + std::to_string((int)r) + ")");
+    return FUSEDTOK_OK;
+}
+
+template <int D, int GC, bool PG>
+void launch_ring(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, cudaStream_t cs) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p.ncta);
+    cfg.blockDim = dim3(RF_THREADS);
+    cfg.dynamicSmemBytes = RfCfg<D, GC>::SMEM_BYTES;
+    cfg.stream = cs;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, decode_ring_f32_kernel<D, GC, PG>, mk, mv, p);
+}
+void launch_ring_any(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, bool paged, cudaStream_t cs) {
+#define FTK_GO(D, GC)                                          \
+    do {                                                       \
+        if (paged) launch_ring<D, GC, true>(mk, mv, p, cs);    \
+        else launch_ring<D, GC, false>(mk, mv, p, cs);         \
+    } while (0)
+    if (p.D == 64) { if (p.GC == 1) FTK_GO(64, 1); else if (p.GC == 4) FTK_GO(64, 4); else FTK_GO(64, 8); }
+    else { if (p.GC == 1) FTK_GO(128, 1); else if (p.GC == 4) FTK_GO(128, 4); else FTK_GO(128, 8); }
+#undef FTK_GO
+}
+
 template <typename T, int D, int GP, bool PG>
 void launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, cudaStream_t cs) {
     // launched with programmatic stream serialization: the kernel's prologue may overlap the tail
@@ -351,7 +397,7 @@ template <typename T> void launch_simt_t(const DecodeParams& p, int lc, cudaStre
 // ranges, and the layout of the split-KV scratch. Both the allocating launchers and the
 // allocation-free one launch from the same plan, so they run the same kernel on the same split.
 struct DecodePlan {
-    bool use_tc = false, paged = false;
+    bool use_tc = false, use_ring = false, paged = false;
     int GC = 1, NCH = 1, lc = 1, gp = 8;
     int ncta = 1;
     int box_rows = TILE, box_shift = 6;
@@ -393,6 +439,11 @@ const int g_env_cost_b = [] {
     const char* e = std::getenv("FUSEDTOK_COST_B");
     return e ? std::max(0, std::atoi(e)) : 1;
 }();
+// FUSEDTOK_F32_RING=0 keeps float32 caches on the generic CUDA-core kernel (for A/B measurements).
+const bool g_env_f32_ring = [] {
+    const char* e = std::getenv("FUSEDTOK_F32_RING");
+    return !(e && e[0] == '0');
+}();
 const int g_env_dyn_tail = [] {
     const char* e = std::getenv("FUSEDTOK_DYN_TAIL");
     return e ? std::atoi(e) : -1;
@@ -405,7 +456,7 @@ inline bool tc_head_dim(int d) {
 }
 
 DecodePlan plan_decode(int dt, const void* q, const void* k, const void* v, bool paged, bool has_lens, int batch,
-                       int hq, int hkv, int rows, int page, int dim, int sm_count) {
+                       int hq, int hkv, int rows, int page, int dim, int sm_count, bool peers = false) {
     DecodePlan pl;
     const int G = hq / hkv;
     pl.paged = paged;
@@ -415,7 +466,20 @@ DecodePlan plan_decode(int dt, const void* q, const void* k, const void* v, bool
                 ((reinterpret_cast<uintptr_t>(q)) & 3u) == 0;
     if (pl.use_tc && !paged && pl.map_rows >= (1ull << 31)) pl.use_tc = false;
     if (pl.use_tc && paged && !(is_pow2(page) && page >= 8)) pl.use_tc = false;
-    if (pl.use_tc) {
+    // float32: the TMA-fed CUDA-core kernel for the common head dims (the KV-length split with peer exchange and
+    // every other shape stay on the generic kernel)
+    // (launches of at most two tiles per SM are all latency: the generic kernel's two small CTAs per SM start faster)
+    const unsigned long long rough_tiles = (unsigned long long)batch * hkv * (unsigned long long)((rows + TILE - 1) / TILE);
+    pl.use_ring = dt == F32 && g_env_f32_ring && !peers && (dim == 64 || dim == 128) &&
+                  rough_tiles > 2ull * (unsigned long long)sm_count &&
+                  ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(q)) & 15u) == 0 &&
+                  (paged ? (is_pow2(page) && page >= 8) : pl.map_rows < (1ull << 31));
+    if (pl.use_ring) {
+        pl.GC = G == 1 ? 1 : (G <= 4 ? 4 : 8);
+        pl.box_rows = paged ? std::min(page, RF_ROWS) : RF_ROWS;
+        pl.box_shift = 0;
+        while ((1 << pl.box_shift) < pl.box_rows) ++pl.box_shift;
+    } else if (pl.use_tc) {
         pl.GC = std::min(G, (dim == 64 || dim == 128) ? 16 : 8);   // only these two have the 16-head MMA tile
         pl.gp = pl.GC <= 8 ? 8 : 16;
         pl.box_rows = paged ? std::min(page, TILE) : TILE;
@@ -432,12 +496,15 @@ DecodePlan plan_decode(int dt, const void* q, const void* k, const void* v, bool
     pl.units = (unsigned long long)batch * hkv * pl.NCH;
     const unsigned long long tiles_per_seq = (unsigned long long)((rows + TILE - 1) / TILE);
     const unsigned long long max_tiles = pl.units * tiles_per_seq;
-    pl.ncta = (int)std::min<unsigned long long>((unsigned long long)sm_count * (pl.use_tc ? 1 : 2), max_tiles);
+    pl.ncta = (int)std::min<unsigned long long>((unsigned long long)sm_count * ((pl.use_tc || pl.use_ring) ? 1 : 2),
+                                                max_tiles);
     if (pl.ncta < 1) pl.ncta = 1;
     pl.words = (size_t)pl.units + 1;
 
     const size_t slot_bytes = (size_t)pl.GC * (dim + 2) * sizeof(float);
     size_t ranges = (size_t)pl.ncta;
+    if (pl.use_ring)
+        pl.sched_table = has_lens && batch <= SCHED_MAX_B && (unsigned long long)batch * tiles_per_seq < (1ull << 31);
     if (pl.use_tc) {
         pl.sched_table = has_lens && batch <= SCHED_MAX_B && (unsigned long long)batch * tiles_per_seq < (1ull << 31);
         const unsigned long long per_max = max_tiles / (unsigned long long)pl.ncta;
@@ -518,11 +585,21 @@ int decode_launch(const DecodePlan& pl, const Scratch& sc, int dt, const void* q
     p.GC = pl.GC; p.NCH = pl.NCH; p.ncta = pl.ncta;
     p.box_rows = pl.box_rows; p.box_shift = pl.box_shift;
     p.dyn_chunk = pl.dyn_chunk; p.dyn_tail_max = pl.dyn_tail_max; p.sched_table = pl.sched_table;
-    p.cost_split = (g_env_cost_split && pl.use_tc && !pl.dyn_chunk) ? 1 : 0;
+    p.cost_split = (g_env_cost_split && (pl.use_tc || pl.use_ring) && !pl.dyn_chunk) ? 1 : 0;
     p.cost_a = g_env_cost_a;
     p.cost_b = g_env_cost_b;
     p.ws_ml = sc.ws_ml; p.ws_acc = sc.ws_acc; p.counters = sc.counters; p.status = sc.status;
 
+    if (pl.use_ring) {
+        int rc = get_encode_fn();
+        if (rc) return rc;
+        CUtensorMap mk, mv;
+        const unsigned long long trows = pl.paged ? (1ull << 31) - 1 : pl.map_rows;
+        if ((rc = encode_map_f32(&mk, k, trows, dim, pl.box_rows))) return rc;
+        if ((rc = encode_map_f32(&mv, v, trows, dim, pl.box_rows))) return rc;
+        launch_ring_any(mk, mv, p, pl.paged, cs);
+        return check_launch("attention split-KV float32 ring kernel launch");
+    }
     if (pl.use_tc) {
         int rc = get_encode_fn();
         if (rc) return rc;
@@ -570,7 +647,7 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
     DeviceState* dev = nullptr;
     if ((rc = device_state(&dev))) return rc;
     const DecodePlan pl = plan_decode(dt, q, k, v, table != nullptr, lens != nullptr, batch, hq, hkv, rows, page, dim,
-                                      dev->sm_count);
+                                      dev->sm_count, peers != nullptr);
     Arena a;
     if ((rc = get_arena(*dev, cs, pl.words, pl.ml_b, pl.acc_b, true, &a))) return rc;
     const Scratch sc{a.status, a.counters, a.ws_ml, a.ws_acc};

@@ -619,3 +619,59 @@ def test_dynamic_range_plan_when_enabled(tmp_path):
         assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
         outs[name] = np.load(path)
     assert np.abs(outs["static"] - outs["dynamic"]).max() <= 2e-2
+
+
+# ---- float32 caches on the TMA-fed kernel (launches of more than two tiles per SM, head dim 64 / 128) ----------
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("group", [1, 3, 4, 5, 8, 16])
+def test_fp32_ring_kernel_contiguous(d, group):
+    """Large enough for the producer-warp + copy-ring float32 kernel: every heads-per-unit variant (group 1; 3, 4 ->
+    4 with spare rows; 5, 8 -> 8; 16 -> two chunks of 8), ragged lengths that end inside the first and the second
+    half of a tile, on a tile boundary and at zero, 1e-5 against the oracle and bit-exact repetition."""
+    hkv = 2
+    rng = np.random.default_rng(d * 17 + group)
+    b, t = 6, 2048
+    q, k, v, lens = cases.make_case(rng, b, hkv * group, hkv, t, d, True)
+    lens[:] = [t, 0, 1, 33, 64, 1500]
+    qt, kt, vt = (torch.from_numpy(x).cuda() for x in (q, k, v))
+    lt = torch.from_numpy(lens).cuda()
+    out = ft.attention_decode(qt, kt, vt, lt)
+    y = out.cpu().numpy()
+    assert np.abs(y - oracle.decode(q, k, v, lens)).max() <= F32_TOL
+    assert np.all(y[1] == 0)
+    assert torch.equal(ft.attention_decode(qt, kt, vt, lt), out)
+    full = ft.attention_decode(qt, kt, vt).cpu().numpy()          # no lens: the schedule is arithmetic
+    assert np.abs(full - oracle.decode(q, k, v)).max() <= F32_TOL
+    assert_status_ok()
+
+
+@pytest.mark.parametrize("page", [8, 16, 64])
+def test_fp32_ring_kernel_paged(page):
+    """The same kernel behind a block table: pages smaller than, equal to half of, and larger than its 32-row boxes;
+    must equal the contiguous kernel's result on the gathered rows bit for bit."""
+    rng = np.random.default_rng(300 + page)
+    b, hq, hkv, d, t = 4, 16, 4, 128, 2048
+    lens = np.array([t, 700, 0, 1025], np.int32)
+    width = t // page
+    nb = b * width + 5
+    q = rng.standard_normal((b, hq, d)).astype(np.float32)
+    kp = rng.standard_normal((nb, hkv, page, d)).astype(np.float32)
+    vp = rng.standard_normal((nb, hkv, page, d)).astype(np.float32)
+    tbl = rng.permutation(nb)[:b * width].reshape(b, width).astype(np.int32)
+    kc = kp[tbl].transpose(0, 2, 1, 3, 4).reshape(b, hkv, t, d)
+    vc = vp[tbl].transpose(0, 2, 1, 3, 4).reshape(b, hkv, t, d)
+    qt, kpt, vpt = (torch.from_numpy(x).cuda() for x in (q, kp, vp))
+    out = torch.empty_like(qt)
+    tblt, lt = torch.from_numpy(tbl).cuda(), torch.from_numpy(lens).cuda()       # kept alive across the launch
+    _fusedtok.attention_decode_paged_launch(qt.data_ptr(), kpt.data_ptr(), vpt.data_ptr(), tblt.data_ptr(),
+                                            lt.data_ptr(), out.data_ptr(), b, hq, hkv, page, width, d,
+                                            torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    y = out.cpu().numpy()
+    assert np.abs(y - oracle.decode(q, np.ascontiguousarray(kc), np.ascontiguousarray(vc), lens)).max() <= F32_TOL
+    contiguous = ft.attention_decode(qt, torch.from_numpy(np.ascontiguousarray(kc)).cuda(),
+                                     torch.from_numpy(np.ascontiguousarray(vc)).cuda(), lt)
+    assert torch.equal(out, contiguous)
+    assert np.all(y[2] == 0)
+    assert_status_ok()
