@@ -753,6 +753,77 @@ __device__ __forceinline__ void merge_unit(const DecodeParams& p, const Plan& pl
     }
 }
 
+// The same fold, same order, same arithmetic, through shared memory: the partials are copied in with
+// cp.async - no registers hold them while they are in flight, so a whole round of them is requested at
+// once - and their (m, l) pairs go into a small table beside them; the fold then reads shared memory.
+// The version above costs one L2 round trip per 8 partials (and 32 registers), this one one round trip
+// per round of MERGE_TABLE.. `rounds` partials: what a unit split over many ranges (one long sequence
+// spread over the whole grid) needs. `stage`: shared memory, 16-byte aligned, free for the calling
+// threads, of merge_stage_bytes(nthreads, S) bytes for rounds of S partials; `sync()` is a barrier over
+// exactly the `nthreads` calling threads.
+constexpr int MERGE_TABLE_BYTES = 16 * 16 * 8;      // (m, l) of up to 16 partials x 16 heads, or 32 x 8, ...
+__host__ __device__ constexpr int merge_stage_bytes(int nthreads, int S) { return MERGE_TABLE_BYTES + S * nthreads * 8; }
+template <typename T, bool PEERS = true, typename Sync>
+__device__ __forceinline__ void merge_unit_staged(const DecodeParams& p, const Plan& pl, const SegDest& d,
+                                                  unsigned int step, int tid, int nthreads, float* stage,
+                                                  int stage_bytes, Sync sync) {
+    const int P = d.r_last - d.r_first + 1;
+    const int D = p.D, halfd = D >> 1;
+    const int E = d.gvalid * halfd;                                // element pairs of the unit
+    // partials per round: what the stage holds, and no more than the table has entries for
+    const int S = min((stage_bytes - MERGE_TABLE_BYTES) / (nthreads * 8), (MERGE_TABLE_BYTES / 8) / d.gvalid);
+    const bool sparse = !pl.per && !pl.ctot && pl.ncta > pl.total;
+    float2* t_ml = reinterpret_cast<float2*>(stage);
+    float2* t_acc = reinterpret_cast<float2*>(stage) + MERGE_TABLE_BYTES / 8;      // [S][nthreads]
+    for (int e0 = 0; e0 < E; e0 += nthreads) {                     // one pass unless the unit has more pairs than threads
+        const int e = e0 + tid;
+        const int g = e / halfd, dd = (e % halfd) * 2;
+        const int pieces = min(nthreads, E - e0) >> 1;             // 16-byte pieces of a partial in this pass (E is even)
+        float m = -INFINITY, l = 0.0f, a0 = 0.0f, a1 = 0.0f;
+        for (int j0 = 0; j0 < P; j0 += S) {
+            const int n = min(S, P - j0);
+            if (j0 | e0) sync();                                   // the previous round has been read
+            for (int i = tid; i < n * pieces; i += nthreads) {
+                const int j = i / pieces, k = i - j * pieces;
+                const int c = d.r_first + j0 + j;
+                if (sparse && range_empty(pl, c)) continue;
+                const float* src = p.ws_acc + ((size_t)c + (size_t)d.unit) * p.GC * D + (size_t)e0 * 2 + k * 4;
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(t_acc + (size_t)j * nthreads + k * 2);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            for (int i = tid; i < n * d.gvalid; i += nthreads) {
+                const int j = i / d.gvalid, gg = i - j * d.gvalid;
+                const int c = d.r_first + j0 + j;
+                float2 v = make_float2(0.0f, 0.0f);                // an empty range's entry says "skip"
+                if (!(sparse && range_empty(pl, c)))
+                    v = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + (((size_t)c + (size_t)d.unit) * p.GC + gg) * 2));
+                t_ml[i] = v;
+            }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            sync();
+            if (e < E) {
+                for (int j = 0; j < n; ++j) {
+                    const float2 ml = t_ml[j * d.gvalid + g];
+                    if (ml.y <= 0.0f) continue;
+                    const float2 v = t_acc[(size_t)j * nthreads + tid];
+                    if (l == 0.0f) {
+                        m = ml.x; l = ml.y; a0 = v.x; a1 = v.y;
+                        continue;
+                    }
+                    const float m_new = fmaxf(m, ml.x);
+                    const float r_old = expf(m - m_new), r_new = expf(ml.x - m_new);
+                    l = lse_fold(l, r_old, ml.y, r_new);
+                    a0 = lse_fold(a0, r_old, v.x, r_new);
+                    a1 = lse_fold(a1, r_old, v.y, r_new);
+                    m = m_new;
+                }
+            }
+        }
+        if (e < E) emit_final2<T, PEERS>(p, step, d.b, d.h0 + g, dd, m, l, a0, a1, dd == 0);
+    }
+}
+
 // One thread per CTA calls this after every thread of the CTA has written and
 // fenced its part of the partial. Returns true if this CTA delivered the last
 // partial of the unit and must therefore merge it.

@@ -86,7 +86,11 @@ template <int D> struct TcCfg {
 #endif
     static_assert(NS % 2 == 0, "ring depth must be even (see above)");
     static constexpr int ACC_STRIDE = D + 4;           // floats; rows stay 16-byte aligned
-    static constexpr int SCRATCH_BYTES = NCW * 8 * ACC_STRIDE * 4;
+    // Scratch of the segment-end fold ([8 warps x 8 heads] rows), also the stage of the cross-range merge:
+    // rounds of 22 partials where that keeps the CTA inside the 196 KB shared-memory configuration.
+    static constexpr int FOLD_BYTES = NCW * 8 * ACC_STRIDE * 4;
+    static constexpr int MERGE_BYTES = merge_stage_bytes(NCW * 32, 22);
+    static constexpr int SCRATCH_BYTES = (DP <= 128 && MERGE_BYTES > FOLD_BYTES) ? MERGE_BYTES : FOLD_BYTES;
     static constexpr int OFF_SCRATCH = NS * STAGE_BYTES;
     static constexpr int OFF_ML = OFF_SCRATCH + SCRATCH_BYTES;       // [NCW][8] float2
     static constexpr int OFF_BAR = OFF_ML + NCW * 8 * 8;             // full[NS], empty[NS]
@@ -244,9 +248,11 @@ __device__ __forceinline__ float ex2(float x) {
 // 0 entry, 1 dependency wait done, 2 schedule done, 3 first tile landed, 4 producer issued its last
 // copy, 5 last tile consumed, 6 exit, 7 ns spent at segment ends (sum), 8 segment ends, 9 ns spent
 // waiting for tiles (sum), 10 ns in the final publish, 11 ranges processed, 12 ns waiting for range
-// descriptors (sum), 13 the SM the CTA ran on, 14 units merged by this CTA.
+// descriptors (sum), 13 the SM the CTA ran on, 14 units merged by this CTA, 15 producer issued its first copy,
+// 16 producer warp starts, 17 its first range located, 18 first stage free and announced, 19 before the merge
+// of a unit, 20 after it (last one of the CTA).
 #ifdef FTK_TIMELINE
-__device__ unsigned long long g_timeline[1024][16];
+__device__ unsigned long long g_timeline[1024][24];
 #define FTK_STAMP(cond, slot) do { if (cond) g_timeline[blockIdx.x][slot] = global_ns(); } while (0)
 #define FTK_ADD(cond, slot, v) do { if (cond) g_timeline[blockIdx.x][slot] += (v); } while (0)
 #define FTK_NOW() global_ns()
@@ -276,7 +282,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef FTK_TIMELINE
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 16; ++i) g_timeline[blockIdx.x][i] = 0;
+        for (int i = 0; i < 24; ++i) g_timeline[blockIdx.x][i] = 0;
         g_timeline[blockIdx.x][0] = global_ns();
         unsigned int smid;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
@@ -352,6 +358,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         // Everything a tile's copies need (row coordinates, block-table
         // entries, byte count) is worked out BEFORE the wait for its ring
         // stage, so that the copies go out the moment the stage is free.
+        FTK_STAMP(lane == 0, 16);
         const uint64_t pol = policy_evict_first();
         int issued = 0;
         int kv = 0, unit_row0 = 0;          // of the current unit
@@ -406,6 +413,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             more = w0.g < w0.end;
         }
         bool gave_up = false;
+        FTK_STAMP(lane == 0, 17);
         while (more) {
             w = (by_scan || pl.ctot) ? w0 : walker_locate(p, prefix, range_start(pl, r), range_start(pl, r + 1));
             bool announce = true;
@@ -432,6 +440,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     ++nd;
                     announce = false;
                 }
+#ifdef FTK_TIMELINE
+                if (lane == 0 && issued == 0) g_timeline[blockIdx.x][18] = global_ns();
+#endif
                 const uint32_t dst_k = smem_base + s * Cfg::STAGE_BYTES;
                 const uint32_t dst_v = dst_k + Cfg::KV_BYTES;
                 const uint32_t fb = bar_full + s * 8;
@@ -454,6 +465,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                         copy_box(dst_v + off, &tm_v);
                     }
                 }
+#ifdef FTK_TIMELINE
+                if (lane == 0 && issued == 0) g_timeline[blockIdx.x][15] = global_ns();
+#endif
                 ++issued;
                 const int ub_before = w.ub, b_before = w.b;
                 walker_advance(p, w);
@@ -806,7 +820,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 bar_consumers();
                 if (*s_last) {
                     __threadfence();
-                    merge_unit<T>(p, pl, pend, step, tc, NCW * 32);
+                    merge_unit_staged<T>(p, pl, pend, step, tc, NCW * 32, s_acc, Cfg::SCRATCH_BYTES, [] { bar_consumers(); });
                     FTK_ADD(tc == 0, 14, 1);
                 }
             }
@@ -826,9 +840,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         if (tc == 0) *s_last = deliver_partial(p, pend) ? 1 : 0;
         bar_consumers();
         if (*s_last) {
+            FTK_STAMP(tc == 0, 19);
             __threadfence();
-            merge_unit<T>(p, pl, pend, step, tc, NCW * 32);
+            merge_unit_staged<T>(p, pl, pend, step, tc, NCW * 32, s_acc, Cfg::SCRATCH_BYTES, [] { bar_consumers(); });
             FTK_ADD(tc == 0, 14, 1);
+            FTK_STAMP(tc == 0, 20);
         }
     }
     FTK_ADD(tc == 0, 10, FTK_NOW() - tl_f0);

@@ -1550,12 +1550,12 @@ int fusedtok_debug_poke_status(int which, int code, int counter_index) {
 }
 
 #ifdef FTK_TIMELINE
-// Diagnostic builds only: copies the per-CTA timeline of the last tensor-core decode launch (1024 x 16
+// Diagnostic builds only: copies the per-CTA timeline of the last tensor-core decode launch (1024 x 24
 // 64-bit words, see decode_tc.cuh) to `host` after synchronising the device.
 int ftk_debug_timeline(void* host) {
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return cuda_fail("device synchronize failed", e);
-    e = cudaMemcpyFromSymbol(host, ftk::g_timeline, sizeof(unsigned long long) * 1024 * 16);
+    e = cudaMemcpyFromSymbol(host, ftk::g_timeline, sizeof(unsigned long long) * 1024 * 24);
     if (e != cudaSuccess) return cuda_fail("timeline read failed", e);
     return FUSEDTOK_OK;
 }
