@@ -622,6 +622,24 @@ __device__ __forceinline__ Walker walker_locate_cost(const DecodeParams& p, cons
     return w;
 }
 
+// Range r of the cost-weighted split, located by a whole (converged) warp: each boundary is a chain of
+// dependent integer divisions that a single thread takes the better part of a microsecond over, and
+// every CTA pays it before its first copy can go out - so odd and even lanes work out one boundary
+// each, at the same time, and the warp shares the result.
+__device__ __forceinline__ Walker walker_locate_cost_range(const DecodeParams& p, const Plan& pl, int r) {
+    const int odd = threadIdx.x & 1;
+    Walker w = walker_locate_cost(p, pl, cost_start(pl, r + odd), 0);
+    const long long end = __shfl_sync(0xffffffffu, w.g, 1);
+    w.g = __shfl_sync(0xffffffffu, w.g, 0);
+    w.b = __shfl_sync(0xffffffffu, w.b, 0);
+    w.ub = __shfl_sync(0xffffffffu, w.ub, 0);
+    w.ti = __shfl_sync(0xffffffffu, w.ti, 0);
+    w.nt = __shfl_sync(0xffffffffu, w.nt, 0);
+    w.len = __shfl_sync(0xffffffffu, w.len, 0);
+    w.end = end;
+    return w;
+}
+
 // Step to the next tile (skipping empty sequences).
 __device__ __forceinline__ void walker_advance(const DecodeParams& p, Walker& w) {
     ++w.g;
@@ -753,15 +771,37 @@ __device__ __forceinline__ void merge_unit(const DecodeParams& p, const Plan& pl
     }
 }
 
-// The same fold, same order, same arithmetic, through shared memory: the partials are copied in with
-// cp.async - no registers hold them while they are in flight, so a whole round of them is requested at
-// once - and their (m, l) pairs go into a small table beside them; the fold then reads shared memory.
-// The version above costs one L2 round trip per 8 partials (and 32 registers), this one one round trip
-// per round of MERGE_TABLE.. `rounds` partials: what a unit split over many ranges (one long sequence
-// spread over the whole grid) needs. `stage`: shared memory, 16-byte aligned, free for the calling
-// threads, of merge_stage_bytes(nthreads, S) bytes for rounds of S partials; `sync()` is a barrier over
-// exactly the `nthreads` calling threads.
-constexpr int MERGE_TABLE_BYTES = 16 * 16 * 8;      // (m, l) of up to 16 partials x 16 heads, or 32 x 8, ...
+// ---- optional timeline (diagnostic builds only: -DFTK_TIMELINE; slots listed in decode_tc.cuh) ----
+__device__ __forceinline__ unsigned long long timeline_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#ifdef FTK_TIMELINE
+__device__ unsigned long long g_timeline[1024][24];
+#define FTK_STAMP(cond, slot) do { if (cond) g_timeline[blockIdx.x][slot] = timeline_ns(); } while (0)
+#define FTK_ADD(cond, slot, v) do { if (cond) g_timeline[blockIdx.x][slot] += (v); } while (0)
+#define FTK_NOW() timeline_ns()
+#else
+#define FTK_STAMP(cond, slot) do { } while (0)
+#define FTK_ADD(cond, slot, v) do { } while (0)
+#define FTK_NOW() 0ull
+#endif
+
+// The same fold, same order, same arithmetic (bit for bit), organised for a unit that was split over
+// many ranges - one long sequence spread over the whole grid:
+//  - the partials are copied into shared memory with cp.async: no registers hold them while they are
+//    in flight, so a whole round of them is requested at once (the version above costs one L2 round
+//    trip per 8 partials and 32 registers);
+//  - the two scale factors of every fold step, exp(m_before - m_after) and exp(m_j - m_after), depend
+//    only on the (m, l) pairs, so one thread per (partial, head) works them out - all steps at the
+//    same time, each from the running maximum before its partial - instead of every thread of a head
+//    walking the same chain of dependent exponentials;
+//  - what is left per element pair is one multiply-add per partial out of shared memory.
+// `stage`: shared memory, 16-byte aligned, free for the calling threads, merge_stage_bytes(nthreads, S)
+// bytes for rounds of S partials; `sync()` is a barrier over exactly the `nthreads` calling threads.
+constexpr int MERGE_ENTRIES = 256;                                      // (partial, head) pairs per round
+constexpr int MERGE_TABLE_BYTES = MERGE_ENTRIES * (8 + 16) + 2 * 16 * 4;   // (m, l), coefficients, running maxima
 __host__ __device__ constexpr int merge_stage_bytes(int nthreads, int S) { return MERGE_TABLE_BYTES + S * nthreads * 8; }
 template <typename T, bool PEERS = true, typename Sync>
 __device__ __forceinline__ void merge_unit_staged(const DecodeParams& p, const Plan& pl, const SegDest& d,
@@ -769,58 +809,103 @@ __device__ __forceinline__ void merge_unit_staged(const DecodeParams& p, const P
                                                   int stage_bytes, Sync sync) {
     const int P = d.r_last - d.r_first + 1;
     const int D = p.D, halfd = D >> 1;
-    const int E = d.gvalid * halfd;                                // element pairs of the unit
-    // partials per round: what the stage holds, and no more than the table has entries for
-    const int S = min((stage_bytes - MERGE_TABLE_BYTES) / (nthreads * 8), (MERGE_TABLE_BYTES / 8) / d.gvalid);
+    const int gv = d.gvalid;
+    const int E = gv * halfd;                                      // element pairs of the unit
+    // partials per round: what the stage holds, and no more than the tables have entries for
+    const int S = min((stage_bytes - MERGE_TABLE_BYTES) / (nthreads * 8), MERGE_ENTRIES / gv);
     const bool sparse = !pl.per && !pl.ctot && pl.ncta > pl.total;
-    float2* t_ml = reinterpret_cast<float2*>(stage);
-    float2* t_acc = reinterpret_cast<float2*>(stage) + MERGE_TABLE_BYTES / 8;      // [S][nthreads]
+    float2* t_ml = reinterpret_cast<float2*>(stage);                                   // [S][gv] (m, l)
+    float4* t_co = reinterpret_cast<float4*>(stage + MERGE_ENTRIES * 2);               // [S][gv] r_old, r_new, l * r_new, live
+    float* t_run = stage + MERGE_ENTRIES * 6;                                          // [2][16] running maximum per head
+    float2* t_acc = reinterpret_cast<float2*>(stage + MERGE_TABLE_BYTES / 4);          // [S][nthreads]
     for (int e0 = 0; e0 < E; e0 += nthreads) {                     // one pass unless the unit has more pairs than threads
         const int e = e0 + tid;
         const int g = e / halfd, dd = (e % halfd) * 2;
         const int pieces = min(nthreads, E - e0) >> 1;             // 16-byte pieces of a partial in this pass (E is even)
-        float m = -INFINITY, l = 0.0f, a0 = 0.0f, a1 = 0.0f;
-        for (int j0 = 0; j0 < P; j0 += S) {
+        float l = 0.0f, a0 = 0.0f, a1 = 0.0f;
+        int round = 0;
+        for (int j0 = 0; j0 < P; j0 += S, ++round) {
             const int n = min(S, P - j0);
             if (j0 | e0) sync();                                   // the previous round has been read
-            for (int i = tid; i < n * pieces; i += nthreads) {
-                const int j = i / pieces, k = i - j * pieces;
+            // (m, l) pairs first - into a register: their round trip overlaps the issue of the copies
+            const int i_ml = tid;                                  // n * gv <= MERGE_ENTRIES <= nthreads is not assumed:
+            float2 ml_mine = make_float2(0.0f, 0.0f);              // the first entry per thread here, the rest below
+            if (i_ml < n * gv) {
+                const int j = i_ml / gv, gg = i_ml - j * gv;
                 const int c = d.r_first + j0 + j;
-                if (sparse && range_empty(pl, c)) continue;
-                const float* src = p.ws_acc + ((size_t)c + (size_t)d.unit) * p.GC * D + (size_t)e0 * 2 + k * 4;
-                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(t_acc + (size_t)j * nthreads + k * 2);
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+                if (!(sparse && range_empty(pl, c)))               // an empty range's entry stays "skip"
+                    ml_mine = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + (((size_t)c + (size_t)d.unit) * p.GC + gg) * 2));
+            }
+            {
+                // piece i = tid, tid + nthreads, ... of the round: (partial j, 16-byte piece k), stepped without a divide
+                const int jstep = nthreads / pieces, kstep = nthreads - jstep * pieces;
+                int j = tid / pieces, k = tid - j * pieces;
+                const size_t slot_floats = (size_t)p.GC * D;
+                const float* src0 = p.ws_acc + ((size_t)d.r_first + j0 + (size_t)d.unit) * slot_floats + (size_t)e0 * 2;
+                for (; j < n; j += jstep) {
+                    if (!(sparse && range_empty(pl, d.r_first + j0 + j))) {
+                        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(t_acc + (size_t)j * nthreads + k * 2);
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src0 + j * slot_floats + k * 4)
+                                     : "memory");
+                    }
+                    k += kstep;
+                    if (k >= pieces) { k -= pieces; ++j; }
+                }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
-            for (int i = tid; i < n * d.gvalid; i += nthreads) {
-                const int j = i / d.gvalid, gg = i - j * d.gvalid;
+            if (i_ml < n * gv) t_ml[i_ml] = ml_mine;
+            for (int i = tid + nthreads; i < n * gv; i += nthreads) {
+                const int j = i / gv, gg = i - j * gv;
                 const int c = d.r_first + j0 + j;
-                float2 v = make_float2(0.0f, 0.0f);                // an empty range's entry says "skip"
+                float2 v = make_float2(0.0f, 0.0f);
                 if (!(sparse && range_empty(pl, c)))
                     v = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + (((size_t)c + (size_t)d.unit) * p.GC + gg) * 2));
                 t_ml[i] = v;
             }
+            if (j0 == 0 && tid < gv) t_run[tid] = -INFINITY;
+            FTK_STAMP(tid == 0, 21);
+            sync();
+            // the fold steps' coefficients. A partial with l <= 0 is skipped; the first live one meets a running
+            // maximum of -inf and gets the factors 0 and 1, which is the reference's "adopt it verbatim".
+            for (int i = tid; i < n * gv; i += nthreads) {
+                const int j = i / gv, gg = i - j * gv;
+                float m_before = t_run[(round & 1) * 16 + gg];
+                for (int k = 0; k < j; ++k) {
+                    const float2 q = t_ml[k * gv + gg];
+                    if (q.y > 0.0f) m_before = fmaxf(m_before, q.x);
+                }
+                const float2 ml = t_ml[i];
+                float4 co = make_float4(1.0f, 0.0f, 0.0f, 0.0f);
+                float m_after = m_before;
+                if (ml.y > 0.0f) {
+                    m_after = fmaxf(m_before, ml.x);
+                    co.x = expf(m_before - m_after);
+                    co.y = expf(ml.x - m_after);
+                    co.z = __fmul_rn(ml.y, co.y);
+                    co.w = 1.0f;
+                }
+                t_co[i] = co;
+                if (j == n - 1) t_run[((round + 1) & 1) * 16 + gg] = m_after;
+            }
             asm volatile("cp.async.wait_all;" ::: "memory");
             sync();
+            FTK_STAMP(tid == 0, 22);
             if (e < E) {
+                // no branch in the loop, so that the shared-memory loads of several steps are in flight together: a
+                // skipped partial has the factors (1, 0) and its values (never written, possibly NaN) are replaced by 0
+#pragma unroll 4
                 for (int j = 0; j < n; ++j) {
-                    const float2 ml = t_ml[j * d.gvalid + g];
-                    if (ml.y <= 0.0f) continue;
-                    const float2 v = t_acc[(size_t)j * nthreads + tid];
-                    if (l == 0.0f) {
-                        m = ml.x; l = ml.y; a0 = v.x; a1 = v.y;
-                        continue;
-                    }
-                    const float m_new = fmaxf(m, ml.x);
-                    const float r_old = expf(m - m_new), r_new = expf(ml.x - m_new);
-                    l = lse_fold(l, r_old, ml.y, r_new);
-                    a0 = lse_fold(a0, r_old, v.x, r_new);
-                    a1 = lse_fold(a1, r_old, v.y, r_new);
-                    m = m_new;
+                    const float4 co = t_co[j * gv + g];
+                    float2 v = t_acc[(size_t)j * nthreads + tid];
+                    if (co.w == 0.0f) v = make_float2(0.0f, 0.0f);
+                    l = fmaf(l, co.x, co.z);
+                    a0 = lse_fold(a0, co.x, v.x, co.y);
+                    a1 = lse_fold(a1, co.x, v.y, co.y);
                 }
             }
         }
-        if (e < E) emit_final2<T, PEERS>(p, step, d.b, d.h0 + g, dd, m, l, a0, a1, dd == 0);
+        FTK_STAMP(tid == 0, 23);
+        if (e < E) emit_final2<T, PEERS>(p, step, d.b, d.h0 + g, dd, t_run[(round & 1) * 16 + g], l, a0, a1, dd == 0);
     }
 }
 
@@ -830,7 +915,13 @@ __device__ __forceinline__ void merge_unit_staged(const DecodeParams& p, const P
 __device__ __forceinline__ bool deliver_partial(const DecodeParams& p, const SegDest& d) {
     const int old = atomicAdd(p.counters + d.unit, 1);
     const bool last = old == d.nparts - 1;
-    if (last) p.counters[d.unit] = 0;          // ready for the next launch
+    if (last) {
+        // acquire: the other partials were fenced before their arrivals were counted; ordering this thread's
+        // view after the count, and the CTA's after this thread's through the barrier that follows, is enough
+        // for the L2-only loads of the merge - no fence by every thread on the critical path
+        __threadfence();
+        p.counters[d.unit] = 0;                // ready for the next launch
+    }
     return last;
 }
 

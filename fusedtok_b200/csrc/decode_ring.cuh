@@ -29,7 +29,10 @@ template <int D, int GC> struct RfCfg {
     static constexpr int STAGE_BYTES = 2 * KV_BYTES;
     static constexpr int NS = (D == 128) ? 5 : 10;                // 160 KB of rows in flight or landed
     static constexpr int OFF_ACC = NS * STAGE_BYTES;              // fold scratch: [warp][GC][D] floats
-    static constexpr int OFF_ML = OFF_ACC + NCW * GC * D * 4;     // [warp][GC] float2
+    // (also the stage of the cross-range merge, in rounds of 20 partials)
+    static constexpr int FOLD_BYTES = NCW * GC * D * 4;
+    static constexpr int ACC_BYTES = FOLD_BYTES > merge_stage_bytes(NCW * 32, 20) ? FOLD_BYTES : merge_stage_bytes(NCW * 32, 20);
+    static constexpr int OFF_ML = OFF_ACC + ACC_BYTES;            // [warp][GC] float2
     static constexpr int OFF_SCALE = OFF_ML + NCW * GC * 8;       // [warp][GC] float
     static constexpr int OFF_GLOB = OFF_SCALE + NCW * GC * 4;     // [GC] float2
     static constexpr int OFF_BAR = (OFF_GLOB + GC * 8 + 7) & ~7;  // full[NS], empty[NS]
@@ -138,8 +141,7 @@ decode_ring_f32_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
     const int r = (int)blockIdx.x;
     if (!by_scan && total > 0) {
         if (pl.ctot) {
-            const Walker e1 = walker_locate_cost(p, pl, cost_start(pl, r + 1), 0);
-            w = walker_locate_cost(p, pl, cost_start(pl, r), e1.g);
+            w = walker_locate_cost_range(p, pl, r);
             have = w.g < w.end;
         } else if (!range_empty(pl, r)) {
             w = walker_locate(p, prefix, range_start(pl, r), range_start(pl, r + 1));
@@ -366,8 +368,9 @@ decode_ring_f32_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
                 if (threadIdx.x == 0) *s_last = deliver_partial(p, dst) ? 1 : 0;
                 bar_consumers();
                 if (*s_last) {
-                    __threadfence();
-                    merge_unit<T, false>(p, pl, dst, 0u, threadIdx.x, NCW * 32);
+                    merge_unit_staged<T, false>(p, pl, dst, 0u, threadIdx.x, NCW * 32, reinterpret_cast<float*>(smem + Cfg::OFF_ACC),
+                                                Cfg::ACC_BYTES, [] { bar_consumers(); });
+                    bar_consumers();      // the stage is the next fold's scratch
                 }
             }
             fresh = true;

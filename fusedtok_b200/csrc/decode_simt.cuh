@@ -360,7 +360,6 @@ decode_simt_kernel(const DecodeParams p) {
                 if (threadIdx.x == 0) s_last = deliver_partial(p, dst) ? 1 : 0;
                 __syncthreads();
                 if (s_last) {
-                    __threadfence();
                     merge_unit<T, PEERS>(p, pl, dst, step, threadIdx.x, SIMT_THREADS);
                 }
             }

@@ -87,9 +87,9 @@ template <int D> struct TcCfg {
     static_assert(NS % 2 == 0, "ring depth must be even (see above)");
     static constexpr int ACC_STRIDE = D + 4;           // floats; rows stay 16-byte aligned
     // Scratch of the segment-end fold ([8 warps x 8 heads] rows), also the stage of the cross-range merge:
-    // rounds of 22 partials where that keeps the CTA inside the 196 KB shared-memory configuration.
+    // rounds of 20 partials where that keeps the CTA inside the 196 KB shared-memory configuration.
     static constexpr int FOLD_BYTES = NCW * 8 * ACC_STRIDE * 4;
-    static constexpr int MERGE_BYTES = merge_stage_bytes(NCW * 32, 22);
+    static constexpr int MERGE_BYTES = merge_stage_bytes(NCW * 32, 20);
     static constexpr int SCRATCH_BYTES = (DP <= 128 && MERGE_BYTES > FOLD_BYTES) ? MERGE_BYTES : FOLD_BYTES;
     static constexpr int OFF_SCRATCH = NS * STAGE_BYTES;
     static constexpr int OFF_ML = OFF_SCRATCH + SCRATCH_BYTES;       // [NCW][8] float2
@@ -250,17 +250,8 @@ __device__ __forceinline__ float ex2(float x) {
 // waiting for tiles (sum), 10 ns in the final publish, 11 ranges processed, 12 ns waiting for range
 // descriptors (sum), 13 the SM the CTA ran on, 14 units merged by this CTA, 15 producer issued its first copy,
 // 16 producer warp starts, 17 its first range located, 18 first stage free and announced, 19 before the merge
-// of a unit, 20 after it (last one of the CTA).
-#ifdef FTK_TIMELINE
-__device__ unsigned long long g_timeline[1024][24];
-#define FTK_STAMP(cond, slot) do { if (cond) g_timeline[blockIdx.x][slot] = global_ns(); } while (0)
-#define FTK_ADD(cond, slot, v) do { if (cond) g_timeline[blockIdx.x][slot] += (v); } while (0)
-#define FTK_NOW() global_ns()
-#else
-#define FTK_STAMP(cond, slot) do { } while (0)
-#define FTK_ADD(cond, slot, v) do { } while (0)
-#define FTK_NOW() 0ull
-#endif
+// of a unit, 20 after it (last one of the CTA), 21-23 inside that merge: requests issued, data landed and
+// coefficients ready, fold done. (Buffer and macros: common.cuh.)
 
 // ---- the kernel ------------------------------------------------------------
 // T: __nv_bfloat16 or __half. D: a multiple of 16 up to 256 (above 128, and where not a multiple of 64, with GP = 8 only). GP: 8 or 16 = query-head rows of
@@ -408,8 +399,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         bool more = by_scan ? have0 : (total > 0 && !range_empty(pl, r));
         if (pl.ctot) {
             // cost-weighted split: this CTA's range is [first tile at cost >= X_r, first tile at cost >= X_{r+1})
-            const Walker e1 = walker_locate_cost(p, pl, cost_start(pl, r + 1), 0);
-            w0 = walker_locate_cost(p, pl, cost_start(pl, r), e1.g);
+            w0 = walker_locate_cost_range(p, pl, r);
             more = w0.g < w0.end;
         }
         bool gave_up = false;
@@ -814,12 +804,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 // was that the unit's last partial? then this CTA merges the unit
                 if (tc == 0) {
                     const bool last = arrivals == pend.nparts - 1;
-                    if (last) p.counters[pend.unit] = 0;           // ready for the next launch
+                    if (last) {
+                        __threadfence();                           // acquire (see deliver_partial)
+                        p.counters[pend.unit] = 0;                 // ready for the next launch
+                    }
                     *s_last = last ? 1 : 0;
                 }
                 bar_consumers();
                 if (*s_last) {
-                    __threadfence();
                     merge_unit_staged<T>(p, pl, pend, step, tc, NCW * 32, s_acc, Cfg::SCRATCH_BYTES, [] { bar_consumers(); });
                     FTK_ADD(tc == 0, 14, 1);
                 }
@@ -841,7 +833,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         bar_consumers();
         if (*s_last) {
             FTK_STAMP(tc == 0, 19);
-            __threadfence();
             merge_unit_staged<T>(p, pl, pend, step, tc, NCW * 32, s_acc, Cfg::SCRATCH_BYTES, [] { bar_consumers(); });
             FTK_ADD(tc == 0, 14, 1);
             FTK_STAMP(tc == 0, 20);

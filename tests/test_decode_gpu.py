@@ -621,6 +621,33 @@ def test_dynamic_range_plan_when_enabled(tmp_path):
     assert np.abs(outs["static"] - outs["dynamic"]).max() <= 2e-2
 
 
+# ---- one unit split over many ranges: the cross-range merge in rounds and passes ---------------------------
+
+@pytest.mark.parametrize("dt,tol", HALF + [pytest.param(torch.float32, F32_TOL, id="fp32")])
+@pytest.mark.parametrize("shape", [(1, 8, 2, 40000, 128),      # 2 units over the whole grid: several rounds of partials
+                                   (1, 16, 1, 30000, 128),     # 16 heads per unit: more element pairs than threads
+                                   (1, 8, 1, 20000, 64),
+                                   (1, 32, 8, 16384, 128),     # the reference's benchmark shape
+                                   (1, 4, 1, 1000, 128),       # fewer tiles than CTAs: most ranges are empty
+                                   (2, 8, 8, 256, 128)])
+def test_one_sequence_spread_over_the_grid(dt, tol, shape):
+    b, hq, hkv, t, d = shape
+    rng = np.random.default_rng(t + d)
+    q, k, v, lens = cases.make_case(rng, b, hq, hkv, t, d, True)
+    lens[:] = t - 37
+    lens[0] = t
+    qt, kt, vt = (torch.from_numpy(x).cuda().to(dt) for x in (q, k, v))
+    qr, kr, vr = (x.float().cpu().numpy() for x in (qt, kt, vt))
+    lt = torch.from_numpy(lens).cuda()
+    out = ft.attention_decode(qt, kt, vt, lt)
+    y = out.float().cpu().numpy()
+    assert np.abs(y - oracle.decode(qr, kr, vr, lens)).max() <= tol
+    assert torch.equal(ft.attention_decode(qt, kt, vt, lt), out)          # the merge order is fixed
+    full = ft.attention_decode(qt, kt, vt).float().cpu().numpy()          # no lens: the schedule is arithmetic
+    assert np.abs(full - oracle.decode(qr, kr, vr)).max() <= tol
+    assert_status_ok()
+
+
 # ---- float32 caches on the TMA-fed kernel (launches of more than two tiles per SM, head dim 64 / 128) ----------
 
 @pytest.mark.parametrize("d", [64, 128])
