@@ -55,10 +55,11 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 L2_BYTES = 126 * 1024 * 1024
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the split-KV
-# kernel on the default workload, from an ncu capture of this kernel (not
-# re-measured by this script: a profiler cannot run inside a timed benchmark).
-NCU_TRAFFIC_BYTES = {"c2": 541363712}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the decode
+# kernel on a workload, from an ncu capture of that kernel on that workload
+# (profiles/: not re-measured by this script, a profiler cannot run inside a
+# timed benchmark). Workloads without a capture report null.
+NCU_TRAFFIC_BYTES = {"c2": 541166080, "c3": 1118304864, "c2_f32": 1078285712}
 
 WORKLOADS = {
     # name: (batch, q heads, kv heads, dim, rows, dtype, paged, description)

@@ -86,6 +86,7 @@ struct DecodeParams {
     int sched_table;      // lens given and the per-sequence tile prefix sums fit the kernel's table
     int cost_split;       // cut the ranges at equal cost (tiles + unit ends) instead of equal tile counts
     int cost_a, cost_b;   // ... a tile counts cost_a, a unit end cost_b
+    int unit_split;       // generic kernel only: CTA c takes unit c whole (ncta == units); no workspace, no counters
     float scale;          // 1/sqrt(D)
 };
 
@@ -411,6 +412,27 @@ template <typename T>
 __device__ bool sched_init(const DecodeParams& p, SchedShared* sh, Walker& w, unsigned int step) {
     const int upb = p.Hkv * p.NCH;
     const int c = blockIdx.x;
+    if (p.unit_split) {
+        // one CTA per (sequence, kv head, head chunk) unit, every unit whole: each segment is final, so
+        // neither the partial slots nor the arrival counters are touched (the launch that needs no
+        // workspace: a first call that arrives inside a stream capture, where nothing may be allocated)
+        const int b = c / upb;
+        const int len = seq_len(p, b);
+        if (threadIdx.x == 0) sh->total = 1;
+        __syncthreads();
+        if (len == 0) {
+            if (c == b * upb && threadIdx.x == 0) zero_rows<T>(p, b, step);
+            return false;
+        }
+        w.b = b;
+        w.ub = c - b * upb;
+        w.ti = 0;
+        w.len = len;
+        w.nt = tiles_of(len);
+        w.g = 0;
+        w.end = w.nt;
+        return true;
+    }
     long long total_nt;
     if (!p.lens) {
         total_nt = (long long)p.B * tiles_of(p.T);

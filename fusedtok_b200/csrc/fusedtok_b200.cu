@@ -237,6 +237,12 @@ int get_arena(DeviceState& d, cudaStream_t cs, size_t words, size_t ml_b, size_t
     return FUSEDTOK_OK;
 }
 
+// True if get_arena would hand these sizes out without allocating anything.
+bool arena_covers(DeviceState& d, size_t words, size_t ml_b, size_t acc_b) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    return d.status != nullptr && d.smem_attr_set && ml_b + acc_b <= d.arena_bytes && words <= d.counters_cap;
+}
+
 // reference: attention_check, src/attention.cu:184-193
 int attention_check(int batch, int hq, int hkv, long long t_seq, int dim) {
     if (batch < 0 || hq < 1 || hkv < 1 || t_seq < 0 || dim < 1)
@@ -398,6 +404,7 @@ template <typename T> void launch_simt_t(const DecodeParams& p, int lc, cudaStre
 // allocation-free one launch from the same plan, so they run the same kernel on the same split.
 struct DecodePlan {
     bool use_tc = false, use_ring = false, paged = false;
+    bool unit_split = false;   // generic kernel, one CTA per unit, no workspace (first call inside a capture)
     int GC = 1, NCH = 1, lc = 1, gp = 8;
     int ncta = 1;
     int box_rows = TILE, box_shift = 6;
@@ -456,12 +463,14 @@ inline bool tc_head_dim(int d) {
 }
 
 DecodePlan plan_decode(int dt, const void* q, const void* k, const void* v, bool paged, bool has_lens, int batch,
-                       int hq, int hkv, int rows, int page, int dim, int sm_count, bool peers = false) {
+                       int hq, int hkv, int rows, int page, int dim, int sm_count, bool peers = false,
+                       bool unit_split = false) {
     DecodePlan pl;
     const int G = hq / hkv;
     pl.paged = paged;
+    pl.unit_split = unit_split;
     pl.map_rows = paged ? 0ull : (unsigned long long)batch * hkv * (unsigned long long)rows;
-    pl.use_tc = dt != F32 && tc_head_dim(dim) &&
+    pl.use_tc = !unit_split && dt != F32 && tc_head_dim(dim) &&
                 ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
                 ((reinterpret_cast<uintptr_t>(q)) & 3u) == 0;
     if (pl.use_tc && !paged && pl.map_rows >= (1ull << 31)) pl.use_tc = false;
@@ -470,7 +479,7 @@ DecodePlan plan_decode(int dt, const void* q, const void* k, const void* v, bool
     // every other shape stay on the generic kernel)
     // (launches of at most two tiles per SM are all latency: the generic kernel's two small CTAs per SM start faster)
     const unsigned long long rough_tiles = (unsigned long long)batch * hkv * (unsigned long long)((rows + TILE - 1) / TILE);
-    pl.use_ring = dt == F32 && g_env_f32_ring && !peers && (dim == 64 || dim == 128) &&
+    pl.use_ring = !unit_split && dt == F32 && g_env_f32_ring && !peers && (dim == 64 || dim == 128) &&
                   rough_tiles > 2ull * (unsigned long long)sm_count &&
                   ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(q)) & 15u) == 0 &&
                   (paged ? (is_pow2(page) && page >= 8) : pl.map_rows < (1ull << 31));
@@ -499,6 +508,7 @@ DecodePlan plan_decode(int dt, const void* q, const void* k, const void* v, bool
     pl.ncta = (int)std::min<unsigned long long>((unsigned long long)sm_count * ((pl.use_tc || pl.use_ring) ? 1 : 2),
                                                 max_tiles);
     if (pl.ncta < 1) pl.ncta = 1;
+    if (unit_split) pl.ncta = (int)std::min<unsigned long long>(pl.units, 0x7fffffffull);   // (the caller checks the bound)
     pl.words = (size_t)pl.units + 1;
 
     const size_t slot_bytes = (size_t)pl.GC * (dim + 2) * sizeof(float);
@@ -588,6 +598,7 @@ int decode_launch(const DecodePlan& pl, const Scratch& sc, int dt, const void* q
     p.cost_split = (g_env_cost_split && (pl.use_tc || pl.use_ring) && !pl.dyn_chunk) ? 1 : 0;
     p.cost_a = g_env_cost_a;
     p.cost_b = g_env_cost_b;
+    p.unit_split = pl.unit_split ? 1 : 0;
     p.ws_ml = sc.ws_ml; p.ws_acc = sc.ws_acc; p.counters = sc.counters; p.status = sc.status;
 
     if (pl.use_ring) {
@@ -648,6 +659,28 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
     if ((rc = device_state(&dev))) return rc;
     const DecodePlan pl = plan_decode(dt, q, k, v, table != nullptr, lens != nullptr, batch, hq, hkv, rows, page, dim,
                                       dev->sm_count, peers != nullptr);
+    if (!peers && !arena_covers(*dev, pl.words, pl.ml_b, pl.acc_b) && stream_is_capturing(cs)) {
+        // The workspace this launch wants does not exist yet and a capture is no place to allocate it. Like
+        // the reference, which then uses its workspace-free single kernel for this launch and for the whole
+        // captured graph (src/attention.cu:1498-1509), degrade to a launch that needs none: the generic kernel,
+        // one CTA per unit, every unit whole. Later calls outside a capture set the workspace up as usual.
+        const DecodePlan up = plan_decode(dt, q, k, v, table != nullptr, lens != nullptr, batch, hq, hkv, rows, page,
+                                          dim, dev->sm_count, false, true);
+        if (up.units > 0x7fffffffull)
+            return fail(FUSEDTOK_RUNTIME_ERROR,
+                        "decode attention workspace must be allocated outside a CUDA graph capture - "
+                        "warm the shape up once before capturing");
+        {
+            std::lock_guard<std::mutex> lock(g_mutex);
+            if (!dev->smem_attr_set) {
+                if ((rc = set_all_smem_attrs())) return rc;      // not a stream operation: legal while capturing
+                dev->smem_attr_set = true;
+            }
+        }
+        const Scratch none{nullptr, nullptr, nullptr, nullptr};
+        return decode_launch(up, none, dt, q, k, v, table, lens, out, partial, batch, hq, hkv, rows, page, tbl_width,
+                             dim, cs, nullptr);
+    }
     Arena a;
     if ((rc = get_arena(*dev, cs, pl.words, pl.ml_b, pl.acc_b, true, &a))) return rc;
     const Scratch sc{a.status, a.counters, a.ws_ml, a.ws_acc};

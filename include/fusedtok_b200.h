@@ -15,9 +15,13 @@
  * memory on the current device; the work is asynchronous on `stream` (0 = the
  * default stream); nothing is synchronised, read back or retained except the
  * library-owned fp32 workspace, which is allocated (per device, grow-only,
- * never freed) on first use. A call that would have to allocate while `stream`
- * is being captured into a CUDA graph fails with FUSEDTOK_RUNTIME_ERROR: warm
- * a shape up once outside the capture. Launches on different streams of one
+ * never freed) on first use. A decode call that would have to allocate while
+ * `stream` is being captured into a CUDA graph allocates nothing: like the
+ * reference (src/attention.cu:1498-1509) it runs that launch on a slower
+ * kernel that needs no workspace (one CTA per (sequence, kv head) unit), and
+ * the captured graph keeps it; warm a shape up once outside the capture to
+ * capture the fast one. Other calls that would allocate during a capture
+ * (exchange buffers, prefill) fail with FUSEDTOK_RUNTIME_ERROR. Launches on different streams of one
  * device share the workspace and must not overlap (same rule as the
  * reference, include/fusedtok/cuda_launch.hpp:187-190).
  *
