@@ -23,12 +23,35 @@ NVCC_FLAGS = [
 ]
 
 
-def stale():
-    if not os.path.exists(LIB):
+# The self-checking variant (tests/test_bounds_build_gpu.py): same sources with -DFTK_BOUNDS.
+BOUNDS_LIB = os.path.join(HERE, "libfusedtok_b200_bounds.so")
+
+
+def stale(target=None):
+    target = target or LIB
+    if not os.path.exists(target):
         return True
-    t = os.path.getmtime(LIB)
+    t = os.path.getmtime(target)
     deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
     return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+
+
+def _command(defines, target, verbose=False):
+    cmd = ["nvcc"] + NVCC_FLAGS + ["-D" + d for d in defines]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    return cmd + [os.path.join(CSRC, s) for s in SOURCES] + ["-o", target]
+
+
+def build_all(force=False):
+    """The product and the self-checking variant, whichever is out of date, compiled side by side (each
+    is one long nvcc run)."""
+    jobs = [(t, subprocess.Popen(_command(d, t))) for d, t in (((), LIB), (("FTK_BOUNDS",), BOUNDS_LIB))
+            if force or stale(t)]
+    failed = [t for t, job in jobs if job.wait() != 0]
+    if failed:
+        raise RuntimeError("nvcc failed for " + ", ".join(failed))
+    return LIB
 
 
 def build(force=False, verbose=False, defines=(), out=None):
@@ -38,16 +61,15 @@ def build(force=False, verbose=False, defines=(), out=None):
     target = out or LIB
     if not force and not defines and not stale():
         return LIB
-    cmd = ["nvcc"] + NVCC_FLAGS + ["-D" + d for d in defines]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", target]
-    subprocess.check_call(cmd)
+    subprocess.check_call(_command(defines, target, verbose))
     return target
 
 
 if __name__ == "__main__":
-    # python fusedtok_b200/_build.py [--force] [-v] [-DNAME ...] [--out path]
+    # python fusedtok_b200/_build.py [--force] [-v] [-DNAME ...] [--out path] | --all
+    if "--all" in sys.argv:
+        print(build_all(force="--force" in sys.argv))
+        sys.exit(0)
     defs = [a[2:] for a in sys.argv[1:] if a.startswith("-D")]
     out_path = sys.argv[sys.argv.index("--out") + 1] if "--out" in sys.argv else None
     if defs and not out_path:

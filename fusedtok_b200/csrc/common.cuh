@@ -48,6 +48,7 @@ enum : int {
     ST_DRAIN_TIMEOUT = 4,
     ST_PEER_TIMEOUT = 5,         // a peer's block of the KV-length split never arrived
     ST_WAIT_RANGE_TIMEOUT = 7,   // a consumer gave up waiting for the producer's next range
+    ST_BOUNDS = 8,               // self-checking build: a computed cache row, partial slot or counter index was out of range
 };
 
 struct DecodeParams {
@@ -88,6 +89,10 @@ struct DecodeParams {
     int cost_a, cost_b;   // ... a tile counts cost_a, a unit end cost_b
     int unit_split;       // generic kernel only: CTA c takes unit c whole (ncta == units); no workspace, no counters
     float scale;          // 1/sqrt(D)
+    // What the launch may touch, for the self-checking build (-DFTK_BOUNDS); 0 = not known, not checked.
+    unsigned long long bound_rows;    // rows of the K (and V) array: B*Hkv*T, or pool blocks * Hkv * page
+    unsigned int bound_slots;         // partial slots of the workspace
+    unsigned int bound_words;         // arrival counters
 };
 
 // Float offset of the acc block inside a triple buffer of `rows` (b, h) rows:
@@ -158,6 +163,25 @@ template <> struct Store<__half> {
 // acc * r_old + x * r_new with the rounding spelled out (one rounded product, one fused multiply-add),
 // so that every place that folds partials - inside a kernel, across kernels, across GPUs - produces the
 // same bits whatever the compiler would otherwise choose to contract.
+// ---- self-checking build (-DFTK_BOUNDS): the stand-in for a memory checker ----------------------------
+// Every cache row a kernel is about to read and every workspace slot / arrival counter it is about to
+// touch is compared with what the host said the launch owns; a value out of range is recorded in the
+// status word (ST_BOUNDS) and the access is redirected (row 0) or left out, so the build reports the
+// mistake instead of faulting. The product build compiles all of it away.
+#ifdef FTK_BOUNDS
+__device__ __forceinline__ bool bounds_ok(const DecodeParams& p, bool ok) {
+    if (!ok && p.status) atomicCAS(p.status, ST_OK, ST_BOUNDS);
+    return ok;
+}
+#define FTK_ROW_OK(p, row) bounds_ok(p, (p).bound_rows == 0 || (unsigned long long)(row) < (p).bound_rows)
+#define FTK_SLOT_OK(p, slot, unit)                                                             \
+    bounds_ok(p, ((p).bound_slots == 0 || (unsigned long long)(slot) < (p).bound_slots) &&    \
+                     ((p).bound_words == 0 || (unsigned long long)(unit) < (p).bound_words))
+#else
+#define FTK_ROW_OK(p, row) true
+#define FTK_SLOT_OK(p, slot, unit) true
+#endif
+
 __device__ __forceinline__ float lse_fold(float acc, float r_old, float x, float r_new) {
     return fmaf(acc, r_old, __fmul_rn(x, r_new));
 }

@@ -115,8 +115,9 @@ decode_ring_f32_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
     bool by_scan = false, have = false;
     long long total;
     if (!p.lens) {
+        // every sequence has p.T rows: plan and range are arithmetic on kernel parameters and may overlap the
+        // previous kernel in the stream; the dependency wait follows them (below)
         total = (long long)p.B * tiles_of(p.T) * upb;
-        asm volatile("griddepcontrol.wait;" ::: "memory");
     } else {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         if (p.sched_table) {
@@ -148,6 +149,7 @@ decode_ring_f32_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
             have = true;
         }
     }
+    if (!p.lens) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (!have) return;
 
     // halves of a tile that hold valid rows: 1 or 2 (the walker never stands on an empty tile)
@@ -180,6 +182,7 @@ decode_ring_f32_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
                     const int blk = __ldg(p.table + (size_t)w.b * p.tbl_width + t0 / p.page);
                     row = (blk * p.Hkv + kv) * p.page + (t0 % p.page);
                 }
+                if (!FTK_ROW_OK(p, row)) row = 0;
                 if (!mbar_wait(bar_empty + s * 8, ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY_TIMEOUT)) {
                     gave_up = true;
                     break;
@@ -355,13 +358,13 @@ decode_ring_f32_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
                 const float2 ml = s_glob[g];
                 if (dst.whole) {
                     emit_final2<T, false>(p, 0u, dst.b, dst.h0 + g, d, ml.x, ml.y, a0, a1, d == 0);
-                } else {
+                } else if (FTK_SLOT_OK(p, dst.slot, dst.unit)) {
                     const size_t pr = dst.slot * p.GC + g;
                     *reinterpret_cast<float2*>(p.ws_acc + pr * D + d) = make_float2(a0, a1);
                     if (d == 0) *reinterpret_cast<float2*>(p.ws_ml + pr * 2) = ml;
                 }
             }
-            if (!dst.whole) {
+            if (!dst.whole && FTK_SLOT_OK(p, dst.slot, dst.unit)) {
                 // publish the partial; the CTA that publishes a unit's last one merges it
                 __threadfence();
                 bar_consumers();

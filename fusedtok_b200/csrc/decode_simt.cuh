@@ -179,10 +179,11 @@ decode_simt_kernel(const DecodeParams p) {
                 } else {
                     row = ((size_t)s.w.b * p.Hkv + kvh) * p.T + (live ? t : t_base);
                 }
+                const bool row_ok = FTK_ROW_OK(p, row);
 #pragma unroll
                 for (int j = 0; j < LC; ++j) {
                     const int c = lane + 32 * j;
-                    const bool on = live && c < chunks;
+                    const bool on = live && row_ok && c < chunks;
                     const size_t off = on ? row * D + c * 4 : 0;
                     cp_async4<T>(slot(stage, r, 0, j), kbase + off, on);
                     cp_async4<T>(slot(stage, r, 1, j), vbase + off, on);
@@ -347,13 +348,13 @@ decode_simt_kernel(const DecodeParams p) {
                 const float2 ml = s_glob[g];
                 if (dst.whole) {
                     emit_final2<T, PEERS>(p, step, dst.b, dst.h0 + g, d, ml.x, ml.y, a0, a1, d == 0);
-                } else {
+                } else if (FTK_SLOT_OK(p, dst.slot, dst.unit)) {
                     const size_t pr = dst.slot * p.GC + g;
                     *reinterpret_cast<float2*>(p.ws_acc + pr * D + d) = make_float2(a0, a1);
                     if (d == 0) *reinterpret_cast<float2*>(p.ws_ml + pr * 2) = ml;
                 }
             }
-            if (!dst.whole) {
+            if (!dst.whole && FTK_SLOT_OK(p, dst.slot, dst.unit)) {
                 // publish the partial; the CTA that publishes a unit's last one merges it
                 __threadfence();
                 __syncthreads();

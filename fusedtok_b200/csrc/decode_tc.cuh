@@ -311,13 +311,28 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     bool have0 = false, by_scan = false;
     long long total;
     unsigned int step = 0;                      // step number of a KV-length split with peer exchange
+    Plan plan;
+    bool located = false;                       // (producer warp) w0 already holds this CTA's range
     if (!p.lens) {
-        // every sequence has p.T rows: the schedule is arithmetic on kernel parameters and
-        // belongs to the part that may overlap the previous kernel
+        // every sequence has p.T rows: the schedule - the plan and, in the producer warp, this CTA's range - is
+        // arithmetic on kernel parameters and belongs to the part that may overlap the previous kernel
         total = (long long)p.B * tiles_of(p.T) * upb;
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        FTK_STAMP(threadIdx.x == 0, 1);
-        step = peer_step(p);
+        plan = make_plan(total, p.ncta, p.dyn_chunk, p.dyn_tail_max);
+        if (p.cost_split && total > 0)
+            plan_enable_cost(plan, (long long)p.B * tiles_of(p.T), p.B, upb, nullptr, nullptr, tiles_of(p.T), p.cost_a,
+                             p.cost_b);
+        if (warp == NCW && plan.ctot) {
+            w0 = walker_locate_cost_range(p, plan, static_range(plan, (int)blockIdx.x));
+            located = true;
+        }
+        // The producer warp of a contiguous cache goes on without waiting - range descriptor, first tile's
+        // coordinates, stage, expect-tx are all shared memory and arithmetic - and waits right before its first
+        // copy; with a block table its very next step reads the table, so it waits here like everybody else.
+        if (warp != NCW || PAGED) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            FTK_STAMP(threadIdx.x == 0, 1);
+            step = peer_step(p);
+        }
     } else {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         FTK_STAMP(threadIdx.x == 0, 1);
@@ -335,11 +350,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         }
     }
     if (*abort_flag) return;
-    Plan plan = make_plan(total, p.ncta, by_scan ? 0 : p.dyn_chunk, p.dyn_tail_max);
-    if (p.cost_split && !by_scan && total > 0) {
-        if (prefix) plan_enable_cost(plan, prefix[p.B], zprefix[p.B], upb, prefix, zprefix, 0, p.cost_a, p.cost_b);
-        else plan_enable_cost(plan, (long long)p.B * tiles_of(p.T), p.B, upb, nullptr, nullptr, tiles_of(p.T), p.cost_a,
-                              p.cost_b);
+    if (p.lens) {
+        plan = make_plan(total, p.ncta, by_scan ? 0 : p.dyn_chunk, p.dyn_tail_max);
+        if (p.cost_split && prefix && total > 0)
+            plan_enable_cost(plan, prefix[p.B], zprefix[p.B], upb, prefix, zprefix, 0, p.cost_a, p.cost_b);
     }
     const Plan pl = plan;
     FTK_STAMP(threadIdx.x == 0, 2);
@@ -389,6 +403,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     bytes = 2 * Cfg::KV_BYTES;
                 }
             }
+            // (small pages: `row` is per lane, and only the lanes that will copy a page hold a page of this tile)
+            if ((!PAGED || p.page > TILE || lane < npg) && !FTK_ROW_OK(p, row)) row = 0;
         };
         int s = 0;                 // ring stage of the next tile
         uint32_t ph = 0;           // phase parity of that stage's current use
@@ -399,10 +415,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         bool more = by_scan ? have0 : (total > 0 && !range_empty(pl, r));
         if (pl.ctot) {
             // cost-weighted split: this CTA's range is [first tile at cost >= X_r, first tile at cost >= X_{r+1})
-            w0 = walker_locate_cost_range(p, pl, r);
+            if (!located) w0 = walker_locate_cost_range(p, pl, r);
             more = w0.g < w0.end;
         }
         bool gave_up = false;
+        bool dep_waited = PAGED || p.lens != nullptr;            // this warp has passed the dependency wait
         FTK_STAMP(lane == 0, 17);
         while (more) {
             w = (by_scan || pl.ctot) ? w0 : walker_locate(p, prefix, range_start(pl, r), range_start(pl, r + 1));
@@ -413,6 +430,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             // has been issued, so the atomic's round trip (microseconds under full memory load) never holds
             // up a copy. A CTA thus always has one dynamic range in reserve.
             int taken = 0;
+            if (pl.per && !dep_waited) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");          // the counter below is global memory
+                dep_waited = true;
+            }
             if (pl.per && lane == 0) taken = atomicAdd(next_tail, 1);
             while (w.g < w.end) {
                 if (!mbar_wait(bar_empty + s * 8, ph ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY_TIMEOUT)) {
@@ -437,6 +458,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 const uint32_t dst_v = dst_k + Cfg::KV_BYTES;
                 const uint32_t fb = bar_full + s * 8;
                 if (lane == 0) mbar_expect_tx(fb, bytes);
+                if (!dep_waited) {
+                    asm volatile("griddepcontrol.wait;" ::: "memory");      // first global access of this warp
+                    dep_waited = true;
+                }
                 const uint32_t panel_bytes = (uint32_t)p.box_rows * 128u;
                 auto copy_box = [&](uint32_t dst, const CUtensorMap* map) {
                     if constexpr (Cfg::SPLIT) tma_load_rows_split<Cfg::NH>(dst, map, row, panel_bytes, fb, pol);
@@ -793,7 +818,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     const float2 ml = make_float2(mg * p.scale, lg);   // m from raw score units to natural-log units
                     if (dst.whole) {
                         emit_final2<T>(p, step, dst.b, dst.h0 + g, d, ml.x, ml.y, a0, a1, d == 0);
-                    } else {
+                    } else if (FTK_SLOT_OK(p, dst.slot, dst.unit)) {
                         const size_t pr = dst.slot * p.GC + g;
                         *reinterpret_cast<float2*>(p.ws_acc + pr * D + d) = make_float2(a0, a1);
                         if (d == 0) *reinterpret_cast<float2*>(p.ws_ml + pr * 2) = ml;
@@ -816,7 +841,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     FTK_ADD(tc == 0, 14, 1);
                 }
             }
-            have_pend = !dst.whole;
+            have_pend = !dst.whole && FTK_SLOT_OK(p, dst.slot, dst.unit);
             pend = dst;
             FTK_ADD(tc == 0, 7, FTK_NOW() - tl_s0);
             FTK_ADD(tc == 0, 8, 1);

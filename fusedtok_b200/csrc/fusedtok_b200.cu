@@ -14,6 +14,7 @@
 #include <cstdio>
 #include <cstring>
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -402,6 +403,10 @@ template <typename T> void launch_simt_t(const DecodeParams& p, int lc, cudaStre
 // count: which kernel, how the GQA group is chunked, the grid, how the tile sequence is cut into
 // ranges, and the layout of the split-KV scratch. Both the allocating launchers and the
 // allocation-free one launch from the same plan, so they run the same kernel on the same split.
+// Blocks in the paged pool of the launches that follow, when a test has said so (fusedtok_debug_set_pool_blocks);
+// 0 = unknown. Only the self-checking build looks at what is derived from it.
+std::atomic<long long> g_debug_pool_blocks{0};
+
 struct DecodePlan {
     bool use_tc = false, use_ring = false, paged = false;
     bool unit_split = false;   // generic kernel, one CTA per unit, no workspace (first call inside a capture)
@@ -599,6 +604,11 @@ int decode_launch(const DecodePlan& pl, const Scratch& sc, int dt, const void* q
     p.cost_a = g_env_cost_a;
     p.cost_b = g_env_cost_b;
     p.unit_split = pl.unit_split ? 1 : 0;
+    // what this launch owns (read by the self-checking build only)
+    p.bound_rows = pl.paged ? (unsigned long long)g_debug_pool_blocks * (unsigned long long)hkv * (unsigned long long)page
+                            : pl.map_rows;
+    p.bound_slots = sc.ws_ml ? (unsigned int)std::min<size_t>(pl.slots, 0xffffffffu) : 0u;
+    p.bound_words = sc.counters ? (unsigned int)std::min<size_t>(pl.words, 0xffffffffu) : 0u;
     p.ws_ml = sc.ws_ml; p.ws_acc = sc.ws_acc; p.counters = sc.counters; p.status = sc.status;
 
     if (pl.use_ring) {
@@ -1541,6 +1551,12 @@ int fusedtok_attention_device_status(int* status) {
             if (*status == 0) *status = word;
         }
     }
+    return FUSEDTOK_OK;
+}
+
+int fusedtok_debug_set_pool_blocks(long long blocks) {
+    if (blocks < 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "pool blocks must be >= 0");
+    g_debug_pool_blocks.store(blocks);
     return FUSEDTOK_OK;
 }
 

@@ -309,6 +309,15 @@ long long fusedtok_attention_launch_count(int reset);
  * Fails if the chosen path has not run on the current device yet. */
 int fusedtok_debug_poke_status(int which, int code, int counter_index);
 
+/* Test hook of the self-checking build (the library compiled with -DFTK_BOUNDS:
+ * every cache row, partial slot and arrival counter a decode kernel computes is
+ * compared with what the launch owns; a value out of range sets status 8 and the
+ * access is redirected or left out instead of made). The contiguous entry points
+ * know the size of their cache; the paged ones are not told the size of the pool,
+ * so a test states it here (0 = unknown, page ids unchecked). No effect on the
+ * product build; no counterpart in the reference. */
+int fusedtok_debug_set_pool_blocks(long long blocks);
+
 #ifdef __cplusplus
 }
 #endif
