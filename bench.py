@@ -59,7 +59,7 @@ FALLBACK_HBM_GBS = 6650.0
 # kernel on a workload, from an ncu capture of that kernel on that workload
 # (profiles/: not re-measured by this script, a profiler cannot run inside a
 # timed benchmark). Workloads without a capture report null.
-NCU_TRAFFIC_BYTES = {"c2": 541166080, "c3": 1118304864, "c2_f32": 1078285712}
+NCU_TRAFFIC_BYTES = {"c2": 541281280, "c3": 1118520704, "c2_f32": 1078616368}
 
 WORKLOADS = {
     # name: (batch, q heads, kv heads, dim, rows, dtype, paged, description)
