@@ -1091,11 +1091,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1 or args.gpus > 1:
-        # NCCL_DEBUG is left as the caller set it; whatever NCCL logs goes to a file (set before NCCL is
-        # loaded) so that stdout stays one JSON line
-        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-        os.environ.setdefault("NCCL_DEBUG_FILE", os.path.join(ROOT, "gpurun_out", "nccl_debug.%h.%p.log"))
+    # (NCCL_DEBUG and NCCL_DEBUG_FILE are left as the caller set them: whatever NCCL logs goes where the caller
+    # sent it; the result is the one line of stdout that starts with '{')
     if args.workload == "refrows":
         if rank == 0:
             run_reference_rows(args)

@@ -872,7 +872,7 @@ __device__ __forceinline__ void merge_unit_staged(const DecodeParams& p, const P
         int round = 0;
         for (int j0 = 0; j0 < P; j0 += S, ++round) {
             const int n = min(S, P - j0);
-            if (j0 | e0) sync();                                   // the previous round has been read
+            if (j0 | e0) sync();                                   // everybody is done reading the stage
             // (m, l) pairs first - into a register: their round trip overlaps the issue of the copies
             const int i_ml = tid;                                  // n * gv <= MERGE_ENTRIES <= nthreads is not assumed:
             float2 ml_mine = make_float2(0.0f, 0.0f);              // the first entry per thread here, the rest below
