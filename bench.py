@@ -91,6 +91,31 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
+def read_only_stream_gbs(torch, device):
+    """Bandwidth of a read-only pass over a buffer far larger than L2 (the library's read_stream kernel),
+    or None if this build of the library lacks it."""
+    from fusedtok_b200 import _fusedtok
+    fn = getattr(_fusedtok._lib, "fusedtok_debug_read_stream", None)
+    if fn is None:
+        return None
+    nbytes = 2 << 30
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    buf.zero_()
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        if fn(buf.data_ptr(), nbytes, stream) != 0:
+            return None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(10):
+        fn(buf.data_ptr(), nbytes, stream)
+    e1.record()
+    torch.cuda.synchronize()
+    del buf
+    return nbytes * 10 / (e0.elapsed_time(e1) * 1e-3) / 1e9
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons with nvidia-smi while the timed
     region runs."""
@@ -669,6 +694,14 @@ def run_ours(args, w, rank, world, local_rank):
         "device_status": status,
         "clocks": clocks,
     }
+    if world == 1 and not args.profile:
+        rs = read_only_stream_gbs(torch, device)
+        if rs:
+            line["roofline"]["read_only_stream"] = {
+                "GBps": rs, "frac": per_gpu / rs,
+                "note": "this library's plain-load kernel reading a 2 GiB buffer once (CUDA events, 10 launches "
+                        "after 3 warm-ups), measured live after the timed region: the read-only counterpart of the "
+                        "copy bandwidth in `peak`"}
     line.update(extra)
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)

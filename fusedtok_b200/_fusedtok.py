@@ -69,6 +69,8 @@ _lib.fusedtok_attention_device_status.argtypes = [ctypes.POINTER(_i)]
 _lib.fusedtok_attention_launch_count.argtypes = [_i]
 _lib.fusedtok_attention_launch_count.restype = ctypes.c_longlong
 _lib.fusedtok_debug_poke_status.argtypes = [_i, _i, _i]
+if hasattr(_lib, "fusedtok_debug_read_stream"):           # (measurement aid of bench.py; same remark as below)
+    _lib.fusedtok_debug_read_stream.argtypes = [_vp, ctypes.c_ulonglong, _sz]
 if hasattr(_lib, "fusedtok_debug_set_pool_blocks"):      # (a test hook: older variant builds lack it; tests/test_abi.py
     _lib.fusedtok_debug_set_pool_blocks.argtypes = [ctypes.c_longlong]      # checks the product library for every export)
 
@@ -93,7 +95,7 @@ EXPORTS = (
     "fusedtok_exchange_open", "fusedtok_exchange_close", "fusedtok_attention_decode_exchange_launch",
     "fusedtok_attention_decode_launch_noalloc",
     "fusedtok_attention_device_status", "fusedtok_attention_launch_count", "fusedtok_debug_poke_status",
-    "fusedtok_debug_set_pool_blocks",
+    "fusedtok_debug_set_pool_blocks", "fusedtok_debug_read_stream",
 )
 
 

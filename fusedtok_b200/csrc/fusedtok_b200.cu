@@ -1554,6 +1554,17 @@ int fusedtok_attention_device_status(int* status) {
     return FUSEDTOK_OK;
 }
 
+int fusedtok_debug_read_stream(const void* src, unsigned long long bytes, uintptr_t stream) {
+    if (!src || (reinterpret_cast<uintptr_t>(src) & 15u) || bytes < 16)
+        return fail(FUSEDTOK_INVALID_ARGUMENT, "read stream: a 16-byte aligned device buffer of at least 16 bytes");
+    DeviceState* dev = nullptr;
+    const int rc = device_state(&dev);
+    if (rc) return rc;
+    read_stream_kernel<<<dev->sm_count * 8, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(src),
+                                                                          (size_t)(bytes / 16), nullptr);
+    return check_launch("read stream kernel launch");
+}
+
 int fusedtok_debug_set_pool_blocks(long long blocks) {
     if (blocks < 0) return fail(FUSEDTOK_INVALID_ARGUMENT, "pool blocks must be >= 0");
     g_debug_pool_blocks.store(blocks);

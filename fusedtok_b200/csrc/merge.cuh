@@ -81,4 +81,27 @@ __global__ void fill_empty_triple_kernel(float* ml, float* acc, long long rows, 
     if (i < rows * D) acc[i] = 0.0f;
 }
 
+// Measurement aid for the benchmark's roofline: reads `n16` 16-byte words once, as fast as plain loads go
+// (8 independent streaming loads in flight per thread), and does nothing with them - the read-only
+// counterpart of a copy bandwidth. `sink` is written only if the XOR of everything read hits one value.
+__global__ void __launch_bounds__(256) read_stream_kernel(const uint4* __restrict__ src, size_t n16, unsigned int* sink) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    uint4 acc = make_uint4(0u, 0u, 0u, 0u);
+    for (; i + 7 * stride < n16; i += 8 * stride) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __ldcs(src + i + j * stride);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            acc.x ^= v[j].x; acc.y ^= v[j].y; acc.z ^= v[j].z; acc.w ^= v[j].w;
+        }
+    }
+    for (; i < n16; i += stride) {
+        const uint4 v = __ldcs(src + i);
+        acc.x ^= v.x; acc.y ^= v.y; acc.z ^= v.z; acc.w ^= v.w;
+    }
+    if ((acc.x ^ acc.y ^ acc.z ^ acc.w) == 0x9e3779b9u && sink) *sink = 1u;
+}
+
 }  // namespace ftk

@@ -318,6 +318,12 @@ int fusedtok_debug_poke_status(int which, int code, int counter_index);
  * product build; no counterpart in the reference. */
 int fusedtok_debug_set_pool_blocks(long long blocks);
 
+/* Measurement aid (bench.py's roofline): launches a kernel that reads `bytes`
+ * of device memory at `src` (16-byte aligned) once with plain streaming loads
+ * and discards them - a read-only bandwidth figure to set beside the copy
+ * bandwidth the roofline is quoted against. No counterpart in the reference. */
+int fusedtok_debug_read_stream(const void* src, unsigned long long bytes, uintptr_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -125,6 +125,18 @@ def test_misaligned_operands_are_refused_before_any_launch():
     assert rc == 1 and b"aligned" in lib.fusedtok_last_error()
 
 
+def test_measurement_and_test_hooks_check_their_arguments():
+    """fusedtok_debug_read_stream (bench.py's read-only bandwidth figure) and fusedtok_debug_set_pool_blocks (the
+    self-checking build's pool size) refuse bad arguments before any CUDA call."""
+    from fusedtok_b200 import _fusedtok
+    lib = _fusedtok._lib
+    assert lib.fusedtok_debug_read_stream(None, 1 << 20, 0) == 1
+    assert lib.fusedtok_debug_read_stream(4096 + 8, 1 << 20, 0) == 1 and b"aligned" in lib.fusedtok_last_error()
+    assert lib.fusedtok_debug_read_stream(4096, 8, 0) == 1
+    assert lib.fusedtok_debug_set_pool_blocks(-1) == 1
+    assert lib.fusedtok_debug_set_pool_blocks(0) == 0
+
+
 def test_exchange_launch_argument_checks():
     from fusedtok_b200 import _fusedtok
     lib = _fusedtok._lib

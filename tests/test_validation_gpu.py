@@ -169,3 +169,12 @@ def test_host_inputs_without_cuda_are_validated_then_refused():
                                   np.zeros((4, 2, 2, 8), np.float32), np.zeros((1, 2), np.int32))
     with pytest.raises(ft.NoHostPathError):
         ft.attention_decode(np.zeros((1, 4, 8), np.float32), k, k.copy())
+
+
+def test_read_stream_measurement_kernel_runs():
+    """bench.py's read-only bandwidth probe: a launch over a small buffer completes and leaves the status clean."""
+    from fusedtok_b200 import _fusedtok
+    buf = torch.zeros(1 << 22, dtype=torch.uint8, device="cuda")
+    assert _fusedtok._lib.fusedtok_debug_read_stream(buf.data_ptr(), buf.numel(), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert _fusedtok.attention_device_status() == 0
