@@ -26,9 +26,13 @@ e2e            : the same metric through the public Python operator with the
                  STATE (it persists on the device between steps), not a step
                  input; `e2e_staged` additionally reports the staged entry point
                  that copies the whole cache from host memory each call.
+e2e_graph      : (N=1) the same end-to-end step captured once and replayed as a
+                 CUDA graph; information beside `e2e`, never instead of it.
 roofline       : HBM bound; achieved = algorithmic bytes / step time (partial
                  kernel incl. its in-kernel merge, plus the launch gap between
-                 steps); peak = measured copy bandwidth.
+                 steps); peak = measured copy bandwidth; `read_only_stream`
+                 (N=1) = a read-only pass of the library's own streaming kernel,
+                 measured live, and the fraction of it that was achieved.
 decode_step    : (N=1, contiguous) the whole step on the device: rope of q and k_new +
                  cache write (one launch) followed by the attention kernel.
 cpu_baseline   : the reference's own CPU implementation (built from the
@@ -625,6 +629,46 @@ def run_ours(args, w, rank, world, local_rank):
     h2d = q_host.numel() * q_host.element_size() + (lens_host.numel() * 4 if lens_host is not None else 0)
     d2h = out_host.numel() * out_host.element_size()
 
+    # ---- the same end-to-end step replayed from a CUDA graph (one graph per K/V set: copy in, decode, copy
+    # out), as a latency-conscious caller of the capturable launchers would run it. Reported beside `e2e`,
+    # never instead of it. Single GPU, plain batch-sharded workloads only.
+    e2e_graph_s = None
+    if dist is None and not split_kv and not args.profile and (not w["paged"] or w["Hq"] // w["Hkv"] in (1, 2, 4, 8, 16)):
+        try:
+            side = torch.cuda.Stream()
+            step_graphs = []
+            with torch.cuda.stream(side):
+                for si in range(n_sets):
+                    k, v = sets[si]
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        q_dev.copy_(q_host, non_blocking=True)
+                        if lens_dev is not None:
+                            lens_dev.copy_(lens_host, non_blocking=True)
+                        o = (ft.attention_decode_paged(q_dev, k, v, table, lens_dev) if w["paged"]
+                             else ft.attention_decode(q_dev, k, v, lens_dev))
+                        out_host.copy_(o, non_blocking=True)
+                    step_graphs.append(g)
+            torch.cuda.synchronize()
+
+            def e2e_graph_step(i):
+                step_graphs[i % n_sets].replay()
+                torch.cuda.synchronize()
+                return float(out_host[0, 0, 0])
+
+            for i in range(3):
+                e2e_graph_step(i)
+            rounds_g = []
+            for _ in range(3):
+                t0 = time.perf_counter()
+                for i in range(args.steps):
+                    e2e_graph_step(i)
+                rounds_g.append(time.perf_counter() - t0)
+            e2e_graph_s = statistics.median(rounds_g)
+            del step_graphs
+        except Exception as exc:      # capture refused by this torch build: the plain figure stands alone
+            print("e2e graph variant skipped: %r" % (exc,), file=sys.stderr)
+
     # ---- max over ranks (round by round), then the median round
     round_ms = max_over_ranks(torch, dist, device, round_ms)
     e2e_rounds = max_over_ranks(torch, dist, device, e2e_rounds)
@@ -694,6 +738,12 @@ def run_ours(args, w, rank, world, local_rank):
         "device_status": status,
         "clocks": clocks,
     }
+    if e2e_graph_s is not None:
+        line["e2e_graph"] = {"value": job_bytes / (e2e_graph_s / args.steps) / 1e9, "unit": "GB/s",
+                             "ms_per_step": e2e_graph_s / args.steps * 1e3,
+                             "note": "the e2e step (H2D of q/lens from pinned memory, decode, D2H of the result) "
+                                     "captured once per K/V set and replayed as a CUDA graph, then synchronised and "
+                                     "read on the host every step"}
     if world == 1 and not args.profile:
         rs = read_only_stream_gbs(torch, device)
         if rs:
