@@ -69,8 +69,11 @@ def _launcher(family, dtype):
 _raw_stream = getattr(getattr(torch, "_C", None), "_cuda_getCurrentRawStream", None)
 
 
+_Tensor = torch.Tensor if torch is not None else ()
+
+
 def _on_gpu(x):
-    return torch is not None and torch.is_tensor(x) and x.is_cuda
+    return isinstance(x, _Tensor) and x.is_cuda
 
 
 def _gqa_heads(hq, hkv, paged=False):
@@ -150,9 +153,8 @@ class _DeviceCall:
     def dims(self, name, layout):
         """Shape of operand `name`, which must have as many dimensions as `layout` names (e.g. "B Hq D")."""
         t = self.tensors[name]
-        want = layout.split()
-        if t.ndim != len(want):
-            raise ValueError(f"{name}: {t.ndim}-D tensor where [{', '.join(want)}] is expected")
+        if t.ndim != layout.count(" ") + 1:
+            raise ValueError(f"{name}: {t.ndim}-D tensor where [{', '.join(layout.split())}] is expected")
         return tuple(t.shape)
 
     def same_shape(self, name, other):
@@ -176,8 +178,9 @@ class _DeviceCall:
     def launch(self, fn, *args):
         """Run launcher `fn(*args, stream)` on the current stream of this call's device."""
         idx = self.device.index
-        if idx is None or idx == torch.cuda.current_device():
-            return fn(*args, self._stream(torch.cuda.current_device()))
+        cur = torch.cuda.current_device()
+        if idx is None or idx == cur:
+            return fn(*args, self._stream(cur))
         with torch.cuda.device(idx):
             return fn(*args, self._stream(idx))
 

@@ -669,7 +669,7 @@ int decode_common(int dt, const void* q, const void* k, const void* v, const int
     if ((rc = device_state(&dev))) return rc;
     const DecodePlan pl = plan_decode(dt, q, k, v, table != nullptr, lens != nullptr, batch, hq, hkv, rows, page, dim,
                                       dev->sm_count, peers != nullptr);
-    if (!peers && !arena_covers(*dev, pl.words, pl.ml_b, pl.acc_b) && stream_is_capturing(cs)) {
+    if (!peers && !partial && !arena_covers(*dev, pl.words, pl.ml_b, pl.acc_b) && stream_is_capturing(cs)) {
         // The workspace this launch wants does not exist yet and a capture is no place to allocate it. Like
         // the reference, which then uses its workspace-free single kernel for this launch and for the whole
         // captured graph (src/attention.cu:1498-1509), degrade to a launch that needs none: the generic kernel,
